@@ -1,0 +1,12 @@
+"""gigaslop_b200: B200 (sm_100a) implementation of gigaslop's quantized-GEMM hot path.
+
+The product is ``libgigaslop_b200.so`` (hand-written CUDA, C ABI declared in
+``include/gigaslop_b200/``); this package is the thin PyTorch-facing host layer.
+"""
+from ._lib import LIB_PATH, device_status, lib  # noqa: F401
+from .ops import (  # noqa: F401
+    quantize_tensor, fp8_quantize_per_token, gemm_i8_i32, gemm_i8, gemm_fp8, gemm_i8_rotary,
+    gemm_fp8_rotary, dual_gemm_i8_silu, dual_gemm_fp8_silu,
+)
+
+__version__ = "0.1.0"

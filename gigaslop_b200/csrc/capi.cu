@@ -1,0 +1,113 @@
+// extern "C" surface of libgigaslop_b200 (see include/gigaslop_b200/gigaslop_b200.h).
+#include "capi_internal.h"
+#include "gemm_kernel.cuh"
+
+using namespace gsb;
+
+static inline cudaStream_t S(gsb200_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+extern "C" {
+
+const char* gsb200_version(void) { return "gigaslop_b200 0.1 (sm_100a)"; }
+
+int32_t gsb200_init(void) { return ensure_device(); }
+
+int32_t gsb200_device_status(uint32_t out[4]) {
+  if (!out) return GSB200_ERR_BAD_ARG;
+  return read_clear_status(out);
+}
+
+int32_t gsb200_set_spin_budget(uint32_t clocks) { return set_spin_budget(clocks); }
+
+int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream) { return selftest_wait_timeout(S(stream)); }
+
+int32_t gsb200_ptq_int8(const void* x, int32_t x_dtype, int64_t ldx, int8_t* q, int64_t ldq, float* scale, int64_t M,
+                        int32_t K, gsb200_stream_t stream) {
+  return launch_ptq(x, x_dtype, ldx, q, ldq, scale, M, K, 0, S(stream));
+}
+
+int32_t gsb200_ptq_fp8(const void* x, int32_t x_dtype, int64_t ldx, uint8_t* q, int64_t ldq, float* scale, int64_t M,
+                       int32_t K, int32_t torch_formulation, gsb200_stream_t stream) {
+  return launch_ptq(x, x_dtype, ldx, q, ldq, scale, M, K, torch_formulation ? 2 : 1, S(stream));
+}
+
+static GemmArgs base_args(int kind, int epi, const void* A, int64_t lda, const void* B0, const void* B1, int64_t ldb,
+                          void* C, int64_t ldc, const float* sa, const float* sb0, const float* sb1, int64_t M,
+                          int32_t N, int32_t K, int32_t flags) {
+  GemmArgs a{};
+  a.kind = kind; a.epi = epi;
+  a.A = A; a.lda = lda; a.B0 = B0; a.B1 = B1; a.ldb = ldb; a.C = C; a.ldc = ldc;
+  a.scale_a = sa; a.scale_b0 = sb0; a.scale_b1 = sb1;
+  a.M = M; a.N = N; a.K = K; a.flags = flags;
+  return a;
+}
+
+int32_t gsb200_gemm_i8_i32(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, int32_t* C, int64_t ldc,
+                           int64_t M, int32_t N, int32_t K, gsb200_stream_t stream) {
+  return launch_gemm(base_args(KIND_I8, EPI_I32, A, lda, B, nullptr, ldb, C, ldc, nullptr, nullptr, nullptr, M, N, K, 0),
+                     S(stream));
+}
+
+int32_t gsb200_gemm_i8_f16(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, void* C, int64_t ldc,
+                           const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K, int32_t flags,
+                           gsb200_stream_t stream) {
+  return launch_gemm(base_args(KIND_I8, EPI_DEQUANT, A, lda, B, nullptr, ldb, C, ldc, scale_a, scale_b, nullptr, M, N,
+                               K, flags),
+                     S(stream));
+}
+
+static int32_t rotary_common(int kind, const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
+                             const float* scale_a, const float* scale_b, const float* sin_tab, const float* cos_tab,
+                             int64_t M, int32_t N, int32_t K, int32_t nhead, int32_t head_dim, int32_t rotary_dim,
+                             int32_t seqlen, int64_t row_offset, int32_t flags, gsb200_stream_t stream) {
+  GemmArgs a = base_args(kind, EPI_ROTARY, A, lda, B, nullptr, ldb, C, ldc, scale_a, scale_b, nullptr, M, N, K, flags);
+  a.sin_tab = sin_tab; a.cos_tab = cos_tab;
+  a.nhead = nhead; a.head_dim = head_dim; a.rotary_dim = rotary_dim; a.seqlen = seqlen; a.row_offset = row_offset;
+  return launch_gemm(a, S(stream));
+}
+
+int32_t gsb200_gemm_i8_rotary_f16(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, void* C, int64_t ldc,
+                                  const float* scale_a, const float* scale_b, const float* sin_tab,
+                                  const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,
+                                  int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
+                                  int32_t flags, gsb200_stream_t stream) {
+  return rotary_common(KIND_I8, A, lda, B, ldb, C, ldc, scale_a, scale_b, sin_tab, cos_tab, M, N, K, nhead, head_dim,
+                       rotary_dim, seqlen, row_offset, flags, stream);
+}
+
+int32_t gsb200_dual_gemm_i8_silu_f16(const int8_t* A, int64_t lda, const int8_t* B_gate, const int8_t* B_up,
+                                     int64_t ldb, void* C, int64_t ldc, const float* scale_a,
+                                     const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,
+                                     int32_t K, int32_t flags, gsb200_stream_t stream) {
+  return launch_gemm(base_args(KIND_I8, EPI_SILU, A, lda, B_gate, B_up, ldb, C, ldc, scale_a, scale_b_gate, scale_b_up,
+                               M, N, K, flags),
+                     S(stream));
+}
+
+int32_t gsb200_gemm_fp8_f16(const uint8_t* A, int64_t lda, const uint8_t* B, int64_t ldb, void* C, int64_t ldc,
+                            const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K, int32_t flags,
+                            gsb200_stream_t stream) {
+  return launch_gemm(base_args(KIND_F8, EPI_DEQUANT, A, lda, B, nullptr, ldb, C, ldc, scale_a, scale_b, nullptr, M, N,
+                               K, flags),
+                     S(stream));
+}
+
+int32_t gsb200_gemm_fp8_rotary_f16(const uint8_t* A, int64_t lda, const uint8_t* B, int64_t ldb, void* C, int64_t ldc,
+                                   const float* scale_a, const float* scale_b, const float* sin_tab,
+                                   const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,
+                                   int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
+                                   int32_t flags, gsb200_stream_t stream) {
+  return rotary_common(KIND_F8, A, lda, B, ldb, C, ldc, scale_a, scale_b, sin_tab, cos_tab, M, N, K, nhead, head_dim,
+                       rotary_dim, seqlen, row_offset, flags, stream);
+}
+
+int32_t gsb200_dual_gemm_fp8_silu_f16(const uint8_t* A, int64_t lda, const uint8_t* B_gate, const uint8_t* B_up,
+                                      int64_t ldb, void* C, int64_t ldc, const float* scale_a,
+                                      const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,
+                                      int32_t K, int32_t flags, gsb200_stream_t stream) {
+  return launch_gemm(base_args(KIND_F8, EPI_SILU, A, lda, B_gate, B_up, ldb, C, ldc, scale_a, scale_b_gate, scale_b_up,
+                               M, N, K, flags),
+                     S(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,220 @@
+// Host side of the tcgen05 GEMM family: argument validation, TMA tensor-map
+// encoding and launch of the persistent kernel (one CTA per SM).
+#include <cuda.h>
+
+#include "capi_internal.h"
+#include "gemm_kernel.cuh"
+
+namespace gsb {
+
+// ---- driver entry point for tensor-map encoding (no link-time libcuda dependency) -------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `esz`-byte elements with a box of box_cols x box_rows and
+// the 128-byte swizzle (box_cols * esz must be 128).
+static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows,
+                        uint64_t cols, uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld_elems * (uint64_t)esz};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "gigaslop_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r);
+    return false;
+  }
+  return true;
+}
+
+// ---- per-device state -------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+static int g_dev_ok[kMaxDevices];       // 0 unknown, 1 ok, -1 unsupported
+static int g_dev_sms[kMaxDevices];
+
+template <int KIND, int EPI>
+static cudaError_t set_attr() {
+  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              GEMM_SMEM_BYTES);
+}
+
+int32_t ensure_device() {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return GSB200_ERR_DEVICE;
+  if (g_dev_ok[dev] == 1) return GSB200_OK;
+  if (g_dev_ok[dev] == -1) return GSB200_ERR_DEVICE;
+  int major = 0, sms = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (major != 10) {
+    fprintf(stderr, "gigaslop_b200: device %d is sm_%d*, this library only carries sm_100a code\n", dev, major * 10);
+    g_dev_ok[dev] = -1;
+    return GSB200_ERR_DEVICE;
+  }
+  cudaError_t errs[] = {
+      set_attr<KIND_I8, EPI_I32>(),     set_attr<KIND_I8, EPI_DEQUANT>(), set_attr<KIND_I8, EPI_ROTARY>(),
+      set_attr<KIND_I8, EPI_SILU>(),    set_attr<KIND_F8, EPI_DEQUANT>(), set_attr<KIND_F8, EPI_ROTARY>(),
+      set_attr<KIND_F8, EPI_SILU>()};
+  for (cudaError_t er : errs)
+    if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
+  if (!encode_fn()) {
+    fprintf(stderr, "gigaslop_b200: cuTensorMapEncodeTiled not available from the driver\n");
+    return GSB200_ERR_DEVICE;
+  }
+  g_dev_sms[dev] = sms;
+  g_dev_ok[dev] = 1;
+  return GSB200_OK;
+}
+
+int sm_count() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices && g_dev_sms[dev] > 0) ? g_dev_sms[dev] : 148;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int KIND, int EPI>
+static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1,
+                               const CUtensorMap& tc, const GemmParams& p, int grid, cudaStream_t st) {
+  gemm_tcgen05_kernel<KIND, EPI><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+  return cudaGetLastError();
+}
+
+int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
+  if (a.M == 0) return GSB200_OK;
+  if (a.M < 0 || a.M > 0x7fffff00ll || a.N <= 0 || a.K <= 0) return GSB200_ERR_BAD_ARG;
+  if (!a.A || !a.B0 || !a.C) return GSB200_ERR_BAD_ARG;
+  if (!aligned16(a.A) || !aligned16(a.B0) || !aligned16(a.C)) return GSB200_ERR_BAD_ARG;
+  if (a.K % 16 != 0 || a.lda < a.K || a.ldb < a.K || a.lda % 16 != 0 || a.ldb % 16 != 0) return GSB200_ERR_BAD_ARG;
+  if (a.ldc < a.N) return GSB200_ERR_BAD_ARG;
+  const bool dual = a.epi == EPI_SILU;
+  if (a.epi == EPI_I32) {
+    if (a.N % 4 != 0 || a.ldc % 4 != 0) return GSB200_ERR_BAD_ARG;
+  } else {
+    if (a.N % 8 != 0 || a.ldc % 8 != 0) return GSB200_ERR_BAD_ARG;
+    if (!a.scale_a || !a.scale_b0) return GSB200_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(a.scale_b0) & 15)) return GSB200_ERR_BAD_ARG;
+  }
+  if (dual) {
+    if (!a.B1 || !aligned16(a.B1) || !a.scale_b1 || (reinterpret_cast<uintptr_t>(a.scale_b1) & 15))
+      return GSB200_ERR_BAD_ARG;
+  }
+  int rot_cols = 0;
+  if (a.epi == EPI_ROTARY) {
+    if (!a.sin_tab || !a.cos_tab || !aligned16(a.sin_tab) || !aligned16(a.cos_tab)) return GSB200_ERR_BAD_ARG;
+    if (a.seqlen < 1 || a.nhead < 1 || a.row_offset < 0) return GSB200_ERR_BAD_ARG;
+    if (a.head_dim != 64 || a.rotary_dim != 64) return GSB200_ERR_UNSUPPORTED;
+    rot_cols = 2 * a.nhead * a.head_dim;
+    if (rot_cols > a.N || a.N % 64 != 0) return GSB200_ERR_BAD_ARG;
+  }
+  int32_t rc = ensure_device();
+  if (rc != GSB200_OK) return rc;
+
+  const int out_cols_per_tile = dual ? BN / 2 : BN;
+  GemmParams p{};
+  p.M = (int)a.M; p.N = a.N; p.K = a.K;
+  p.m_blocks = (int)((a.M + BM - 1) / BM);
+  p.n_blocks = (a.N + out_cols_per_tile - 1) / out_cols_per_tile;
+  p.k_blocks = (a.K + BK - 1) / BK;
+  p.C = a.C; p.ldc = a.ldc;
+  p.scale_a = a.scale_a; p.scale_b0 = a.scale_b0; p.scale_b1 = a.scale_b1;
+  p.sin_tab = a.sin_tab; p.cos_tab = a.cos_tab;
+  p.seqlen = a.seqlen > 0 ? a.seqlen : 1;
+  p.rot_cols = rot_cols;
+  p.row_offset = (int)(a.row_offset % p.seqlen);
+  p.direct_store = (a.flags & GSB200_FLAG_DIRECT_STORE) ? 1 : 0;
+  const long long tiles = (long long)p.m_blocks * p.n_blocks;
+  if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
+
+  CUtensorMap ta, tb0, tb1, tc;
+  const CUtensorMapDataType u8 = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  bool ok = make_map_2d(&ta, u8, 1, a.A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
+  ok = ok && make_map_2d(&tb0, u8, 1, a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
+  ok = ok && make_map_2d(&tb1, u8, 1, dual ? a.B1 : a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
+  if (a.epi != EPI_I32)
+    ok = ok && make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.C, (uint64_t)a.M, (uint64_t)a.N,
+                           (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS);
+  else
+    tc = ta;
+  if (!ok) return GSB200_ERR_BAD_ARG;
+
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  cudaError_t e = cudaErrorInvalidValue;
+  if (a.kind == KIND_I8) {
+    switch (a.epi) {
+      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, st); break;
+      default: return GSB200_ERR_BAD_ARG;
+    }
+  } else if (a.kind == KIND_F8) {
+    switch (a.epi) {
+      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, st); break;
+      default: return GSB200_ERR_BAD_ARG;
+    }
+  } else {
+    return GSB200_ERR_BAD_ARG;
+  }
+  return cuda_status(e, "gemm launch");
+}
+
+// ---- self-test of the bounded wait ------------------------------------------------------------
+// One warp waits on an mbarrier that nothing ever arrives at.  With a small spin budget the
+// wait gives up, records ST_TIMEOUT_EPILOGUE in the status word and the kernel returns
+// normally: the give-up path is exercised without hanging or faulting the device.
+__global__ void selftest_wait_timeout_kernel() {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag = 0; fence_mbar_init(); }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, ST_TIMEOUT_EPILOGUE, 0xdead);
+  __syncthreads();
+}
+
+int32_t selftest_wait_timeout(cudaStream_t st) {
+  selftest_wait_timeout_kernel<<<1, 32, 0, st>>>();
+  return cuda_status(cudaGetLastError(), "selftest launch");
+}
+
+// ---- status word --------------------------------------------------------------------------------
+int32_t read_clear_status(uint32_t out[4]) {
+  unsigned int h[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(h, g_status, sizeof(h));
+  if (e != cudaSuccess) return cuda_status(e, "status read");
+  for (int i = 0; i < 4; ++i) out[i] = h[i];
+  if (h[0] != 0 || h[1] != 0) {
+    unsigned int z[2] = {0, 0};
+    e = cudaMemcpyToSymbol(g_status, z, sizeof(z));
+    if (e != cudaSuccess) return cuda_status(e, "status clear");
+  }
+  return GSB200_OK;
+}
+
+int32_t set_spin_budget(uint32_t clocks) {
+  cudaError_t e = cudaMemcpyToSymbol(g_status, &clocks, sizeof(clocks), 2 * sizeof(unsigned int));
+  return cuda_status(e, "set spin budget");
+}
+
+}  // namespace gsb

@@ -1,0 +1,5 @@
+// libgigaslop_b200 is built as one translation unit so that the device status
+// word and the inline PTX helpers are shared without relocatable device code.
+#include "quant.cu"
+#include "gemm.cu"
+#include "capi.cu"

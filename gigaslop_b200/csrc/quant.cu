@@ -1,0 +1,183 @@
+// Per-token (per-row) absmax quantisers: fp16/fp32 [M,K] -> int8 or E4M3 [M,K]
+// plus one fp32 dequantisation scale per row.  HBM-bound: each row is read once
+// with 16/32-byte vector loads, held in registers across the warp-shuffle max
+// reduction, and written once with 8-byte stores.  One warp owns one row.
+//
+// The arithmetic order is part of the contract (results are bit-exact against the
+// CPU reference): INT8 uses qs = 127/amax (IEEE division), q = rne(x*qs), scale =
+// 1/qs; FP8 has the kernel formulation (x * (448/amax)) and the torch formulation
+// (x / (amax/448)).
+#include <cuda_fp8.h>
+
+#include "capi_internal.h"
+
+namespace gsb {
+
+constexpr int QUANT_WARPS = 8;
+
+template <typename Tin>
+__device__ __forceinline__ void load8(const Tin* p, float (&v)[8]);
+
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[8]) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p + 4));
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+__device__ __forceinline__ float warp_max(float m) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  return m;
+}
+
+__device__ __forceinline__ uint32_t q_i8(float x, float qs) {
+  int q = __float2int_rn(__fmul_rn(x, qs));      // round half to even
+  q = max(-127, min(127, q));
+  return static_cast<uint32_t>(q) & 0xffu;
+}
+
+__device__ __forceinline__ uint2 pack_i8(const float (&v)[8], float qs) {
+  uint2 o;
+  o.x = q_i8(v[0], qs) | (q_i8(v[1], qs) << 8) | (q_i8(v[2], qs) << 16) | (q_i8(v[3], qs) << 24);
+  o.y = q_i8(v[4], qs) | (q_i8(v[5], qs) << 8) | (q_i8(v[6], qs) << 16) | (q_i8(v[7], qs) << 24);
+  return o;
+}
+
+// FP8: mode 0 multiplies by inv = 448/amax; mode 1 divides by scale = amax/448 and clamps.
+template <int MODE>
+__device__ __forceinline__ float fp8_prescale(float x, float f) {
+  if constexpr (MODE == 0) return __fmul_rn(x, f);
+  else return fminf(fmaxf(__fdiv_rn(x, f), -448.f), 448.f);
+}
+template <int MODE>
+__device__ __forceinline__ uint2 pack_e4m3(const float (&v)[8], float f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 pr = make_float2(fp8_prescale<MODE>(v[2 * i], f), fp8_prescale<MODE>(v[2 * i + 1], f));
+    w[i] = __nv_cvt_float2_to_fp8x2(pr, __NV_SATFINITE, __NV_E4M3);    // rn, saturate to +-448
+  }
+  uint2 o;
+  o.x = w[0] | (w[1] << 16);
+  o.y = w[2] | (w[3] << 16);
+  return o;
+}
+
+// FMT: 0 = int8, 1 = e4m3 kernel formulation, 2 = e4m3 torch formulation.
+// NV > 0: the row (<= NV*256 elements) is cached in registers.  NV == 0: any K, second pass re-reads.
+template <typename Tin, int FMT, int NV>
+__global__ void __launch_bounds__(QUANT_WARPS * 32)
+ptq_kernel(const Tin* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+           float* __restrict__ scale, long long M, int K) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * QUANT_WARPS + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const Tin* xr = x + row * ldx;
+  uint8_t* qr = q + row * ldq;
+  const int nvec = K >> 3;
+
+  float vals[NV > 0 ? NV : 1][8];
+  float amax = 0.f;
+  if constexpr (NV > 0) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        load8<Tin>(xr + v * 8, vals[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vals[i][j]));
+      }
+    }
+  } else {
+    for (int v = lane; v < nvec; v += 32) {
+      load8<Tin>(xr + v * 8, vals[0]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vals[0][j]));
+    }
+  }
+  amax = warp_max(amax);
+
+  float f;   // factor applied to the elements
+  float s;   // dequantisation scale written out
+  if constexpr (FMT == 0) {
+    amax = fmaxf(amax, 1e-8f);
+    f = __fdiv_rn(127.0f, amax);
+    s = __frcp_rn(f);
+  } else {
+    amax = fmaxf(amax, 1e-12f);
+    s = __fdiv_rn(amax, 448.0f);
+    f = (FMT == 1) ? __fdiv_rn(448.0f, amax) : s;
+  }
+  if (lane == 0) scale[row] = s;
+
+  auto emit = [&](int v, const float (&vv)[8]) {
+    uint2 o;
+    if constexpr (FMT == 0) o = pack_i8(vv, f);
+    else if constexpr (FMT == 1) o = pack_e4m3<0>(vv, f);
+    else o = pack_e4m3<1>(vv, f);
+    *reinterpret_cast<uint2*>(qr + v * 8) = o;
+  };
+  if constexpr (NV > 0) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) emit(v, vals[i]);
+    }
+  } else {
+    for (int v = lane; v < nvec; v += 32) {
+      load8<Tin>(xr + v * 8, vals[0]);
+      emit(v, vals[0]);
+    }
+  }
+}
+
+template <typename Tin, int FMT>
+static cudaError_t launch_fmt(const void* x, long long ldx, void* q, long long ldq, float* scale, long long M, int K,
+                              cudaStream_t st) {
+  const unsigned blocks = (unsigned)((M + QUANT_WARPS - 1) / QUANT_WARPS);
+  const Tin* xp = static_cast<const Tin*>(x);
+  uint8_t* qp = static_cast<uint8_t*>(q);
+  if (K <= 512) ptq_kernel<Tin, FMT, 2><<<blocks, QUANT_WARPS * 32, 0, st>>>(xp, ldx, qp, ldq, scale, M, K);
+  else if (K <= 1024) ptq_kernel<Tin, FMT, 4><<<blocks, QUANT_WARPS * 32, 0, st>>>(xp, ldx, qp, ldq, scale, M, K);
+  else if (K <= 2048) ptq_kernel<Tin, FMT, 8><<<blocks, QUANT_WARPS * 32, 0, st>>>(xp, ldx, qp, ldq, scale, M, K);
+  else ptq_kernel<Tin, FMT, 0><<<blocks, QUANT_WARPS * 32, 0, st>>>(xp, ldx, qp, ldq, scale, M, K);
+  return cudaGetLastError();
+}
+
+int32_t launch_ptq(const void* x, int x_dtype, long long ldx, void* q, long long ldq, float* scale, long long M, int K,
+                   int fmt, cudaStream_t st) {
+  if (M == 0) return GSB200_OK;
+  if (!x || !q || !scale || M < 0 || K <= 0) return GSB200_ERR_BAD_ARG;
+  if (K % 8 != 0 || ldx < K || ldq < K || ldq % 8 != 0) return GSB200_ERR_BAD_ARG;
+  const int esz = x_dtype == GSB200_F16 ? 2 : 4;
+  if (x_dtype != GSB200_F16 && x_dtype != GSB200_F32) return GSB200_ERR_BAD_ARG;
+  if ((ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+    return GSB200_ERR_BAD_ARG;
+  if ((M + QUANT_WARPS - 1) / QUANT_WARPS > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
+  cudaError_t e;
+  if (x_dtype == GSB200_F16) {
+    if (fmt == 0) e = launch_fmt<__half, 0>(x, ldx, q, ldq, scale, M, K, st);
+    else if (fmt == 1) e = launch_fmt<__half, 1>(x, ldx, q, ldq, scale, M, K, st);
+    else if (fmt == 2) e = launch_fmt<__half, 2>(x, ldx, q, ldq, scale, M, K, st);
+    else return GSB200_ERR_BAD_ARG;
+  } else {
+    if (fmt == 0) e = launch_fmt<float, 0>(x, ldx, q, ldq, scale, M, K, st);
+    else if (fmt == 1) e = launch_fmt<float, 1>(x, ldx, q, ldq, scale, M, K, st);
+    else if (fmt == 2) e = launch_fmt<float, 2>(x, ldx, q, ldq, scale, M, K, st);
+    else return GSB200_ERR_BAD_ARG;
+  }
+  return cuda_status(e, "ptq launch");
+}
+
+}  // namespace gsb

@@ -1,0 +1,157 @@
+"""PyTorch-facing host functions over the C ABI.  torch supplies device memory
+and streams; every byte of compute happens in libgigaslop_b200.so.
+
+Function names and argument meaning follow the reference's host helpers
+(``quantize_tensor``, ``fp8_quantize_per_token``) and kernels.
+"""
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("gigaslop_b200 operates on CUDA tensors only (no CPU fallback)")
+
+
+def _rowmajor(t, name):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with unit inner stride")
+    return t
+
+
+def _dt(t):
+    if t.dtype == torch.float16:
+        return _lib.F16
+    if t.dtype == torch.float32:
+        return _lib.F32
+    raise TypeError("activations must be float16 or float32")
+
+
+def quantize_tensor(t, dim=-1, out=None, out_scale=None):
+    """Per-row symmetric absmax INT8 quantiser; same contract as the reference's
+    ``quantize_tensor`` (cute/bench_quant_i8.py:15-31): returns (int8 [M,K], fp32 dequant scale [M])."""
+    if dim not in (-1, t.dim() - 1):
+        raise ValueError("only per-row (last-dim) quantisation is on the hot path")
+    _need_cuda(t)
+    x = _rowmajor(t, "t")
+    M, K = x.shape
+    q = out if out is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = out_scale if out_scale is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
+    check(lib().gsb200_ptq_int8(x.data_ptr(), _dt(x), x.stride(0), q.data_ptr(), q.stride(0), s.data_ptr(),
+                                M, K, _stream()), "quantize_tensor")
+    return q, s
+
+
+def fp8_quantize_per_token(x, torch_formulation=True, out=None, out_scale=None):
+    """Per-row E4M3 quantiser (fly/rdna_fp8_preshuffle_gemm.py:57-70); ``torch_formulation=False``
+    selects the device-kernel arithmetic of fly/rdna_fp8_per_token_quantize.py."""
+    _need_cuda(x)
+    x = _rowmajor(x, "x")
+    M, K = x.shape
+    q = out if out is not None else torch.empty((M, K), dtype=torch.float8_e4m3fn, device=x.device)
+    s = out_scale if out_scale is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
+    check(lib().gsb200_ptq_fp8(x.data_ptr(), _dt(x), x.stride(0), q.data_ptr(), q.stride(0), s.data_ptr(),
+                               M, K, 1 if torch_formulation else 0, _stream()), "fp8_quantize_per_token")
+    return q, s
+
+
+def _check_ab(A, B, dtypes):
+    _need_cuda(A, B)
+    _rowmajor(A, "A"); _rowmajor(B, "B")
+    if A.dtype not in dtypes or B.dtype not in dtypes:
+        raise TypeError(f"operands must be one of {dtypes}")
+    if A.shape[1] != B.shape[1]:
+        raise ValueError("A is [M,K], B is [N,K]: K mismatch")
+    return A.shape[0], B.shape[0], A.shape[1]
+
+
+_I8 = (torch.int8,)
+_F8 = (torch.float8_e4m3fn, torch.uint8)
+
+
+def gemm_i8_i32(A, B, out=None):
+    """Exact int32 ``A[M,K] . B[N,K]^T`` (cute/ampere_gemm_i8.py TensorOpGemmI8, int32 output)."""
+    M, N, K = _check_ab(A, B, _I8)
+    C = out if out is not None else torch.empty((M, N), dtype=torch.int32, device=A.device)
+    check(lib().gsb200_gemm_i8_i32(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(), C.stride(0),
+                                   M, N, K, _stream()), "gemm_i8_i32")
+    return C
+
+
+def _gemm_f16(fn, name, A, B, scale_a, scale_b, out, flags, dtypes):
+    M, N, K = _check_ab(A, B, dtypes)
+    _need_cuda(scale_a, scale_b)
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=A.device)
+    check(fn(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(), C.stride(0),
+             scale_a.data_ptr(), scale_b.data_ptr(), M, N, K, flags, _stream()), name)
+    return C
+
+
+def gemm_i8(A, B, scale_a, scale_b, out=None, flags=0):
+    """W8A8 GEMM with per-token x per-channel dequant to fp16 (cute/ampere_gemm_i8_quant_rmem.py)."""
+    return _gemm_f16(lib().gsb200_gemm_i8_f16, "gemm_i8", A, B, scale_a, scale_b, out, flags, _I8)
+
+
+def gemm_fp8(A, B, scale_a, scale_b, out=None, flags=0):
+    """FP8 GEMM, ``B`` K-major ``[N,K]`` (fly/rdna_fp8_preshuffle_gemm.py compile_fp8_gemm)."""
+    return _gemm_f16(lib().gsb200_gemm_fp8_f16, "gemm_fp8", A, B, scale_a, scale_b, out, flags, _F8)
+
+
+def _rotary(fn, name, A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
+            row_offset, out, flags, dtypes):
+    M, N, K = _check_ab(A, B, dtypes)
+    _need_cuda(scale_a, scale_b, sin_buf, cos_buf)
+    if sin_buf.dtype != torch.float32 or not sin_buf.is_contiguous() or not cos_buf.is_contiguous():
+        raise ValueError("sin/cos must be contiguous float32 [seqlen, rotary_dim/2]")
+    if sin_buf.shape[0] < seqlen or sin_buf.shape[1] != rotary_dim // 2:
+        raise ValueError("sin/cos table smaller than seqlen")
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=A.device)
+    check(fn(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(), C.stride(0),
+             scale_a.data_ptr(), scale_b.data_ptr(), sin_buf.data_ptr(), cos_buf.data_ptr(),
+             M, N, K, nhead, head_dim, rotary_dim, seqlen, row_offset, flags, _stream()), name)
+    return C
+
+
+def gemm_i8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
+                   row_offset=0, out=None, flags=0):
+    """QKV GEMM + rotary epilogue (cute/ampere_gemm_i8_rotary.py TensorOpGemmI8Rotary)."""
+    return _rotary(lib().gsb200_gemm_i8_rotary_f16, "gemm_i8_rotary", A, B, scale_a, scale_b, sin_buf, cos_buf,
+                   nhead, head_dim, rotary_dim, seqlen, row_offset, out, flags, _I8)
+
+
+def gemm_fp8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
+                    row_offset=0, out=None, flags=0):
+    """FP8 QKV GEMM + rotary (fly/rdna_fp8_gemm_rotary.py compile_fp8_gemm_rotary)."""
+    return _rotary(lib().gsb200_gemm_fp8_rotary_f16, "gemm_fp8_rotary", A, B, scale_a, scale_b, sin_buf, cos_buf,
+                   nhead, head_dim, rotary_dim, seqlen, row_offset, out, flags, _F8)
+
+
+def _dual(fn, name, A, Bg, Bu, scale_a, sbg, sbu, out, flags, dtypes):
+    M, N, K = _check_ab(A, Bg, dtypes)
+    _check_ab(A, Bu, dtypes)
+    if Bu.shape != Bg.shape or Bu.stride(0) != Bg.stride(0):
+        raise ValueError("gate and up weights must share shape and row stride")
+    _need_cuda(scale_a, sbg, sbu)
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=A.device)
+    check(fn(A.data_ptr(), A.stride(0), Bg.data_ptr(), Bu.data_ptr(), Bg.stride(0), C.data_ptr(), C.stride(0),
+             scale_a.data_ptr(), sbg.data_ptr(), sbu.data_ptr(), M, N, K, flags, _stream()), name)
+    return C
+
+
+def dual_gemm_i8_silu(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=None, flags=0):
+    """``silu(A.Bg^T) * (A.Bu^T)`` (cute/ampere_dual_gemm_i8_silu.py TensorOpDualGemmI8Silu)."""
+    return _dual(lib().gsb200_dual_gemm_i8_silu_f16, "dual_gemm_i8_silu", A, B_gate, B_up, scale_a,
+                 scale_b_gate, scale_b_up, out, flags, _I8)
+
+
+def dual_gemm_fp8_silu(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=None, flags=0):
+    """FP8 SwiGLU dual GEMM (fly/rdna_fp8_dual_gemm_silu.py compile_fp8_dual_gemm_silu)."""
+    return _dual(lib().gsb200_dual_gemm_fp8_silu_f16, "dual_gemm_fp8_silu", A, B_gate, B_up, scale_a,
+                 scale_b_gate, scale_b_up, out, flags, _F8)

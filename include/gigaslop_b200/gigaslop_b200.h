@@ -1,0 +1,118 @@
+/*
+ * gigaslop_b200 -- plain C ABI of the B200 (sm_100a) quantized-GEMM library.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, allocates nothing and returns a status:
+ *   0   success (kernel enqueued)
+ *  <0   argument / capability error (GSB200_ERR_*), nothing was launched
+ *  >0   the cudaError_t of a failed CUDA call (also printed to stderr)
+ * All matrices are row-major; A is [M,K], weights are K-major [N,K] (the layout of
+ * an nn.Linear weight), outputs are [M,N].  Leading dimensions are in elements.
+ * Alignment: base pointers 16 bytes, lda/ldb multiples of 16 (bytes of 8-bit
+ * data), ldc a multiple of 8 (fp16) or 4 (int32); K % 16 == 0; N % 8 == 0.
+ * M is arbitrary (tail rows are handled inside the kernels).
+ *
+ * The reference project exposes each kernel through a generated per-kernel
+ * header (module struct + tensor descriptors + `cute_dsl_<prefix>_wrapper`, or
+ * HIP `fp8_*_wrapper`); those drop-in headers live next to this file and are thin
+ * inline shims over the functions declared here.  Each declaration cites the
+ * reference interface it stands in for (paths relative to the reference root).
+ */
+#ifndef GIGASLOP_B200_H_
+#define GIGASLOP_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GSB200_OK 0
+#define GSB200_ERR_BAD_ARG (-1)      /* null / misaligned pointer, bad size (reference wrappers return -1 for a bad M) */
+#define GSB200_ERR_UNSUPPORTED (-2)  /* shape outside what the kernels were built for */
+#define GSB200_ERR_DEVICE (-3)       /* current device is not an sm_100 part */
+#define GSB200_ERR_TIMEOUT (-4)      /* a bounded device-side wait gave up (see gsb200_device_status) */
+
+#define GSB200_F16 0
+#define GSB200_F32 1
+
+/* bit flags for the `flags` argument of the GEMM entry points */
+#define GSB200_FLAG_DIRECT_STORE 1   /* diagnostic: epilogue stores straight from registers (no smem + TMA store) */
+
+typedef struct CUstream_st* gsb200_stream_t; /* == cudaStream_t */
+
+/* Library / device management.  No reference counterpart: the generated
+ * `<prefix>_Kernel_Module_Load` (cute/main.cpp:95-96) maps onto gsb200_init. */
+const char* gsb200_version(void);
+int32_t gsb200_init(void);                       /* validate the current device, set kernel attributes */
+int32_t gsb200_device_status(uint32_t out[4]);   /* read-and-clear the device status word (0 = healthy) */
+int32_t gsb200_set_spin_budget(uint32_t clocks); /* bound (SM clocks) for device-side waits; 0 restores the default */
+/* Launches one warp that waits on a barrier nothing signals; with a small spin budget the wait gives up and
+ * sets bit 2 of the status word.  Exercises the give-up path without hanging the device. */
+int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream);
+
+/* Per-token symmetric absmax INT8 quantiser: q = rne(x * (127/amax)), scale = 1/(127/amax).
+ * Stands in for quantize_tensor (cute/bench_quant_i8.py:15-31); the reference has no
+ * GPU kernel for it.  Bit-exact with that function on fp32(x). */
+int32_t gsb200_ptq_int8(const void* x, int32_t x_dtype, int64_t ldx, int8_t* q, int64_t ldq, float* scale,
+                        int64_t M, int32_t K, gsb200_stream_t stream);
+
+/* Per-token E4M3 quantiser, scale = amax/448.  torch_formulation = 0: elements = x * (448/amax)
+ * (the device kernel, fly/rdna_fp8_per_token_quantize.py:127-148, exported as fp8_ptq_wrapper
+ * at fly/export_fp8_dual_gemm_silu.py:311-329); 1: elements = clamp(x / scale)
+ * (fp8_quantize_per_token, fly/rdna_fp8_preshuffle_gemm.py:57-70). */
+int32_t gsb200_ptq_fp8(const void* x, int32_t x_dtype, int64_t ldx, uint8_t* q, int64_t ldq, float* scale,
+                       int64_t M, int32_t K, int32_t torch_formulation, gsb200_stream_t stream);
+
+/* C_i32 = A_i8 . B_i8^T.  TensorOpGemmI8 int32-out (cute/ampere_gemm_i8.py:181-702).  N % 4 == 0. */
+int32_t gsb200_gemm_i8_i32(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, int32_t* C, int64_t ldc,
+                           int64_t M, int32_t N, int32_t K, gsb200_stream_t stream);
+
+/* C_f16 = f16( f32(acc) * (sA[m]*sB[n]) ).  TensorOpGemmI8 with the dequant epilogue
+ * (cute/ampere_gemm_i8_quant_rmem.py:181-786; exported as cute_dsl_gemm_i8_std_wrapper,
+ * cute/export_gemm_i8.py:16-28, called at cute/main.cpp:125).  Also the SwiGLU down-projection. */
+int32_t gsb200_gemm_i8_f16(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, void* C, int64_t ldc,
+                           const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K,
+                           int32_t flags, gsb200_stream_t stream);
+
+/* QKV projection with rotary embedding fused into the epilogue.  TensorOpGemmI8Rotary
+ * (cute/ampere_gemm_i8_rotary.py:44-397; wrapper called at cute/main_rotary.cpp:158).
+ * Columns [0, 2*nhead*head_dim) are rotated per head (x0 = first half, x1 = second half of the
+ * head; out0 = x0*cos - x1*sin, out1 = x0*sin + x1*cos), the rest (V) passes through.
+ * sin/cos are fp32 [>= seqlen, rotary_dim/2] row-major; the angle row of output row m is
+ * (m + row_offset) % seqlen (row_offset lets a shard of M keep global positions).
+ * Built for head_dim = rotary_dim = 64; N % 64 == 0. */
+int32_t gsb200_gemm_i8_rotary_f16(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, void* C,
+                                  int64_t ldc, const float* scale_a, const float* scale_b, const float* sin_tab,
+                                  const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,
+                                  int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
+                                  int32_t flags, gsb200_stream_t stream);
+
+/* C_f16 = silu(A.Bg^T * sA*sBg) * (A.Bu^T * sA*sBu).  TensorOpDualGemmI8Silu
+ * (cute/ampere_dual_gemm_i8_silu.py:36-438; export at cute/export_dual_gemm_i8_silu.py:53-63). */
+int32_t gsb200_dual_gemm_i8_silu_f16(const int8_t* A, int64_t lda, const int8_t* B_gate, const int8_t* B_up,
+                                     int64_t ldb, void* C, int64_t ldc, const float* scale_a,
+                                     const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,
+                                     int32_t K, int32_t flags, gsb200_stream_t stream);
+
+/* FP8-E4M3 twins (fp32 accumulate, C = (acc*sA[m])*sB[n]).  Weights are taken K-major [N,K]
+ * (not the RDNA WMMA pre-shuffle of fly/rdna_fp8_preshuffle_gemm.py:40-54).
+ * compile_fp8_gemm (fly/rdna_fp8_preshuffle_gemm.py:94-421), compile_fp8_gemm_rotary
+ * (fly/rdna_fp8_gemm_rotary.py:64-421), compile_fp8_dual_gemm_silu (fly/rdna_fp8_dual_gemm_silu.py:70-395). */
+int32_t gsb200_gemm_fp8_f16(const uint8_t* A, int64_t lda, const uint8_t* B, int64_t ldb, void* C, int64_t ldc,
+                            const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K,
+                            int32_t flags, gsb200_stream_t stream);
+int32_t gsb200_gemm_fp8_rotary_f16(const uint8_t* A, int64_t lda, const uint8_t* B, int64_t ldb, void* C,
+                                   int64_t ldc, const float* scale_a, const float* scale_b, const float* sin_tab,
+                                   const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,
+                                   int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
+                                   int32_t flags, gsb200_stream_t stream);
+int32_t gsb200_dual_gemm_fp8_silu_f16(const uint8_t* A, int64_t lda, const uint8_t* B_gate, const uint8_t* B_up,
+                                      int64_t ldb, void* C, int64_t ldc, const float* scale_a,
+                                      const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,
+                                      int32_t K, int32_t flags, gsb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GIGASLOP_B200_H_ */

@@ -1,0 +1,211 @@
+"""GPU parity: tcgen05 INT8 GEMMs through the C ABI vs the CPU oracle.
+
+Integer accumulators and the dequant / rotary epilogues are compared bit for bit
+against the arithmetic model; every fp16 result is also held to the reference's
+own tolerance against the reference's fp32 host math."""
+import pytest
+import torch
+
+import oracle
+from conftest import load_golden
+from util import T, assert_bitexact, assert_close, f16_equal_up_to_signed_zero, need_lib, rand_i8, rand_scales
+
+pytestmark = pytest.mark.gpu
+
+DIRECT = 1
+
+
+def test_gemm_i32_golden():
+    g = need_lib()
+    gold = load_golden("gemm_i32")
+    for tag in ("small", "full"):
+        c = g.gemm_i8_i32(T(gold["a_" + tag]).cuda(), T(gold["b_" + tag]).cuda())
+        assert_bitexact(c, T(gold["c_" + tag]), f"int32 accumulators ({tag}) vs reference golden")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (128, 256, 512), (1, 8, 16), (127, 264, 144), (129, 512, 512),
+                                   (300, 1536, 512), (1000, 512, 2048), (4096, 1536, 512), (256, 2048, 384)])
+def test_gemm_i32_bitexact(M, N, K):
+    g = need_lib()
+    gen = torch.Generator().manual_seed(M * 131 + N * 17 + K)
+    A, B = rand_i8(gen, M, K), rand_i8(gen, N, K)
+    c = g.gemm_i8_i32(A.cuda(), B.cuda())
+    assert_bitexact(c, oracle.gemm_i32(A, B), f"int32 accumulators {M}x{N}x{K}")
+
+
+def test_gemm_i32_worst_case_magnitude():
+    g = need_lib()
+    A = torch.full((128, 2048), 127, dtype=torch.int8)
+    B = torch.full((256, 2048), -127, dtype=torch.int8)
+    B[::2] = 127
+    c = g.gemm_i8_i32(A.cuda(), B.cuda())
+    assert_bitexact(c, oracle.gemm_i32(A, B))
+
+
+@pytest.mark.parametrize("flags", [0, DIRECT])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (16384, 512, 512), (257, 520, 512), (64, 1536, 512), (2000, 512, 2048)])
+def test_gemm_dequant(M, N, K, flags):
+    g = need_lib()
+    gen = torch.Generator().manual_seed(1000 + M + N + K)
+    A, B = rand_i8(gen, M, K), rand_i8(gen, N, K)
+    sa, sb = rand_scales(gen, M, 5e-3, 5e-2), rand_scales(gen, N)
+    c = g.gemm_i8(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), flags=flags)
+    exact = oracle.gemm_dequant_exact(A, B, sa, sb)
+    assert f16_equal_up_to_signed_zero(c, exact) == 0, "fp16 output differs from the exact-accumulator model"
+    ref = oracle.gemm_dequant_ref(A, B, sa, sb)
+    assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="vs reference fp32 math")
+
+
+def test_gemm_dequant_strided_views():
+    g = need_lib()
+    gen = torch.Generator().manual_seed(5)
+    Abig, Bbig = rand_i8(gen, 200, 1024), rand_i8(gen, 264, 1024)
+    A, B = Abig[:, 256:768], Bbig[:, :512]
+    sa, sb = rand_scales(gen, 200), rand_scales(gen, 264)
+    Cbig = torch.zeros(200, 512, dtype=torch.float16, device="cuda")
+    out = Cbig[:, :264]
+    g.gemm_i8(Abig.cuda()[:, 256:768], Bbig.cuda()[:, :512], sa.cuda(), sb.cuda(), out=out)
+    exact = oracle.gemm_dequant_exact(A.contiguous(), B.contiguous(), sa, sb)
+    assert f16_equal_up_to_signed_zero(out, exact) == 0
+    assert float(Cbig[:, 264:].abs().max()) == 0.0, "wrote outside the N columns"
+
+
+@pytest.mark.parametrize("flags", [0, DIRECT])
+def test_rotary_reference_scenario(flags):
+    """The reference's own JIT parity case: M=64 (4x16), K=512, N=1536 (cute/test_gemm_i8_rotary_vs_openfish.py)."""
+    g = need_lib()
+    gold = load_golden("rotary")
+    nhead, head_dim, rotary_dim, seqlen = (int(v) for v in gold["dims"])
+    a, b, sa, sb, sn, cs = (T(gold[k]) for k in ("a", "b", "sa", "sb", "sin", "cos"))
+    c = g.gemm_i8_rotary(a.cuda(), b.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(),
+                         nhead, head_dim, rotary_dim, seqlen, flags=flags)
+    ref16 = T(gold["c"]).half()
+    err = (c.cpu().float() - ref16.float()).abs().max().item()
+    assert err <= 0.05, f"max abs err {err} vs the reference's 0.05 gate"
+    exact = oracle.rotary_exact(a, b, sa, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)
+    assert f16_equal_up_to_signed_zero(c, exact) == 0
+
+
+@pytest.mark.parametrize("M,seqlen,row_offset,flags", [(256, 1024, 0, 0), (256, 333, 0, 0), (4096, 2048, 0, 0),
+                                                       (1000, 2048, 1536, 0), (130, 16, 5, DIRECT)])
+def test_rotary_shapes(M, seqlen, row_offset, flags):
+    g = need_lib()
+    nhead, head_dim, rotary_dim, K = 8, 64, 64, 512
+    N = 3 * nhead * head_dim
+    gen = torch.Generator().manual_seed(2000 + M + seqlen)
+    X = torch.randn(M, K, generator=gen)
+    A, sa = oracle.quantize_tensor(X)
+    B, sb = rand_i8(gen, N, K), rand_scales(gen, N)
+    sn, cs = oracle.rope_tables(max(seqlen, 16), rotary_dim // 2, head_dim)
+    c = g.gemm_i8_rotary(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(),
+                         nhead, head_dim, rotary_dim, seqlen, row_offset=row_offset, flags=flags)
+    # the oracle indexes angle rows by m % seqlen: emulate the shard offset by prepending rows
+    pad = row_offset
+    Ap = torch.cat([torch.zeros(pad, K, dtype=torch.int8), A])
+    sap = torch.cat([torch.ones(pad), sa])
+    exact = oracle.rotary_exact(Ap, B, sap, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)[pad:]
+    assert f16_equal_up_to_signed_zero(c, exact) == 0
+    ref = oracle.rotary_ref(Ap, B, sap, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)[pad:]
+    assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="rotary vs reference math")
+
+
+def test_rotary_identity_table_equals_plain_gemm():
+    """sin=0, cos=1 must reproduce the plain dequant GEMM (the ROTARY_IDENTITY check of cute/main_rotary.cpp:99-103)."""
+    g = need_lib()
+    gen = torch.Generator().manual_seed(9)
+    A, B = rand_i8(gen, 256, 512), rand_i8(gen, 1536, 512)
+    sa, sb = rand_scales(gen, 256), rand_scales(gen, 1536)
+    sn, cs = torch.zeros(1024, 32), torch.ones(1024, 32)
+    c = g.gemm_i8_rotary(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(), 8, 64, 64, 1024)
+    plain = g.gemm_i8(A.cuda(), B.cuda(), sa.cuda(), sb.cuda())
+    assert f16_equal_up_to_signed_zero(c, plain.cpu()) == 0
+
+
+@pytest.mark.parametrize("flags", [0, DIRECT])
+def test_dual_silu_golden(flags):
+    g = need_lib()
+    gold = load_golden("dual_silu")
+    a, bg, bu, sa, sbg, sbu = (T(gold[k]) for k in ("a", "bg", "bu", "sa", "sbg", "sbu"))
+    c = g.dual_gemm_i8_silu(a.cuda(), bg.cuda(), bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda(), flags=flags)
+    ref = T(gold["c"])
+    assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="SwiGLU vs reference golden")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 2048, 512), (4096, 2048, 512), (65, 136, 512)])
+def test_dual_silu_shapes(M, N, K):
+    g = need_lib()
+    gen = torch.Generator().manual_seed(3000 + M + N)
+    X = torch.randn(M, K, generator=gen)
+    A, sa = oracle.quantize_tensor(X)
+    Bg, Bu = rand_i8(gen, N, K), rand_i8(gen, N, K)
+    sbg, sbu = rand_scales(gen, N), rand_scales(gen, N)
+    c = g.dual_gemm_i8_silu(A.cuda(), Bg.cuda(), Bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda())
+    model = oracle.dual_gemm_silu_model(A, Bg, Bu, sa, sbg, sbu)
+    assert_close(c, model, atol=2 * float(model.float().abs().max()) * 2 ** -11, rtol=2e-3, what="vs kernel model")
+    ref = oracle.dual_gemm_silu_ref(A, Bg, Bu, sa, sbg, sbu)
+    assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="vs reference math")
+
+
+def test_ffn_chain_int8():
+    """quantise -> dual GEMM SiLU -> re-quantise -> down-projection, each stage checked against the
+    oracle fed with the device's own (bit-exact) intermediates so errors do not compound."""
+    g = need_lib()
+    gen = torch.Generator().manual_seed(4004)
+    M, D, F = 1024, 512, 2048
+    x = torch.randn(M, D, generator=gen).half()
+    Wg, Wu, Wd = rand_i8(gen, F, D), rand_i8(gen, F, D), rand_i8(gen, D, F)
+    sg, su, sd = rand_scales(gen, F), rand_scales(gen, F), rand_scales(gen, D)
+    xq, xs = g.quantize_tensor(x.cuda())
+    q_ref, s_ref = oracle.quantize_tensor(x.float())
+    assert_bitexact(xq, q_ref); assert_bitexact(xs, s_ref)
+    h = g.dual_gemm_i8_silu(xq, Wg.cuda(), Wu.cuda(), xs, sg.cuda(), su.cuda())
+    ref_h = oracle.dual_gemm_silu_ref(q_ref, Wg, Wu, s_ref, sg, su)
+    assert_close(h, ref_h.half(), atol=2 * float(ref_h.abs().max()) * 2 ** -11, rtol=1e-2, what="SwiGLU stage")
+    hq, hs = g.quantize_tensor(h)
+    hq_ref, hs_ref = oracle.quantize_tensor(h.cpu().float())
+    assert_bitexact(hq, hq_ref); assert_bitexact(hs, hs_ref)
+    y = g.gemm_i8(hq, Wd.cuda(), hs, sd.cuda())
+    assert f16_equal_up_to_signed_zero(y, oracle.gemm_dequant_exact(hq_ref, Wd, hs_ref, sd)) == 0
+
+
+def test_config2_full_size_sampled_rows():
+    """BASELINE config 2 at full size (65536 tokens = 32 chunks x 2048 steps): rows are independent, so
+    parity is checked on row blocks (first / middle / last tile, a ragged slice) against the oracle."""
+    g = need_lib()
+    nhead, head_dim, rotary_dim, seqlen, K = 8, 64, 64, 2048, 512
+    M, N = 65536, 1536
+    gen = torch.Generator().manual_seed(2001)
+    x = torch.randn(M, K, generator=gen).half()
+    B, sb = rand_i8(gen, N, K), rand_scales(gen, N)
+    sn, cs = oracle.rope_tables(seqlen, 32, head_dim)
+    xq, xs = g.quantize_tensor(x.cuda())
+    c = g.gemm_i8_rotary(xq, B.cuda(), xs, sb.cuda(), sn.cuda(), cs.cuda(), nhead, head_dim, rotary_dim, seqlen)
+    c = c.cpu()
+    for lo, hi in [(0, 256), (32768 - 64, 32768 + 64), (65536 - 256, 65536), (12345, 12345 + 77)]:
+        q_ref, s_ref = oracle.quantize_tensor(x[lo:hi].float())
+        assert_bitexact(xq[lo:hi], q_ref)
+        pad = lo % seqlen
+        Ap = torch.cat([torch.zeros(pad, K, dtype=torch.int8), q_ref])
+        sap = torch.cat([torch.ones(pad), s_ref])
+        exact = oracle.rotary_exact(Ap, B, sap, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)[pad:]
+        assert f16_equal_up_to_signed_zero(c[lo:hi], exact) == 0, f"rows {lo}:{hi}"
+
+
+def test_bad_arguments_are_rejected_before_launch():
+    g = need_lib()
+    A = torch.zeros(128, 512, dtype=torch.int8, device="cuda")
+    B = torch.zeros(256, 512, dtype=torch.int8, device="cuda")
+    s = torch.ones(256, device="cuda")
+    with pytest.raises(RuntimeError):
+        g.gemm_i8(A[:, :500], B[:, :500], s, s)              # K % 16 != 0
+    with pytest.raises(RuntimeError):
+        g.gemm_i8(A[:, 8:264], B[:, 8:264], s, s)            # misaligned base
+    sn = torch.zeros(16, 32, device="cuda")
+    with pytest.raises(RuntimeError):
+        g.gemm_i8_rotary(A, B, s, s, sn, sn, 8, 64, 64, 16)  # 2*nhead*head_dim > N
+    sn64 = torch.zeros(16, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        g.gemm_i8_rotary(A, B, s, s, sn64, sn64, 1, 128, 128, 16)  # unsupported head_dim
+    with pytest.raises(RuntimeError):
+        g.gemm_i8(A.cpu(), B.cpu(), s.cpu(), s.cpu())        # no CPU path
+    assert g.device_status()[0] == 0
