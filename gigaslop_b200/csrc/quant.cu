@@ -4,8 +4,7 @@
 // reduction, and written once with 8-byte stores.  One warp owns one row.
 //
 // The arithmetic order is part of the contract (results are bit-exact against the
-// CPU reference): INT8 uses qs = 127/amax (IEEE division), q = rne(x*qs), scale =
-// 1/qs; FP8 has the kernel formulation (x * (448/amax)) and the torch formulation
+// CPU reference): INT8 uses qs = (1/amax)*127, q = rne(x*qs), scale = 1/qs; FP8 has the kernel formulation (x * (448/amax)) and the torch formulation
 // (x / (amax/448)).
 #include <cuda_fp8.h>
 
@@ -112,7 +111,9 @@ ptq_kernel(const Tin* __restrict__ x, long long ldx, uint8_t* __restrict__ q, lo
   float s;   // dequantisation scale written out
   if constexpr (FMT == 0) {
     amax = fmaxf(amax, 1e-8f);
-    f = __fdiv_rn(127.0f, amax);
+    // the reference computes `127 / amax` with a Python scalar numerator, which PyTorch evaluates as
+    // reciprocal(amax) * 127 (two roundings) -- reproduced here so every int8 value matches
+    f = __fmul_rn(__frcp_rn(amax), 127.0f);
     s = __frcp_rn(f);
   } else {
     amax = fmaxf(amax, 1e-12f);

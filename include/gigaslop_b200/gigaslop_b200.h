@@ -51,7 +51,7 @@ int32_t gsb200_set_spin_budget(uint32_t clocks); /* bound (SM clocks) for device
  * sets bit 2 of the status word.  Exercises the give-up path without hanging the device. */
 int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream);
 
-/* Per-token symmetric absmax INT8 quantiser: q = rne(x * (127/amax)), scale = 1/(127/amax).
+/* Per-token symmetric absmax INT8 quantiser: qs = (1/amax)*127 (as PyTorch evaluates 127/amax), q = rne(x*qs), scale = 1/qs.
  * Stands in for quantize_tensor (cute/bench_quant_i8.py:15-31); the reference has no
  * GPU kernel for it.  Bit-exact with that function on fp32(x). */
 int32_t gsb200_ptq_int8(const void* x, int32_t x_dtype, int64_t ldx, int8_t* q, int64_t ldq, float* scale,

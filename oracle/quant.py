@@ -18,7 +18,10 @@ def quantize_tensor(t, dim=-1):
     ``cute/test_gemm_i8_rotary_vs_openfish.py:35-40``,
     ``cute/bench_gemm_i8_rotary.py:15-20``, ``cute/bench_dual_gemm_i8_silu.py:15-20``):
     amax clamped to 1e-8, ``qs = 127/amax``, ``q = round_half_even(t*qs)``
-    clamped to +-127, dequant scale ``= 1/qs``.  ``t`` must be fp32.
+    clamped to +-127, dequant scale ``= 1/qs``.  ``t`` must be fp32.  Note that
+    PyTorch evaluates ``127 / tensor`` (Python scalar numerator) as
+    ``tensor.reciprocal() * 127`` -- two roundings, not one IEEE division -- and the
+    device kernel reproduces exactly that.
     """
     qm = 127
     fr = t.abs().amax(dim=dim).clamp_min(1e-8)
@@ -62,7 +65,7 @@ def fp8_quantize_per_token_kernel(x_f32):
     with round-to-nearest-even and saturation to +-448.
     """
     amax = x_f32.abs().amax(dim=-1, keepdim=True).clamp(min=1e-12)
-    inv = FP8_MAX / amax
+    inv = torch.full_like(amax, FP8_MAX) / amax          # a true IEEE division, as the device code does
     scale = amax / FP8_MAX
     q = (x_f32 * inv).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
     return q, scale.squeeze(-1)
