@@ -11,6 +11,7 @@ ERRORS = {-1: "bad argument", -2: "unsupported shape", -3: "device is not sm_100
 
 F16, F32 = 0, 1
 FLAG_DIRECT_STORE = 1
+FLAG_STREAMING = 2
 
 _i32, _i64, _p = C.c_int32, C.c_int64, C.c_void_p
 

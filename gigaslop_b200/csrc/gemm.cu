@@ -25,9 +25,10 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major tensor [rows, cols] of `esz`-byte elements with a box of box_cols x box_rows and
-// the 128-byte swizzle (box_cols * esz must be 128).
+// the given swizzle (box_cols * esz must equal the swizzle span).
 static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows,
-                        uint64_t cols, uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows) {
+                        uint64_t cols, uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows,
+                        CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -35,7 +36,7 @@ static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const v
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     fprintf(stderr, "gigaslop_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r);
     return false;
@@ -50,7 +51,10 @@ static int g_dev_sms[kMaxDevices];
 
 template <int KIND, int EPI>
 static cudaError_t set_attr() {
-  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               GEMM_SMEM_BYTES);
 }
 
@@ -94,8 +98,9 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <int KIND, int EPI>
 static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1,
-                               const CUtensorMap& tc, const GemmParams& p, int grid, cudaStream_t st) {
-  gemm_tcgen05_kernel<KIND, EPI><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+                               const CUtensorMap& tc, const GemmParams& p, int grid, bool wres, cudaStream_t st) {
+  if (wres) gemm_tcgen05_kernel<KIND, EPI, true><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+  else gemm_tcgen05_kernel<KIND, EPI, false><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
   return cudaGetLastError();
 }
 
@@ -142,6 +147,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.rot_cols = rot_cols;
   p.row_offset = (int)(a.row_offset % p.seqlen);
   p.direct_store = (a.flags & GSB200_FLAG_DIRECT_STORE) ? 1 : 0;
+  p.ablate = (a.flags >> 8) & 3;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
 
@@ -152,26 +158,46 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   ok = ok && make_map_2d(&tb1, u8, 1, dual ? a.B1 : a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
   if (a.epi != EPI_I32)
     ok = ok && make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.C, (uint64_t)a.M, (uint64_t)a.N,
-                           (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS);
+                           (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
   else
     tc = ta;
   if (!ok) return GSB200_ERR_BAD_ARG;
 
-  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  // weight-stationary schedule whenever the W slice (256 rows x K) fits its 128 KiB of shared memory
+  // (the rotary epilogue instead streams with a row-block-major walk, so that a token's sin/cos row and
+  // scale are fetched once per row block rather than once per tile)
+  const bool wres = p.k_blocks <= WRES_MAX_KBLOCKS && a.epi != EPI_ROTARY && !(a.flags & GSB200_FLAG_STREAMING);
+  int grid;
+  p.m_major = 0;
+  if (wres) {
+    int groups = sm_count() / p.n_blocks;
+    if (groups < 1) groups = 1;
+    if (groups > p.m_blocks) groups = p.m_blocks;
+    p.n_groups = groups;
+    grid = groups * p.n_blocks;
+  } else {
+    p.n_groups = 0;
+    if (a.epi == EPI_ROTARY && !(a.flags & GSB200_FLAG_STREAMING)) {
+      p.m_major = 1;
+      grid = p.m_blocks < sm_count() ? p.m_blocks : sm_count();
+    } else {
+      grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    }
+  }
   cudaError_t e = cudaErrorInvalidValue;
   if (a.kind == KIND_I8) {
     switch (a.epi) {
-      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, st); break;
-      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, st); break;
-      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, wres, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else if (a.kind == KIND_F8) {
     switch (a.epi) {
-      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, st); break;
-      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, wres, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else {

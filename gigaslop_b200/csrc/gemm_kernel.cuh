@@ -7,17 +7,27 @@
 //   EPI_ROTARY   dequant, then rotate-half on the Q|K columns  (QKV projection)
 //   EPI_SILU     f16( silu(gate) * up ), gate|up in one UMMA   (SwiGLU dual GEMM)
 //
-// One CTA per SM; tiles of 128 rows x 256 accumulator columns x 128 K-bytes are
-// walked n-fastest so CTAs that run together share A row-blocks in L2 while the
-// weights (<= 2 MiB) stay L2 resident: A is read from HBM once, C written once.
+// Two schedules share the epilogue:
 //
-//   warp 0      TMA producer   global -> 128B-swizzled smem ring (no multicast)
+//   WRES = true  (K <= 512, the QKV / SwiGLU / LSTM-input shapes): weight-stationary.
+//       A CTA keeps its 256-row slice of W (all of K, <= 128 KiB) in shared memory for
+//       the whole kernel and streams 128-row blocks of A through a 4-stage ring, so the
+//       L2 -> SM traffic per 128x256 output tile is the 64 KiB of A only.  CTAs are
+//       arranged as (row-block group) x (W slice); the CTAs of one group walk the same
+//       row blocks, so A comes from HBM once and from L2 for the other slices.
+//   WRES = false (any K, e.g. the K = 2048 down-projection): both operands stream
+//       through a 4-stage ring, tiles walked n-fastest.
+//
+//   warp 0      TMA producer   global -> 128B-swizzled smem (no multicast)
 //   warp 1      TMEM owner + single-thread tcgen05.mma issue
 //   warps 2..9  epilogue: tcgen05.ld (thread = accumulator row) -> math ->
-//               swizzled smem staging -> TMA store (per-warp 32 x 64 fp16 boxes)
+//               swizzled smem staging -> TMA store (per-warp 32 x 32 fp16 boxes)
 //
 // Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue
-// of tile i overlaps the MMAs of tile i+1.
+// of tile i overlaps the MMAs of tile i+1.  The epilogue reads nothing from global
+// memory inside its column loop: per-channel scales sit in shared memory, the
+// per-token scale and the sin/cos row of the thread's token are fetched into
+// registers once per tile before the accumulator wait.
 #pragma once
 #include "ptx.cuh"
 
@@ -30,25 +40,43 @@ constexpr int BM = 128;            // rows per tile (UMMA M)
 constexpr int BN = 256;            // accumulator columns per tile (UMMA N)
 constexpr int BK = 128;            // K bytes per smem stage (= one 128B swizzle row)
 constexpr int UMMA_K = 32;         // K bytes per tcgen05.mma for 8-bit kinds
-constexpr int STAGES = 3;
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_WARPS = 8;
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int WRES_MAX_KBLOCKS = 4;                     // W slice kept resident: up to K = 512
+constexpr int NSTAGE = 3;                               // ring depth of either schedule
 constexpr int OUT_BOX_ROWS = 32;
-constexpr int OUT_BOX_COLS = 64;                        // fp16 -> 128 B rows
-constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 4 KiB
-constexpr int OUT_BUFS = 2;
-constexpr int GEMM_SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES + 256;
-static_assert(GEMM_SMEM_BYTES <= 227 * 1024, "shared memory budget");
+constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
+constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
+constexpr int SCALE_SET_BYTES = 512;                    // 128 fp32 per-channel scales: the columns of one warp group
+
+// Shared-memory map (offsets from a 1 KiB-aligned base).
+//   WRES:      [W slice 4 x 32 KiB][A ring 3 x 16 KiB][staging 8 warps x 3 x 2 KiB][scales][barriers]
+//   streaming: [ring 3 x (A 16 KiB | B 32 KiB)]       [staging 8 warps x 4 x 2 KiB][scales][barriers]
+template <bool WRES>
+struct SmemMap {
+  static constexpr int RING_BYTES =
+      WRES ? WRES_MAX_KBLOCKS * B_STAGE_BYTES + NSTAGE * A_STAGE_BYTES : NSTAGE * (A_STAGE_BYTES + B_STAGE_BYTES);
+  static constexpr int OUT_BUFS = WRES ? 3 : 4;
+  static constexpr int OUT_OFF = RING_BYTES;
+  static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
+  static constexpr int BAR_OFF = SCALE_OFF + 2 /*groups*/ * 2 /*tile parity*/ * SCALE_SET_BYTES;
+  static constexpr int USED = BAR_OFF + 256;
+};
+constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
+static_assert(SmemMap<true>::USED <= GEMM_SMEM_BYTES && SmemMap<false>::USED <= GEMM_SMEM_BYTES, "shared memory budget");
 static_assert(GEMM_SMEM_BYTES > 116 * 1024, "one CTA per SM is what makes the 512-column TMEM allocation safe");
+
+constexpr unsigned int ST_BAD_SMEM_ALIGN = 1u << 8;
 
 struct GemmParams {
   int M, N, K;                 // N = output columns (dual GEMM: columns of each of gate / up)
   int m_blocks, n_blocks, k_blocks;
+  int n_groups;                // WRES: number of row-block groups (grid = n_groups * n_blocks)
+  int m_major;                 // streaming: a CTA walks all column blocks of a row block before the next row block
   void* C;                     // output base (direct-store path and int32 output)
   long long ldc;               // output row stride in elements
   const float* scale_a;        // [M]
@@ -60,6 +88,7 @@ struct GemmParams {
   int rot_cols;                // 2 * nhead * head_dim: columns below this are rotated (head_dim = 64, rotary_dim = 64)
   int row_offset;              // global row index of this shard's row 0
   int direct_store;            // 1: plain st.global from registers instead of smem + TMA store
+  int ablate;                  // timing ablations (results are then wrong): 1 = skip the output stores, 2 = skip the epilogue body
 };
 
 template <int KIND>
@@ -68,53 +97,95 @@ __device__ __forceinline__ float acc_to_float(uint32_t v) {
   else return __uint_as_float(v);
 }
 
-// Combine the per-token and per-channel scale with the accumulator exactly as the
-// reference kernels do: INT8 multiplies the two scales first and applies the product
-// (cute/ampere_gemm_i8_quant_rmem.py:603,727); FP8 applies them left to right
-// (fly/rdna_fp8_preshuffle_gemm.py:392-396).
+// Dequantise two adjacent accumulator columns.  The per-token and per-channel scales are combined with
+// the accumulator exactly as the reference kernels do: INT8 multiplies the two scales first and applies
+// the product (cute/ampere_gemm_i8_quant_rmem.py:603,727); FP8 applies them left to right
+// (fly/rdna_fp8_preshuffle_gemm.py:392-396).  sa2 = (sA, sA), sb2 = (sB[n], sB[n+1]).
 template <int KIND>
-__device__ __forceinline__ float dequant(uint32_t acc, float sa, float sb) {
-  if constexpr (KIND == KIND_I8) return __fmul_rn(acc_to_float<KIND>(acc), __fmul_rn(sa, sb));
-  else return __fmul_rn(__fmul_rn(acc_to_float<KIND>(acc), sa), sb);
+__device__ __forceinline__ uint64_t dequant2(uint32_t a0, uint32_t a1, uint64_t sa2, uint64_t sb2) {
+  const uint64_t acc = pk2(acc_to_float<KIND>(a0), acc_to_float<KIND>(a1));
+  if constexpr (KIND == KIND_I8) return fmul2(acc, fmul2(sa2, sb2));
+  else return fmul2(fmul2(acc, sa2), sb2);
 }
 
-__device__ __forceinline__ float4 ld_scale4(const float* s, int n, int N) {
-  if (n + 4 <= N) return __ldg(reinterpret_cast<const float4*>(s + n));
-  return make_float4(0.f, 0.f, 0.f, 0.f);
+// 8 consecutive columns -> 8 fp16 (one 16-byte piece).  s01/s23 hold the 8 per-channel scales as pairs.
+template <int KIND>
+__device__ __forceinline__ uint4 dequant_piece(const uint32_t* v, uint64_t sa2, ulonglong2 s_lo, ulonglong2 s_hi) {
+  uint4 o;
+  o.x = pack_half2_from(dequant2<KIND>(v[0], v[1], sa2, s_lo.x));
+  o.y = pack_half2_from(dequant2<KIND>(v[2], v[3], sa2, s_lo.y));
+  o.z = pack_half2_from(dequant2<KIND>(v[4], v[5], sa2, s_hi.x));
+  o.w = pack_half2_from(dequant2<KIND>(v[6], v[7], sa2, s_hi.y));
+  return o;
 }
 
-// Write 8 consecutive fp16 (one 16-byte piece) of this thread's row into the
-// staging buffer in the 128-byte swizzle a SWIZZLE_128B TMA store expects:
-// piece p of row r lives at r*128 + ((p ^ (r & 7)) * 16).
-__device__ __forceinline__ void stage_piece(uint8_t* buf, int row, int piece, uint4 v) {
-  *reinterpret_cast<uint4*>(buf + row * 128 + ((piece ^ (row & 7)) << 4)) = v;
+// Staging boxes are 32 rows x 32 fp16 in the 64-byte swizzle a SWIZZLE_64B TMA store expects: the 16-byte
+// piece p (0..3) of row r lives at r*64 + ((p ^ ((r >> 1) & 3)) * 16), which is also conflict-free for
+// 16-byte shared stores by a warp whose lane index is the row.
+struct true_tag { static constexpr bool value = true; };
+struct false_tag { static constexpr bool value = false; };
+
+// Tile -> (row block, column block) for this CTA's `it`-th tile.  Returns false past the end.
+//   WRES:               fixed column block, row blocks group, group + n_groups, ...
+//   streaming, m_major: row blocks cta, cta + grid, ...; all column blocks of one before the next
+//                       (per-row epilogue state -- token scale, sin/cos row -- is then fetched once per row block)
+//   streaming:          tiles cta, cta + grid, ... with the column block fastest
+template <bool WRES>
+__device__ __forceinline__ bool tile_coords(const GemmParams& p, int it, int& m_blk, int& n_blk) {
+  if constexpr (WRES) {
+    n_blk = blockIdx.x % p.n_blocks;
+    m_blk = blockIdx.x / p.n_blocks + it * p.n_groups;
+    return m_blk < p.m_blocks;
+  } else {
+    if (p.m_major) {
+      n_blk = it % p.n_blocks;
+      m_blk = blockIdx.x + (it / p.n_blocks) * gridDim.x;
+      return m_blk < p.m_blocks;
+    }
+    const long long t = (long long)blockIdx.x + (long long)it * gridDim.x;
+    if (t >= (long long)p.m_blocks * p.n_blocks) return false;
+    m_blk = (int)(t / p.n_blocks);
+    n_blk = (int)(t % p.n_blocks);
+    return true;
+  }
 }
 
-template <int KIND, int EPI>
+template <int KIND, int EPI, bool WRES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_c,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_base = smem;
-  uint8_t* out_base = smem + STAGES * STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(out_base + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES);
-  uint64_t* full_bar = bars;                       // [STAGES]
-  uint64_t* empty_bar = bars + STAGES;             // [STAGES]
-  uint64_t* acc_full = bars + 2 * STAGES;          // [ACC_STAGES]
+  using Map = SmemMap<WRES>;
+  constexpr int OUT_BUFS = Map::OUT_BUFS;
+  if (smem + Map::USED > smem_raw + GEMM_SMEM_BYTES) {     // cannot happen with a 1 KiB-aligned window; never run off the end
+    if (threadIdx.x == 0) atomicOr(&g_status[0], ST_BAD_SMEM_ALIGN);
+    return;
+  }
+  uint8_t* out_base = smem + Map::OUT_OFF;
+  float* scale_base = reinterpret_cast<float*>(smem + Map::SCALE_OFF);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Map::BAR_OFF);
+  uint64_t* full_bar = bars;                       // [NSTAGE]
+  uint64_t* empty_bar = bars + NSTAGE;             // [NSTAGE]
+  uint64_t* acc_full = bars + 2 * NSTAGE;          // [ACC_STAGES]
   uint64_t* acc_empty = acc_full + ACC_STAGES;     // [ACC_STAGES]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_STAGES);
+  uint64_t* w_full = acc_empty + ACC_STAGES;       // WRES: the resident W slice has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  // ring layout.  WRES: [W slice: k_blocks x 32 KiB][A stages: 3 x 16 KiB]; streaming: 3 x [A 16 KiB | B 32 KiB]
+  uint8_t* w_base = smem;
+  uint8_t* a_ring = smem + WRES_MAX_KBLOCKS * B_STAGE_BYTES;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.m_blocks * p.n_blocks;
   constexpr int OUT_COLS_PER_TILE = (EPI == EPI_SILU) ? BN / 2 : BN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
+    mbar_init(w_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1);
@@ -130,19 +201,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int s = 0; uint32_t ph = 0; bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / p.n_blocks) * BM;
-        const int n0 = (t % p.n_blocks) * OUT_COLS_PER_TILE;
+      if constexpr (WRES) {
+        const int n0 = (blockIdx.x % p.n_blocks) * OUT_COLS_PER_TILE;
+        const int n1 = (EPI == EPI_SILU) ? n0 : n0 + BN / 2;
+        mbar_arrive_expect_tx(w_full, p.k_blocks * B_STAGE_BYTES);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          uint8_t* sb = w_base + kb * B_STAGE_BYTES;
+          tma_load_2d(sb, &tm_b0, w_full, kb * BK, n0);
+          tma_load_2d(sb + (BN / 2) * BK, &tm_b1, w_full, kb * BK, n1);
+        }
+      }
+      int m_blk, n_blk;
+      for (int it = 0; ok && tile_coords<WRES>(p, it, m_blk, n_blk); ++it) {
+        const int m0 = m_blk * BM;
+        const int n0 = n_blk * OUT_COLS_PER_TILE;
         const int n1 = (EPI == EPI_SILU) ? n0 : n0 + BN / 2;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | s)) { ok = false; break; }
-          uint8_t* sa = stage_base + s * STAGE_BYTES;
-          uint8_t* sb = sa + A_STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(sa, &tm_a, &full_bar[s], kb * BK, m0);
-          tma_load_2d(sb, &tm_b0, &full_bar[s], kb * BK, n0);
-          tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if constexpr (WRES) {
+            mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES);
+            tma_load_2d(a_ring + s * A_STAGE_BYTES, &tm_a, &full_bar[s], kb * BK, m0);
+          } else {
+            uint8_t* sa = smem + s * (A_STAGE_BYTES + B_STAGE_BYTES);
+            uint8_t* sb = sa + A_STAGE_BYTES;
+            mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
+            tma_load_2d(sa, &tm_a, &full_bar[s], kb * BK, m0);
+            tma_load_2d(sb, &tm_b0, &full_bar[s], kb * BK, n0);
+            tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
+          }
+          if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
       }
       if (!ok) {                       // give copies already in flight time to land before the CTA exits
@@ -154,8 +241,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, BM, BN) : umma_idesc(1, 0, 0, BM, BN);
-      int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      int s = 0; uint32_t ph = 0; bool ok = true;
+      if constexpr (WRES) {
+        ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200);
+        tc_fence_after();
+      }
+      int m_blk, n_blk;
+      for (int it = 0; ok && tile_coords<WRES>(p, it, m_blk, n_blk); ++it) {
         const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as)) { ok = false; break; }
         tc_fence_after();
@@ -163,9 +255,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(stage_base + s * STAGE_BYTES);
+          uint32_t a_addr, b_addr;
+          if constexpr (WRES) {
+            a_addr = smem_u32(a_ring + s * A_STAGE_BYTES);
+            b_addr = smem_u32(w_base + kb * B_STAGE_BYTES);
+          } else {
+            a_addr = smem_u32(smem + s * (A_STAGE_BYTES + B_STAGE_BYTES));
+            b_addr = a_addr + A_STAGE_BYTES;
+          }
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
-          const uint64_t b_desc = umma_smem_desc_sw128(a_addr + A_STAGE_BYTES);
+          const uint64_t b_desc = umma_smem_desc_sw128(b_addr);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t koff = (uint64_t)((k * UMMA_K) >> 4);
@@ -173,7 +272,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             else umma_f8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
           }
           umma_commit(&empty_bar[s]);          // smem stage reusable once these MMAs retire
-          if (++s == STAGES) { s = 0; ph ^= 1; }
+          if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&acc_full[as]);     // accumulator complete
       }
@@ -184,25 +283,77 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int q = warp & 3;                // TMEM lane quarter this warp may read
     const int grp = e >> 2;                // column half of the tile handled by this warp
     uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;
-    int it = 0; int obuf = 0; bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    constexpr int WARP_OUT_COLS = OUT_COLS_PER_TILE / 2;          // output columns per warp per tile (128 / 64)
+    const int wcol0 = grp * WARP_OUT_COLS;                        // first output column (inside the tile) of this warp
+    int obuf = 0; bool ok = true;
+    int m_blk, n_blk;
+    // per-row state, fetched once per row block and kept in registers across its column blocks
+    float sa = 0.f;
+    uint64_t sn2[16], cs2[16];             // sin / cos row of this thread's token as fp32 pairs
+    int cur_m_blk = -1;
+    uint32_t stg_off[4];                   // byte offsets of the 4 pieces of this thread's row in a swizzled staging box
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
+    for (int it = 0; ok && tile_coords<WRES>(p, it, m_blk, n_blk); ++it) {
       const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
-      const int m0 = (t / p.n_blocks) * BM;
-      const int n0 = (t % p.n_blocks) * OUT_COLS_PER_TILE;
+      const int m0 = m_blk * BM;
+      const int n0 = n_blk * OUT_COLS_PER_TILE;
+      const int row_base = m0 + q * 32;
+      const int row = row_base + lane;
+      const bool row_ok = row < p.M;
+
+      // ---- per-tile prologue: everything that comes from global memory, before the accumulator wait ----
+      float4 sbv = make_float4(0.f, 0.f, 0.f, 0.f);
+      // The four warps of a column group share one scale set per tile parity (they all write the same
+      // values).  A set is rewritten only after the accumulator wait of a tile two steps later, which
+      // cannot complete before every warp has released -- hence finished reading -- the older tile.
+      float* sc = scale_base + (grp * 2 + (WRES ? 0 : (it & 1))) * (SCALE_SET_BYTES / 4);
+      if constexpr (EPI != EPI_I32) {
+        if (m_blk != cur_m_blk) {
+          cur_m_blk = m_blk;
+          sa = row_ok ? __ldg(p.scale_a + row) : 0.f;
+          if constexpr (EPI == EPI_ROTARY) {
+            const int pos = row_ok ? (int)(((long long)row + p.row_offset) % p.seqlen) : 0;
+            const ulonglong2* s4 = reinterpret_cast<const ulonglong2*>(p.sin_tab + (long long)pos * 32);
+            const ulonglong2* c4 = reinterpret_cast<const ulonglong2*>(p.cos_tab + (long long)pos * 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const ulonglong2 a = __ldg(s4 + j), b = __ldg(c4 + j);
+              sn2[2 * j] = a.x; sn2[2 * j + 1] = a.y;
+              cs2[2 * j] = b.x; cs2[2 * j + 1] = b.y;
+            }
+          }
+        }
+        if (!WRES || it == 0) {
+          // per-channel scales of this warp group's columns (dual: 64 gate | 64 up): fetched now, parked in
+          // shared memory after the accumulator wait (see below)
+          if constexpr (EPI == EPI_SILU) {
+            const int n = n0 + wcol0 + (lane & 15) * 4;
+            const float* src = (lane < 16) ? p.scale_b0 : p.scale_b1;
+            if (n + 4 <= p.N) sbv = __ldg(reinterpret_cast<const float4*>(src + n));
+          } else {
+            const int n = n0 + wcol0 + lane * 4;
+            if (n + 4 <= p.N) sbv = __ldg(reinterpret_cast<const float4*>(p.scale_b0 + n));
+          }
+        }
+      }
+
       // warp-uniform outcome: the tcgen05.ld below needs the whole warp
       if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as))) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row_base = m0 + q * 32;
-      const int row = row_base + lane;
       const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
-      if (row_base < p.M) {
-        const bool row_ok = row < p.M;
-        float sa = 0.f;
-        if constexpr (EPI != EPI_I32) sa = row_ok ? __ldg(p.scale_a + row) : 0.f;
+      if constexpr (EPI != EPI_I32) {
+        if (!WRES || it == 0) {
+          if constexpr (EPI == EPI_SILU) *reinterpret_cast<float4*>(sc + (lane < 16 ? 0 : 64) + (lane & 15) * 4) = sbv;
+          else *reinterpret_cast<float4*>(sc + lane * 4) = sbv;
+          __syncwarp();
+        }
+      }
 
+      if (row_base < p.M && !(p.ablate & 2)) {
         if constexpr (EPI == EPI_I32) {
           // raw accumulators, direct 16-byte stores
           constexpr int COLS = BN / 2;
@@ -221,143 +372,170 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
           }
         } else {
-          constexpr int CHUNKS = OUT_COLS_PER_TILE / 2 / OUT_BOX_COLS;     // 64-column chunks per warp
-          int pos = 0;
-          if constexpr (EPI == EPI_ROTARY) pos = row_ok ? (int)(((long long)row + p.row_offset) % p.seqlen) : 0;
-#pragma unroll 1
-          for (int ch = 0; ch < CHUNKS; ++ch) {
-            const int ocol = grp * (OUT_COLS_PER_TILE / 2) + ch * OUT_BOX_COLS;   // column inside the tile's output
-            const int n = n0 + ocol;                                            // global output column
-            if (n >= p.N) break;
-            uint8_t* buf = out_buf + obuf * OUT_BUF_BYTES;
-            if (!p.direct_store) {
-              if (lane == 0) tma_store_wait_read<OUT_BUFS - 1>();   // the store that last used this buffer has read it
-              __syncwarp();
-            }
-            __half* drow = reinterpret_cast<__half*>(p.C) + (long long)row * p.ldc + n;
+          const uint64_t sa2 = pk2(sa, sa);
+          // The body exists twice: the product path (swizzled staging + TMA store) and a diagnostic path
+          // that stores straight from registers; the choice is made once per tile.
+          auto run_tile = [&](auto direct_tag) {
+            constexpr bool DIRECT = decltype(direct_tag)::value;
+            __half* drow0 = reinterpret_cast<__half*>(p.C) + (long long)row * p.ldc;
+            // one 32-column box = 4 pieces of 8 fp16
+            auto box_begin = [&]() {
+              if constexpr (!DIRECT) {
+                if (lane == 0) tma_store_wait_read<OUT_BUFS - 1>();   // the store that last used this buffer has read it
+                __syncwarp();
+              }
+            };
+            auto put = [&](int n, int piece, uint4 o) {
+              if constexpr (DIRECT) {
+                if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = o;
+              } else {
+                *reinterpret_cast<uint4*>(out_buf + obuf * OUT_BUF_BYTES + stg_off[piece]) = o;
+              }
+            };
+            auto box_end = [&](int n) {
+              if constexpr (!DIRECT) {
+                fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
+                __syncwarp();
+                if (lane == 0 && !(p.ablate & 1)) { tma_store_2d(&tm_c, out_buf + obuf * OUT_BUF_BYTES, n, row_base); tma_store_commit(); }
+                obuf = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
+              }
+            };
 
             if constexpr (EPI == EPI_DEQUANT) {
+              // 32-column steps; the TMEM load of step i+1 is in flight while step i is converted and staged
+              constexpr int NSUB = WARP_OUT_COLS / 32;
+              uint32_t v[2][32];
+              tmem_ld_32x32b_x32(t_row + wcol0, v[0]);
 #pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(t_row + ocol + half * 32, v);
+              for (int ci = 0; ci < NSUB; ++ci) {
                 tmem_ld_wait();
+                if (ci + 1 < NSUB) tmem_ld_32x32b_x32(t_row + wcol0 + (ci + 1) * 32, v[(ci + 1) & 1]);
+                const int c = ci * 32;
+                const int n = n0 + wcol0 + c;
+                if (n < p.N) {
+                  box_begin();
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  const float4 s0 = ld_scale4(p.scale_b0, n + half * 32 + j, p.N);
-                  const float4 s1 = ld_scale4(p.scale_b0, n + half * 32 + j + 4, p.N);
-                  uint4 o;
-                  o.x = pack_half2(dequant<KIND>(v[j + 0], sa, s0.x), dequant<KIND>(v[j + 1], sa, s0.y));
-                  o.y = pack_half2(dequant<KIND>(v[j + 2], sa, s0.z), dequant<KIND>(v[j + 3], sa, s0.w));
-                  o.z = pack_half2(dequant<KIND>(v[j + 4], sa, s1.x), dequant<KIND>(v[j + 5], sa, s1.y));
-                  o.w = pack_half2(dequant<KIND>(v[j + 6], sa, s1.z), dequant<KIND>(v[j + 7], sa, s1.w));
-                  const int piece = half * 4 + (j >> 3);
-                  if (p.direct_store) {
-                    if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow + piece * 8) = o;
-                  } else {
-                    stage_piece(buf, lane, piece, o);
+                  for (int j = 0; j < 32; j += 8) {
+                    const ulonglong2 s_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
+                    const ulonglong2 s_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
+                    put(n, j >> 3, dequant_piece<KIND>(&v[ci & 1][j], sa2, s_lo, s_hi));
                   }
+                  box_end(n);
                 }
               }
             } else if constexpr (EPI == EPI_ROTARY) {
-              // one 64-wide head: x0 = columns 0..31, x1 = columns 32..63, both rows of this thread
-              uint32_t v0[32], v1[32];
-              tmem_ld_32x32b_x32(t_row + ocol, v0);
-              tmem_ld_32x32b_x32(t_row + ocol + 32, v1);
-              tmem_ld_wait();
-              const bool rot = n < p.rot_cols;
-              const float* sin_row = p.sin_tab + (long long)pos * 32;
-              const float* cos_row = p.cos_tab + (long long)pos * 32;
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float x0[8], x1[8];
-                {
-                  const float4 a0 = ld_scale4(p.scale_b0, n + j, p.N), a1 = ld_scale4(p.scale_b0, n + j + 4, p.N);
-                  const float4 b0 = ld_scale4(p.scale_b0, n + 32 + j, p.N), b1 = ld_scale4(p.scale_b0, n + 32 + j + 4, p.N);
-                  const float sb0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                  const float sb1[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    x0[i] = dequant<KIND>(v0[j + i], sa, sb0[i]);
-                    x1[i] = dequant<KIND>(v1[j + i], sa, sb1[i]);
-                  }
-                }
-                float o0[8], o1[8];
-                if (rot) {
-                  const float4 s_a = __ldg(reinterpret_cast<const float4*>(sin_row + j));
-                  const float4 s_b = __ldg(reinterpret_cast<const float4*>(sin_row + j + 4));
-                  const float4 c_a = __ldg(reinterpret_cast<const float4*>(cos_row + j));
-                  const float4 c_b = __ldg(reinterpret_cast<const float4*>(cos_row + j + 4));
-                  const float sn[8] = {s_a.x, s_a.y, s_a.z, s_a.w, s_b.x, s_b.y, s_b.z, s_b.w};
-                  const float cs[8] = {c_a.x, c_a.y, c_a.z, c_a.w, c_b.x, c_b.y, c_b.z, c_b.w};
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    // separately rounded products: the result is reproducible bit for bit on a CPU
-                    o0[i] = __fsub_rn(__fmul_rn(x0[i], cs[i]), __fmul_rn(x1[i], sn[i]));
-                    o1[i] = __fadd_rn(__fmul_rn(x0[i], sn[i]), __fmul_rn(x1[i], cs[i]));
-                  }
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) { o0[i] = x0[i]; o1[i] = x1[i]; }
-                }
-                uint4 lo, hi;
-                lo.x = pack_half2(o0[0], o0[1]); lo.y = pack_half2(o0[2], o0[3]);
-                lo.z = pack_half2(o0[4], o0[5]); lo.w = pack_half2(o0[6], o0[7]);
-                hi.x = pack_half2(o1[0], o1[1]); hi.y = pack_half2(o1[2], o1[3]);
-                hi.z = pack_half2(o1[4], o1[5]); hi.w = pack_half2(o1[6], o1[7]);
-                const int piece = j >> 3;
-                if (p.direct_store) {
-                  if (row_ok) {
-                    if (n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow + piece * 8) = lo;
-                    if (n + 32 + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow + 32 + piece * 8) = hi;
-                  }
-                } else {
-                  stage_piece(buf, lane, piece, lo);
-                  stage_piece(buf, lane, 4 + piece, hi);
-                }
-              }
-            } else {   // EPI_SILU: gate at accumulator column ocol, up at BN/2 + ocol
-#pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                uint32_t g[32], u[32];
-                tmem_ld_32x32b_x32(t_row + ocol + half * 32, g);
-                tmem_ld_32x32b_x32(t_row + BN / 2 + ocol + half * 32, u);
+              // one 64-wide head per step: x0 = columns 0..31, x1 = columns 32..63 of the head; the two
+              // 32-column halves go to two staging boxes that are open at the same time
+#pragma unroll 1
+              for (int c = 0; c < WARP_OUT_COLS; c += 64) {
+                const int n = n0 + wcol0 + c;
+                if (n >= p.N) break;
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(t_row + wcol0 + c, v0);
+                tmem_ld_32x32b_x32(t_row + wcol0 + c + 32, v1);
                 tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  const int nn = n + half * 32 + j;
-                  const float4 g0 = ld_scale4(p.scale_b0, nn, p.N), g1 = ld_scale4(p.scale_b0, nn + 4, p.N);
-                  const float4 u0 = ld_scale4(p.scale_b1, nn, p.N), u1 = ld_scale4(p.scale_b1, nn + 4, p.N);
-                  const float sg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                  const float su[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-                  float o[8];
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const float gate = dequant<KIND>(g[j + i], sa, sg[i]);
-                    const float up = dequant<KIND>(u[j + i], sa, su[i]);
-                    const float sig = __frcp_rn(1.0f + __expf(-gate));
-                    o[i] = gate * sig * up;
-                  }
-                  uint4 ov;
-                  ov.x = pack_half2(o[0], o[1]); ov.y = pack_half2(o[2], o[3]);
-                  ov.z = pack_half2(o[4], o[5]); ov.w = pack_half2(o[6], o[7]);
-                  const int piece = half * 4 + (j >> 3);
-                  if (p.direct_store) {
-                    if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow + piece * 8) = ov;
+                const int buf_lo = obuf, buf_hi = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
+                if constexpr (!DIRECT) {
+                  if (lane == 0) tma_store_wait_read<OUT_BUFS - 2>();   // both boxes free
+                  __syncwarp();
+                }
+                auto put2 = [&](int piece, uint4 lo, uint4 hi) {
+                  if constexpr (DIRECT) {
+                    if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = lo;
+                    if (row_ok && n + 32 + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + 32 + piece * 8) = hi;
                   } else {
-                    stage_piece(buf, lane, piece, ov);
+                    *reinterpret_cast<uint4*>(out_buf + buf_lo * OUT_BUF_BYTES + stg_off[piece]) = lo;
+                    *reinterpret_cast<uint4*>(out_buf + buf_hi * OUT_BUF_BYTES + stg_off[piece]) = hi;
                   }
+                };
+                if (n < p.rot_cols) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8) {
+                    const ulonglong2 a_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
+                    const ulonglong2 a_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
+                    const ulonglong2 b_lo = *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j);
+                    const ulonglong2 b_hi = *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j + 4);
+                    const uint64_t sb0[4] = {a_lo.x, a_lo.y, a_hi.x, a_hi.y};
+                    const uint64_t sb1[4] = {b_lo.x, b_lo.y, b_hi.x, b_hi.y};
+                    uint32_t o0[4], o1[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const uint64_t x0 = dequant2<KIND>(v0[j + 2 * i], v0[j + 2 * i + 1], sa2, sb0[i]);
+                      const uint64_t x1 = dequant2<KIND>(v1[j + 2 * i], v1[j + 2 * i + 1], sa2, sb1[i]);
+                      const uint64_t c2 = cs2[(j >> 1) + i], s2 = sn2[(j >> 1) + i];
+                      // Separately rounded products and sums: reproducible bit for bit on a CPU.  The final
+                      // add / subtract is scalar on purpose: a packed multiply feeding a packed add was seen
+                      // to be contracted into a fused multiply-add, which rounds once instead of twice.
+                      float p0, p1, q0, q1, r0, r1, t0, t1;
+                      upk2(fmul2(x0, c2), p0, p1); upk2(fmul2(x1, s2), q0, q1);
+                      upk2(fmul2(x0, s2), r0, r1); upk2(fmul2(x1, c2), t0, t1);
+                      o0[i] = pack_half2(__fsub_rn(p0, q0), __fsub_rn(p1, q1));
+                      o1[i] = pack_half2(__fadd_rn(r0, t0), __fadd_rn(r1, t1));
+                    }
+                    put2(j >> 3, make_uint4(o0[0], o0[1], o0[2], o0[3]), make_uint4(o1[0], o1[1], o1[2], o1[3]));
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8) {
+                    put2(j >> 3,
+                         dequant_piece<KIND>(&v0[j], sa2, *reinterpret_cast<const ulonglong2*>(sc + c + j),
+                                             *reinterpret_cast<const ulonglong2*>(sc + c + j + 4)),
+                         dequant_piece<KIND>(&v1[j], sa2, *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j),
+                                             *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j + 4)));
+                  }
+                }
+                if constexpr (!DIRECT) {
+                  fence_proxy_async_smem();
+                  __syncwarp();
+                  if (lane == 0 && !(p.ablate & 1)) {
+                    tma_store_2d(&tm_c, out_buf + buf_lo * OUT_BUF_BYTES, n, row_base); tma_store_commit();
+                    tma_store_2d(&tm_c, out_buf + buf_hi * OUT_BUF_BYTES, n + 32, row_base); tma_store_commit();
+                  }
+                  obuf = (buf_hi + 1 == OUT_BUFS) ? 0 : buf_hi + 1;
+                }
+              }
+            } else {   // EPI_SILU: gate at accumulator column c, up at BN/2 + c; next step's loads in flight
+              constexpr int NSUB = WARP_OUT_COLS / 32;
+              uint32_t g[2][32], u[2][32];
+              tmem_ld_32x32b_x32(t_row + wcol0, g[0]);
+              tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0, u[0]);
+#pragma unroll
+              for (int ci = 0; ci < NSUB; ++ci) {
+                tmem_ld_wait();
+                if (ci + 1 < NSUB) {
+                  tmem_ld_32x32b_x32(t_row + wcol0 + (ci + 1) * 32, g[(ci + 1) & 1]);
+                  tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0 + (ci + 1) * 32, u[(ci + 1) & 1]);
+                }
+                const int c = ci * 32;
+                const int n = n0 + wcol0 + c;
+                if (n < p.N) {
+                  box_begin();
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8) {
+                    const ulonglong2 g_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
+                    const ulonglong2 g_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
+                    const ulonglong2 u_lo = *reinterpret_cast<const ulonglong2*>(sc + 64 + c + j);
+                    const ulonglong2 u_hi = *reinterpret_cast<const ulonglong2*>(sc + 64 + c + j + 4);
+                    const uint64_t sg[4] = {g_lo.x, g_lo.y, g_hi.x, g_hi.y};
+                    const uint64_t su[4] = {u_lo.x, u_lo.y, u_hi.x, u_hi.y};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      float g0, g1;
+                      upk2(dequant2<KIND>(g[ci & 1][j + 2 * i], g[ci & 1][j + 2 * i + 1], sa2, sg[i]), g0, g1);
+                      const uint64_t up = dequant2<KIND>(u[ci & 1][j + 2 * i], u[ci & 1][j + 2 * i + 1], sa2, su[i]);
+                      // silu(gate) = gate / (1 + exp(-gate)); exp and the division use the fast hardware approximations
+                      const uint64_t sl = pk2(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
+                      o[i] = pack_half2_from(fmul2(sl, up));
+                    }
+                    put(n, j >> 3, make_uint4(o[0], o[1], o[2], o[3]));
+                  }
+                  box_end(n);
                 }
               }
             }
-
-            if (!p.direct_store) {
-              fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
-              __syncwarp();
-              if (lane == 0) { tma_store_2d(&tm_c, buf, n, row_base); tma_store_commit(); }
-              obuf ^= 1;
-            }
-          }
+          };
+          if (p.direct_store) run_tile(true_tag{}); else run_tile(false_tag{});
         }
       }
       // hand the accumulator stage back to the MMA warp

@@ -23,6 +23,9 @@ constexpr unsigned int ST_TIMEOUT_EPILOGUE = 1u << 2;
 constexpr unsigned int ST_TIMEOUT_LSTM     = 1u << 3;
 
 constexpr long long kDefaultSpinBudget = 2000000000ll;   // ~1 s of SM clocks
+// Upper bound (ns) a try_wait may keep the thread suspended before it returns to the polling loop; the
+// hardware wakes it as soon as the phase completes, so a waiting role costs almost no issue slots.
+constexpr unsigned int kTryWaitSuspendNs = 20000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -63,10 +66,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitSuspendNs)
       : "memory");
   return ok != 0;
 }
@@ -234,6 +237,28 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- packed fp32 pairs (sm_100 f32x2 pipe): each op is two IEEE round-to-nearest results ---------
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+  uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r;
+}
+__device__ __forceinline__ void upk2(uint64_t r, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r));
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ uint64_t fsub2(uint64_t a, uint64_t b) {
+  uint64_t d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ uint32_t pack_half2_from(uint64_t v) {
+  float lo, hi; upk2(v, lo, hi);
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
 
 // ---- misc -----------------------------------------------------------------------
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {

@@ -38,6 +38,9 @@ extern "C" {
 
 /* bit flags for the `flags` argument of the GEMM entry points */
 #define GSB200_FLAG_DIRECT_STORE 1   /* diagnostic: epilogue stores straight from registers (no smem + TMA store) */
+#define GSB200_FLAG_ABLATE_STORES 0x100   /* timing ablation, output is NOT written: skip the epilogue's stores */
+#define GSB200_FLAG_ABLATE_EPILOGUE 0x200 /* timing ablation, output is NOT written: skip the epilogue body */
+#define GSB200_FLAG_STREAMING 2      /* diagnostic: stream both operands even when the weight slice could stay resident */
 
 typedef struct CUstream_st* gsb200_stream_t; /* == cudaStream_t */
 

@@ -12,7 +12,8 @@ from util import T, assert_bitexact, assert_close, f16_equal_up_to_signed_zero, 
 
 pytestmark = pytest.mark.gpu
 
-DIRECT = 1
+DIRECT = 1        # epilogue stores straight from registers
+STREAM = 2        # stream both operands even where the weight slice could stay resident
 
 
 def test_gemm_i32_golden():
@@ -42,8 +43,9 @@ def test_gemm_i32_worst_case_magnitude():
     assert_bitexact(c, oracle.gemm_i32(A, B))
 
 
-@pytest.mark.parametrize("flags", [0, DIRECT])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (16384, 512, 512), (257, 520, 512), (64, 1536, 512), (2000, 512, 2048)])
+@pytest.mark.parametrize("flags", [0, DIRECT, STREAM])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (16384, 512, 512), (257, 520, 512), (64, 1536, 512), (2000, 512, 2048),
+                                   (5000, 1536, 384), (3000, 4096, 512)])
 def test_gemm_dequant(M, N, K, flags):
     g = need_lib()
     gen = torch.Generator().manual_seed(1000 + M + N + K)
@@ -87,7 +89,8 @@ def test_rotary_reference_scenario(flags):
 
 
 @pytest.mark.parametrize("M,seqlen,row_offset,flags", [(256, 1024, 0, 0), (256, 333, 0, 0), (4096, 2048, 0, 0),
-                                                       (1000, 2048, 1536, 0), (130, 16, 5, DIRECT)])
+                                                       (1000, 2048, 1536, 0), (130, 16, 5, DIRECT), (20000, 2048, 0, 0),
+                                                       (4096, 2048, 0, STREAM), (700, 77, 3, STREAM)])
 def test_rotary_shapes(M, seqlen, row_offset, flags):
     g = need_lib()
     nhead, head_dim, rotary_dim, K = 8, 64, 64, 512
@@ -131,15 +134,16 @@ def test_dual_silu_golden(flags):
     assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="SwiGLU vs reference golden")
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 2048, 512), (4096, 2048, 512), (65, 136, 512)])
-def test_dual_silu_shapes(M, N, K):
+@pytest.mark.parametrize("flags", [0, STREAM])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 2048, 512), (4096, 2048, 512), (65, 136, 512), (9000, 2048, 512)])
+def test_dual_silu_shapes(M, N, K, flags):
     g = need_lib()
     gen = torch.Generator().manual_seed(3000 + M + N)
     X = torch.randn(M, K, generator=gen)
     A, sa = oracle.quantize_tensor(X)
     Bg, Bu = rand_i8(gen, N, K), rand_i8(gen, N, K)
     sbg, sbu = rand_scales(gen, N), rand_scales(gen, N)
-    c = g.dual_gemm_i8_silu(A.cuda(), Bg.cuda(), Bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda())
+    c = g.dual_gemm_i8_silu(A.cuda(), Bg.cuda(), Bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda(), flags=flags)
     model = oracle.dual_gemm_silu_model(A, Bg, Bu, sa, sbg, sbu)
     assert_close(c, model, atol=2 * float(model.float().abs().max()) * 2 ** -11, rtol=2e-3, what="vs kernel model")
     ref = oracle.dual_gemm_silu_ref(A, Bg, Bu, sa, sbg, sbu)
