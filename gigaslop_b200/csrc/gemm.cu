@@ -51,10 +51,11 @@ static int g_dev_sms[kMaxDevices];
 
 template <int KIND, int EPI>
 static cudaError_t set_attr() {
-  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, true>,
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  constexpr int RES = (EPI == EPI_ROTARY) ? SCHED_ARES : SCHED_WRES;
+  return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               GEMM_SMEM_BYTES);
 }
 
@@ -98,9 +99,11 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 template <int KIND, int EPI>
 static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1,
-                               const CUtensorMap& tc, const GemmParams& p, int grid, bool wres, cudaStream_t st) {
-  if (wres) gemm_tcgen05_kernel<KIND, EPI, true><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
-  else gemm_tcgen05_kernel<KIND, EPI, false><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+                               const CUtensorMap& tc, const GemmParams& p, int grid, bool resident, cudaStream_t st) {
+  // resident-operand schedule: rotary keeps A (activation-stationary), the others keep W (weight-stationary)
+  constexpr int RES = (EPI == EPI_ROTARY) ? SCHED_ARES : SCHED_WRES;
+  if (resident) gemm_tcgen05_kernel<KIND, EPI, RES><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+  else gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
   return cudaGetLastError();
 }
 
@@ -147,7 +150,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.rot_cols = rot_cols;
   p.row_offset = (int)(a.row_offset % p.seqlen);
   p.direct_store = (a.flags & GSB200_FLAG_DIRECT_STORE) ? 1 : 0;
-  p.ablate = (a.flags >> 8) & 3;
+  p.ablate = (a.flags >> 8) & 7;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
 
@@ -163,41 +166,39 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     tc = ta;
   if (!ok) return GSB200_ERR_BAD_ARG;
 
-  // weight-stationary schedule whenever the W slice (256 rows x K) fits its 128 KiB of shared memory
-  // (the rotary epilogue instead streams with a row-block-major walk, so that a token's sin/cos row and
-  // scale are fetched once per row block rather than once per tile)
-  const bool wres = p.k_blocks <= WRES_MAX_KBLOCKS && a.epi != EPI_ROTARY && !(a.flags & GSB200_FLAG_STREAMING);
+  // One operand stays resident in shared memory whenever K <= 512 (its 4 K-pieces fit): the W slice for the
+  // dequant / SwiGLU epilogues, the A row block for the rotary epilogue (whose per-row sin/cos state is then
+  // fetched once per row block).  Larger K streams both operands.
+  const bool resident = p.k_blocks <= RES_MAX_KBLOCKS && !(a.flags & GSB200_FLAG_STREAMING);
   int grid;
   p.m_major = 0;
-  if (wres) {
+  p.n_groups = 0;
+  if (resident && a.epi != EPI_ROTARY) {
     int groups = sm_count() / p.n_blocks;
     if (groups < 1) groups = 1;
     if (groups > p.m_blocks) groups = p.m_blocks;
     p.n_groups = groups;
     grid = groups * p.n_blocks;
+  } else if (a.epi == EPI_ROTARY) {
+    p.m_major = 1;
+    grid = p.m_blocks < sm_count() ? p.m_blocks : sm_count();
   } else {
-    p.n_groups = 0;
-    if (a.epi == EPI_ROTARY && !(a.flags & GSB200_FLAG_STREAMING)) {
-      p.m_major = 1;
-      grid = p.m_blocks < sm_count() ? p.m_blocks : sm_count();
-    } else {
-      grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    }
+    grid = (int)(tiles < sm_count() ? tiles : sm_count());
   }
   cudaError_t e = cudaErrorInvalidValue;
   if (a.kind == KIND_I8) {
     switch (a.epi) {
-      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, wres, st); break;
-      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, wres, st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, wres, st); break;
-      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else if (a.kind == KIND_F8) {
     switch (a.epi) {
-      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, wres, st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, wres, st); break;
-      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, wres, st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else {

@@ -7,27 +7,26 @@
 //   EPI_ROTARY   dequant, then rotate-half on the Q|K columns  (QKV projection)
 //   EPI_SILU     f16( silu(gate) * up ), gate|up in one UMMA   (SwiGLU dual GEMM)
 //
-// Two schedules share the epilogue:
+// Three schedules share the epilogue (tiles are 128 rows x 256 accumulator columns):
 //
-//   WRES = true  (K <= 512, the QKV / SwiGLU / LSTM-input shapes): weight-stationary.
-//       A CTA keeps its 256-row slice of W (all of K, <= 128 KiB) in shared memory for
-//       the whole kernel and streams 128-row blocks of A through a 4-stage ring, so the
-//       L2 -> SM traffic per 128x256 output tile is the 64 KiB of A only.  CTAs are
-//       arranged as (row-block group) x (W slice); the CTAs of one group walk the same
-//       row blocks, so A comes from HBM once and from L2 for the other slices.
-//   WRES = false (any K, e.g. the K = 2048 down-projection): both operands stream
-//       through a 4-stage ring, tiles walked n-fastest.
+//   SCHED_WRES   (K <= 512; dequant / SwiGLU): weight-stationary.  A CTA keeps its 256-row slice of W
+//                (all of K, <= 128 KiB) in shared memory for the whole kernel and streams 128-row
+//                blocks of A through a ring: L2 -> SM traffic per tile is the 64 KiB of A only.  CTAs
+//                form (row-block group) x (W slice); the CTAs of a group walk the same row blocks, so
+//                A comes from HBM once and from L2 for the other slices.
+//   SCHED_ARES   (K <= 512; rotary): activation-stationary.  A CTA owns row blocks; the 64 KiB A block
+//                stays in shared memory while every column block of W streams past it.  The per-row
+//                epilogue state (token scale, the token's sin/cos row) is fetched once per row block.
+//   SCHED_STREAM (any K, e.g. the K = 2048 down-projection): both operands stream through a ring.
 //
 //   warp 0      TMA producer   global -> 128B-swizzled smem (no multicast)
 //   warp 1      TMEM owner + single-thread tcgen05.mma issue
 //   warps 2..9  epilogue: tcgen05.ld (thread = accumulator row) -> math ->
-//               swizzled smem staging -> TMA store (per-warp 32 x 32 fp16 boxes)
+//               swizzled smem staging -> TMA store (per-warp 32 x 32 fp16 boxes, issued in pairs)
 //
-// Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue
-// of tile i overlaps the MMAs of tile i+1.  The epilogue reads nothing from global
-// memory inside its column loop: per-channel scales sit in shared memory, the
-// per-token scale and the sin/cos row of the thread's token are fetched into
-// registers once per tile before the accumulator wait.
+// Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue of tile i overlaps
+// the MMAs of tile i+1.  The epilogue reads nothing from global memory inside its column loop:
+// per-channel scales sit in shared memory, the per-token scale is prefetched one tile ahead.
 #pragma once
 #include "ptx.cuh"
 
@@ -35,6 +34,7 @@ namespace gsb {
 
 enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3 };
 enum : int { KIND_I8 = 0, KIND_F8 = 1 };
+enum : int { SCHED_STREAM = 0, SCHED_WRES = 1, SCHED_ARES = 2 };
 
 constexpr int BM = 128;            // rows per tile (UMMA M)
 constexpr int BN = 256;            // accumulator columns per tile (UMMA N)
@@ -46,28 +46,33 @@ constexpr int EPI_WARPS = 8;
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
-constexpr int WRES_MAX_KBLOCKS = 4;                     // W slice kept resident: up to K = 512
-constexpr int NSTAGE = 3;                               // ring depth of either schedule
+constexpr int RES_MAX_KBLOCKS = 4;                      // resident operand (W slice or A block): up to K = 512
+constexpr int NSTAGE = 3;                               // ring depth of every schedule
 constexpr int OUT_BOX_ROWS = 32;
 constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
 constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
 constexpr int SCALE_SET_BYTES = 512;                    // 128 fp32 per-channel scales: the columns of one warp group
 
 // Shared-memory map (offsets from a 1 KiB-aligned base).
-//   WRES:      [W slice 4 x 32 KiB][A ring 3 x 16 KiB][staging 8 warps x 3 x 2 KiB][scales][barriers]
-//   streaming: [ring 3 x (A 16 KiB | B 32 KiB)]       [staging 8 warps x 4 x 2 KiB][scales][barriers]
-template <bool WRES>
+//   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales][barriers]
+//   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales][barriers]
+//   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 4 x 2 KiB][scales][barriers]
+template <int SCHED>
 struct SmemMap {
-  static constexpr int RING_BYTES =
-      WRES ? WRES_MAX_KBLOCKS * B_STAGE_BYTES + NSTAGE * A_STAGE_BYTES : NSTAGE * (A_STAGE_BYTES + B_STAGE_BYTES);
-  static constexpr int OUT_BUFS = WRES ? 3 : 4;
-  static constexpr int OUT_OFF = RING_BYTES;
+  static constexpr int RES_BYTES = SCHED == SCHED_WRES ? RES_MAX_KBLOCKS * B_STAGE_BYTES
+                                 : SCHED == SCHED_ARES ? RES_MAX_KBLOCKS * A_STAGE_BYTES : 0;
+  static constexpr int STAGE_BYTES = SCHED == SCHED_WRES ? A_STAGE_BYTES
+                                   : SCHED == SCHED_ARES ? B_STAGE_BYTES : A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int RING_OFF = RES_BYTES;
+  static constexpr int OUT_BUFS = SCHED == SCHED_WRES ? 3 : 4;   // 32x32 fp16 staging boxes per epilogue warp
+  static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
   static constexpr int BAR_OFF = SCALE_OFF + 2 /*groups*/ * 2 /*tile parity*/ * SCALE_SET_BYTES;
   static constexpr int USED = BAR_OFF + 256;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
-static_assert(SmemMap<true>::USED <= GEMM_SMEM_BYTES && SmemMap<false>::USED <= GEMM_SMEM_BYTES, "shared memory budget");
+static_assert(SmemMap<0>::USED <= GEMM_SMEM_BYTES && SmemMap<1>::USED <= GEMM_SMEM_BYTES &&
+              SmemMap<2>::USED <= GEMM_SMEM_BYTES, "shared memory budget");
 static_assert(GEMM_SMEM_BYTES > 116 * 1024, "one CTA per SM is what makes the 512-column TMEM allocation safe");
 
 constexpr unsigned int ST_BAD_SMEM_ALIGN = 1u << 8;
@@ -76,7 +81,7 @@ struct GemmParams {
   int M, N, K;                 // N = output columns (dual GEMM: columns of each of gate / up)
   int m_blocks, n_blocks, k_blocks;
   int n_groups;                // WRES: number of row-block groups (grid = n_groups * n_blocks)
-  int m_major;                 // streaming: a CTA walks all column blocks of a row block before the next row block
+  int m_major;                 // STREAM: a CTA walks all column blocks of a row block before the next (ARES always does)
   void* C;                     // output base (direct-store path and int32 output)
   long long ldc;               // output row stride in elements
   const float* scale_a;        // [M]
@@ -127,17 +132,16 @@ struct false_tag { static constexpr bool value = false; };
 
 // Tile -> (row block, column block) for this CTA's `it`-th tile.  Returns false past the end.
 //   WRES:               fixed column block, row blocks group, group + n_groups, ...
-//   streaming, m_major: row blocks cta, cta + grid, ...; all column blocks of one before the next
-//                       (per-row epilogue state -- token scale, sin/cos row -- is then fetched once per row block)
-//   streaming:          tiles cta, cta + grid, ... with the column block fastest
-template <bool WRES>
+//   ARES, STREAM m_major: row blocks cta, cta + grid, ...; all column blocks of one before the next
+//   STREAM:             tiles cta, cta + grid, ... with the column block fastest
+template <int SCHED>
 __device__ __forceinline__ bool tile_coords(const GemmParams& p, int it, int& m_blk, int& n_blk) {
-  if constexpr (WRES) {
+  if constexpr (SCHED == SCHED_WRES) {
     n_blk = blockIdx.x % p.n_blocks;
     m_blk = blockIdx.x / p.n_blocks + it * p.n_groups;
     return m_blk < p.m_blocks;
   } else {
-    if (p.m_major) {
+    if (SCHED == SCHED_ARES || p.m_major) {
       n_blk = it % p.n_blocks;
       m_blk = blockIdx.x + (it / p.n_blocks) * gridDim.x;
       return m_blk < p.m_blocks;
@@ -150,33 +154,34 @@ __device__ __forceinline__ bool tile_coords(const GemmParams& p, int it, int& m_
   }
 }
 
-template <int KIND, int EPI, bool WRES>
+template <int KIND, int EPI, int SCHED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_c,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  using Map = SmemMap<WRES>;
+  using Map = SmemMap<SCHED>;
+  constexpr bool WRES = SCHED == SCHED_WRES;
+  constexpr bool ARES = SCHED == SCHED_ARES;
   constexpr int OUT_BUFS = Map::OUT_BUFS;
   if (smem + Map::USED > smem_raw + GEMM_SMEM_BYTES) {     // cannot happen with a 1 KiB-aligned window; never run off the end
     if (threadIdx.x == 0) atomicOr(&g_status[0], ST_BAD_SMEM_ALIGN);
     return;
   }
+  uint8_t* res_base = smem;                                // WRES: W slice, ARES: A block (k_blocks pieces)
+  uint8_t* ring = smem + Map::RING_OFF;
   uint8_t* out_base = smem + Map::OUT_OFF;
   float* scale_base = reinterpret_cast<float*>(smem + Map::SCALE_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Map::BAR_OFF);
-  uint64_t* full_bar = bars;                       // [NSTAGE]
-  uint64_t* empty_bar = bars + NSTAGE;             // [NSTAGE]
-  uint64_t* acc_full = bars + 2 * NSTAGE;          // [ACC_STAGES]
-  uint64_t* acc_empty = acc_full + ACC_STAGES;     // [ACC_STAGES]
-  uint64_t* w_full = acc_empty + ACC_STAGES;       // WRES: the resident W slice has landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(w_full + 1);
+  uint64_t* full_bar = bars;                               // [NSTAGE]  ring stage filled
+  uint64_t* empty_bar = bars + NSTAGE;                     // [NSTAGE]  ring stage consumed
+  uint64_t* acc_full = bars + 2 * NSTAGE;                  // [ACC_STAGES]
+  uint64_t* acc_empty = acc_full + ACC_STAGES;             // [ACC_STAGES]
+  uint64_t* res_full = acc_empty + ACC_STAGES;             // [RES_MAX_KBLOCKS] resident piece landed (WRES uses [0] only)
+  uint64_t* res_empty = res_full + RES_MAX_KBLOCKS;        // [RES_MAX_KBLOCKS] ARES: A piece no longer needed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_empty + RES_MAX_KBLOCKS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  // ring layout.  WRES: [W slice: k_blocks x 32 KiB][A stages: 3 x 16 KiB]; streaming: 3 x [A 16 KiB | B 32 KiB]
-  uint8_t* w_base = smem;
-  uint8_t* a_ring = smem + WRES_MAX_KBLOCKS * B_STAGE_BYTES;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -185,7 +190,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
-    mbar_init(w_full, 1);
+    for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], 1); mbar_init(&res_empty[s], 1); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1);
@@ -204,28 +209,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if constexpr (WRES) {
         const int n0 = (blockIdx.x % p.n_blocks) * OUT_COLS_PER_TILE;
         const int n1 = (EPI == EPI_SILU) ? n0 : n0 + BN / 2;
-        mbar_arrive_expect_tx(w_full, p.k_blocks * B_STAGE_BYTES);
+        mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          uint8_t* sb = w_base + kb * B_STAGE_BYTES;
-          tma_load_2d(sb, &tm_b0, w_full, kb * BK, n0);
-          tma_load_2d(sb + (BN / 2) * BK, &tm_b1, w_full, kb * BK, n1);
+          uint8_t* sb = res_base + kb * B_STAGE_BYTES;
+          tma_load_2d(sb, &tm_b0, &res_full[0], kb * BK, n0);
+          tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &res_full[0], kb * BK, n1);
         }
       }
       int m_blk, n_blk;
-      for (int it = 0; ok && tile_coords<WRES>(p, it, m_blk, n_blk); ++it) {
+      uint32_t rph = 0;                       // ARES: phase of the resident-A barriers, flips per row block
+      for (int it = 0; ok && !(p.ablate & 4) && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
         const int m0 = m_blk * BM;
         const int n0 = n_blk * OUT_COLS_PER_TILE;
         const int n1 = (EPI == EPI_SILU) ? n0 : n0 + BN / 2;
+        if (ARES && n_blk == 0 && it != 0) rph ^= 1;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if constexpr (ARES) {
+            if (n_blk == 0) {                 // new row block: refill this K piece of A once its last reader retired
+              if (!mbar_wait(&res_empty[kb], rph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x300 | kb)) { ok = false; break; }
+              mbar_arrive_expect_tx(&res_full[kb], A_STAGE_BYTES);
+              tma_load_2d(res_base + kb * A_STAGE_BYTES, &tm_a, &res_full[kb], kb * BK, m0);
+            }
+          }
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | s)) { ok = false; break; }
+          uint8_t* st = ring + s * Map::STAGE_BYTES;
           if constexpr (WRES) {
             mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES);
-            tma_load_2d(a_ring + s * A_STAGE_BYTES, &tm_a, &full_bar[s], kb * BK, m0);
+            tma_load_2d(st, &tm_a, &full_bar[s], kb * BK, m0);
+          } else if constexpr (ARES) {
+            mbar_arrive_expect_tx(&full_bar[s], B_STAGE_BYTES);
+            tma_load_2d(st, &tm_b0, &full_bar[s], kb * BK, n0);
+            tma_load_2d(st + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
           } else {
-            uint8_t* sa = smem + s * (A_STAGE_BYTES + B_STAGE_BYTES);
-            uint8_t* sb = sa + A_STAGE_BYTES;
+            uint8_t* sb = st + A_STAGE_BYTES;
             mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
-            tma_load_2d(sa, &tm_a, &full_bar[s], kb * BK, m0);
+            tma_load_2d(st, &tm_a, &full_bar[s], kb * BK, m0);
             tma_load_2d(sb, &tm_b0, &full_bar[s], kb * BK, n0);
             tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
           }
@@ -242,27 +260,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (lane == 0) {
       constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, BM, BN) : umma_idesc(1, 0, 0, BM, BN);
       int s = 0; uint32_t ph = 0; bool ok = true;
-      if constexpr (WRES) {
-        ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200);
+      if (WRES && !(p.ablate & 4)) {
+        ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200);
         tc_fence_after();
       }
       int m_blk, n_blk;
-      for (int it = 0; ok && tile_coords<WRES>(p, it, m_blk, n_blk); ++it) {
+      uint32_t rph = 0;
+      for (int it = 0; ok && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
         const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        if (ARES && n_blk == 0 && it != 0) rph ^= 1;
+        for (int kb = 0; kb < p.k_blocks && !(p.ablate & 4); ++kb) {
+          if constexpr (ARES) {
+            if (n_blk == 0 && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb)) { ok = false; break; }
+          }
           if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s)) { ok = false; break; }
           tc_fence_after();
           uint32_t a_addr, b_addr;
-          if constexpr (WRES) {
-            a_addr = smem_u32(a_ring + s * A_STAGE_BYTES);
-            b_addr = smem_u32(w_base + kb * B_STAGE_BYTES);
-          } else {
-            a_addr = smem_u32(smem + s * (A_STAGE_BYTES + B_STAGE_BYTES));
-            b_addr = a_addr + A_STAGE_BYTES;
-          }
+          const uint32_t st = smem_u32(ring + s * Map::STAGE_BYTES);
+          if constexpr (WRES) { a_addr = st; b_addr = smem_u32(res_base + kb * B_STAGE_BYTES); }
+          else if constexpr (ARES) { a_addr = smem_u32(res_base + kb * A_STAGE_BYTES); b_addr = st; }
+          else { a_addr = st; b_addr = st + A_STAGE_BYTES; }
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
           const uint64_t b_desc = umma_smem_desc_sw128(b_addr);
 #pragma unroll
@@ -271,7 +291,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if constexpr (KIND == KIND_I8) umma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
             else umma_f8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
           }
-          umma_commit(&empty_bar[s]);          // smem stage reusable once these MMAs retire
+          umma_commit(&empty_bar[s]);          // ring stage reusable once these MMAs retire
+          if (ARES && n_blk == p.n_blocks - 1) umma_commit(&res_empty[kb]);   // last reader of this A piece
           if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&acc_full[as]);     // accumulator complete
@@ -282,19 +303,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int e = warp - 2;                // 0..7
     const int q = warp & 3;                // TMEM lane quarter this warp may read
     const int grp = e >> 2;                // column half of the tile handled by this warp
-    uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;
+    uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's pair of staging boxes
     constexpr int WARP_OUT_COLS = OUT_COLS_PER_TILE / 2;          // output columns per warp per tile (128 / 64)
     const int wcol0 = grp * WARP_OUT_COLS;                        // first output column (inside the tile) of this warp
     int obuf = 0; bool ok = true;
     int m_blk, n_blk;
-    // per-row state, fetched once per row block and kept in registers across its column blocks
-    float sa = 0.f;
+    // per-row state, fetched once per row block and kept in registers across its column blocks; the
+    // token scale of the NEXT row block is prefetched while the current tile is processed
+    float sa = 0.f, sa_next = 0.f;
     uint64_t sn2[16], cs2[16];             // sin / cos row of this thread's token as fp32 pairs
     int cur_m_blk = -1;
     uint32_t stg_off[4];                   // byte offsets of the 4 pieces of this thread's row in a swizzled staging box
 #pragma unroll
     for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
-    for (int it = 0; ok && tile_coords<WRES>(p, it, m_blk, n_blk); ++it) {
+    if constexpr (EPI != EPI_I32) {
+      if (tile_coords<SCHED>(p, 0, m_blk, n_blk)) {
+        const int r = m_blk * BM + q * 32 + lane;
+        if (r < p.M) sa_next = __ldg(p.scale_a + r);
+      }
+    }
+    for (int it = 0; ok && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
       const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
       const int m0 = m_blk * BM;
       const int n0 = n_blk * OUT_COLS_PER_TILE;
@@ -311,7 +339,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if constexpr (EPI != EPI_I32) {
         if (m_blk != cur_m_blk) {
           cur_m_blk = m_blk;
-          sa = row_ok ? __ldg(p.scale_a + row) : 0.f;
+          sa = sa_next;
           if constexpr (EPI == EPI_ROTARY) {
             const int pos = row_ok ? (int)(((long long)row + p.row_offset) % p.seqlen) : 0;
             const ulonglong2* s4 = reinterpret_cast<const ulonglong2*>(p.sin_tab + (long long)pos * 32);
@@ -322,6 +350,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               sn2[2 * j] = a.x; sn2[2 * j + 1] = a.y;
               cs2[2 * j] = b.x; cs2[2 * j + 1] = b.y;
             }
+          }
+        }
+        {
+          int nm, nn;
+          if (tile_coords<SCHED>(p, it + 1, nm, nn) && nm != m_blk) {
+            const int r = nm * BM + q * 32 + lane;
+            sa_next = (r < p.M) ? __ldg(p.scale_a + r) : 0.f;
           }
         }
         if (!WRES || it == 0) {
@@ -378,49 +413,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           auto run_tile = [&](auto direct_tag) {
             constexpr bool DIRECT = decltype(direct_tag)::value;
             __half* drow0 = reinterpret_cast<__half*>(p.C) + (long long)row * p.ldc;
-            // one 32-column box = 4 pieces of 8 fp16
-            auto box_begin = [&]() {
+            // Output leaves in pairs of 32-column boxes (4 pieces of 8 fp16 per row and box): both boxes are
+            // staged, then one proxy fence + one warp sync publish them to two TMA stores.  (Plain coalesced
+            // global stores from the staged boxes were measured and are slower than the TMA stores.)
+            int buf_a = 0, buf_b = 0;
+            auto pair_begin = [&]() {
+              buf_a = obuf; buf_b = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
               if constexpr (!DIRECT) {
-                if (lane == 0) tma_store_wait_read<OUT_BUFS - 1>();   // the store that last used this buffer has read it
+                if (lane == 0) tma_store_wait_read<OUT_BUFS - 2>();   // the stores that last used these two buffers have read them
                 __syncwarp();
               }
             };
-            auto put = [&](int n, int piece, uint4 o) {
+            auto put = [&](int which, int n, int piece, uint4 o) {
               if constexpr (DIRECT) {
                 if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = o;
               } else {
-                *reinterpret_cast<uint4*>(out_buf + obuf * OUT_BUF_BYTES + stg_off[piece]) = o;
+                *reinterpret_cast<uint4*>(out_buf + (which ? buf_b : buf_a) * OUT_BUF_BYTES + stg_off[piece]) = o;
               }
             };
-            auto box_end = [&](int n) {
+            auto pair_end = [&](int n_a, int n_b) {
               if constexpr (!DIRECT) {
                 fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
                 __syncwarp();
-                if (lane == 0 && !(p.ablate & 1)) { tma_store_2d(&tm_c, out_buf + obuf * OUT_BUF_BYTES, n, row_base); tma_store_commit(); }
-                obuf = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
+                if (lane == 0 && !(p.ablate & 1)) {
+                  tma_store_2d(&tm_c, out_buf + buf_a * OUT_BUF_BYTES, n_a, row_base); tma_store_commit();
+                  if (n_b < p.N) { tma_store_2d(&tm_c, out_buf + buf_b * OUT_BUF_BYTES, n_b, row_base); tma_store_commit(); }
+                }
+                obuf = (buf_b + 1 == OUT_BUFS) ? 0 : buf_b + 1;
               }
             };
 
             if constexpr (EPI == EPI_DEQUANT) {
-              // 32-column steps; the TMEM load of step i+1 is in flight while step i is converted and staged
+              // all of this warp's accumulator columns are fetched with back-to-back TMEM loads and one wait
               constexpr int NSUB = WARP_OUT_COLS / 32;
-              uint32_t v[2][32];
-              tmem_ld_32x32b_x32(t_row + wcol0, v[0]);
+              uint32_t v[NSUB][32];
 #pragma unroll
-              for (int ci = 0; ci < NSUB; ++ci) {
-                tmem_ld_wait();
-                if (ci + 1 < NSUB) tmem_ld_32x32b_x32(t_row + wcol0 + (ci + 1) * 32, v[(ci + 1) & 1]);
-                const int c = ci * 32;
-                const int n = n0 + wcol0 + c;
+              for (int ci = 0; ci < NSUB; ++ci) tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, v[ci]);
+              tmem_ld_wait();
+#pragma unroll
+              for (int pr = 0; pr < NSUB / 2; ++pr) {
+                const int n = n0 + wcol0 + pr * 64;
                 if (n < p.N) {
-                  box_begin();
+                  pair_begin();
 #pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    const ulonglong2 s_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
-                    const ulonglong2 s_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
-                    put(n, j >> 3, dequant_piece<KIND>(&v[ci & 1][j], sa2, s_lo, s_hi));
+                  for (int h = 0; h < 2; ++h) {
+                    const int c = pr * 64 + h * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                      const ulonglong2 s_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
+                      const ulonglong2 s_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
+                      put(h, n + h * 32, j >> 3, dequant_piece<KIND>(&v[pr * 2 + h][j], sa2, s_lo, s_hi));
+                    }
                   }
-                  box_end(n);
+                  pair_end(n, n + 32);
                 }
               }
             } else if constexpr (EPI == EPI_ROTARY) {
@@ -434,20 +479,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 tmem_ld_32x32b_x32(t_row + wcol0 + c, v0);
                 tmem_ld_32x32b_x32(t_row + wcol0 + c + 32, v1);
                 tmem_ld_wait();
-                const int buf_lo = obuf, buf_hi = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
-                if constexpr (!DIRECT) {
-                  if (lane == 0) tma_store_wait_read<OUT_BUFS - 2>();   // both boxes free
-                  __syncwarp();
-                }
-                auto put2 = [&](int piece, uint4 lo, uint4 hi) {
-                  if constexpr (DIRECT) {
-                    if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = lo;
-                    if (row_ok && n + 32 + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + 32 + piece * 8) = hi;
-                  } else {
-                    *reinterpret_cast<uint4*>(out_buf + buf_lo * OUT_BUF_BYTES + stg_off[piece]) = lo;
-                    *reinterpret_cast<uint4*>(out_buf + buf_hi * OUT_BUF_BYTES + stg_off[piece]) = hi;
-                  }
-                };
+                pair_begin();
+                auto put2 = [&](int piece, uint4 lo, uint4 hi) { put(0, n, piece, lo); put(1, n + 32, piece, hi); };
                 if (n < p.rot_cols) {
 #pragma unroll
                   for (int j = 0; j < 32; j += 8) {
@@ -484,32 +517,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                                              *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j + 4)));
                   }
                 }
-                if constexpr (!DIRECT) {
-                  fence_proxy_async_smem();
-                  __syncwarp();
-                  if (lane == 0 && !(p.ablate & 1)) {
-                    tma_store_2d(&tm_c, out_buf + buf_lo * OUT_BUF_BYTES, n, row_base); tma_store_commit();
-                    tma_store_2d(&tm_c, out_buf + buf_hi * OUT_BUF_BYTES, n + 32, row_base); tma_store_commit();
-                  }
-                  obuf = (buf_hi + 1 == OUT_BUFS) ? 0 : buf_hi + 1;
-                }
+                pair_end(n, n + 32);
               }
-            } else {   // EPI_SILU: gate at accumulator column c, up at BN/2 + c; next step's loads in flight
-              constexpr int NSUB = WARP_OUT_COLS / 32;
-              uint32_t g[2][32], u[2][32];
-              tmem_ld_32x32b_x32(t_row + wcol0, g[0]);
-              tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0, u[0]);
+            } else {   // EPI_SILU: gate at accumulator column c, up at BN/2 + c
+              constexpr int NSUB = WARP_OUT_COLS / 32;      // 2 boxes = one pair
+              uint32_t g[NSUB][32], u[NSUB][32];
 #pragma unroll
               for (int ci = 0; ci < NSUB; ++ci) {
-                tmem_ld_wait();
-                if (ci + 1 < NSUB) {
-                  tmem_ld_32x32b_x32(t_row + wcol0 + (ci + 1) * 32, g[(ci + 1) & 1]);
-                  tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0 + (ci + 1) * 32, u[(ci + 1) & 1]);
-                }
-                const int c = ci * 32;
-                const int n = n0 + wcol0 + c;
-                if (n < p.N) {
-                  box_begin();
+                tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, g[ci]);
+                tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0 + ci * 32, u[ci]);
+              }
+              tmem_ld_wait();
+              const int n = n0 + wcol0;
+              if (n < p.N) {
+                pair_begin();
+#pragma unroll
+                for (int h = 0; h < NSUB; ++h) {
+                  const int c = h * 32;
 #pragma unroll
                   for (int j = 0; j < 32; j += 8) {
                     const ulonglong2 g_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
@@ -522,16 +546,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                       float g0, g1;
-                      upk2(dequant2<KIND>(g[ci & 1][j + 2 * i], g[ci & 1][j + 2 * i + 1], sa2, sg[i]), g0, g1);
-                      const uint64_t up = dequant2<KIND>(u[ci & 1][j + 2 * i], u[ci & 1][j + 2 * i + 1], sa2, su[i]);
+                      upk2(dequant2<KIND>(g[h][j + 2 * i], g[h][j + 2 * i + 1], sa2, sg[i]), g0, g1);
+                      const uint64_t up = dequant2<KIND>(u[h][j + 2 * i], u[h][j + 2 * i + 1], sa2, su[i]);
                       // silu(gate) = gate / (1 + exp(-gate)); exp and the division use the fast hardware approximations
                       const uint64_t sl = pk2(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
                       o[i] = pack_half2_from(fmul2(sl, up));
                     }
-                    put(n, j >> 3, make_uint4(o[0], o[1], o[2], o[3]));
+                    put(h, n + h * 32, j >> 3, make_uint4(o[0], o[1], o[2], o[3]));
                   }
-                  box_end(n);
                 }
+                pair_end(n, n + 32);
               }
             }
           };
