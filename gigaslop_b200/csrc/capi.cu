@@ -111,3 +111,39 @@ int32_t gsb200_dual_gemm_fp8_silu_f16(const uint8_t* A, int64_t lda, const uint8
 }
 
 }  // extern "C"
+
+// ---- module hooks named by the reference's generated headers -------------------------------------------
+// `<prefix>_Kernel_Module_Load` calls `_mlir_<prefix>_cuda_init` once and `_mlir_<prefix>_cuda_load_to_device`
+// once per visible device (cute/main.cpp:14-15,95-96).  Here "init" has nothing to load and "load to device"
+// validates the device and sets the kernels' shared-memory attributes on it.
+namespace {
+void module_init(void** args) {
+  // args = { cudaLibrary_t** library, cudaError_t* ret }
+  if (!args) return;
+  if (args[0]) **reinterpret_cast<cudaLibrary_t**>(args[0]) = nullptr;
+  if (args[1]) *reinterpret_cast<cudaError_t*>(args[1]) = cudaSuccess;
+}
+void module_load_to_device(void** args) {
+  // args = { cudaLibrary_t** library, int32_t* device_id, cudaError_t* ret }
+  if (!args || !args[1] || !args[2]) return;
+  const int dev = *reinterpret_cast<int32_t*>(args[1]);
+  cudaError_t* ret = reinterpret_cast<cudaError_t*>(args[2]);
+  int prev = 0;
+  *ret = cudaGetDevice(&prev);
+  if (*ret != cudaSuccess) return;
+  *ret = cudaSetDevice(dev);
+  if (*ret != cudaSuccess) return;
+  const int32_t rc = ensure_device();
+  cudaSetDevice(prev);
+  *ret = rc == GSB200_OK ? cudaSuccess : (rc > 0 ? static_cast<cudaError_t>(rc) : cudaErrorInvalidDevice);
+}
+}  // namespace
+
+#define GSB200_MODULE_HOOKS(P)                                                          \
+  extern "C" void _mlir_##P##_cuda_init(void** a) { module_init(a); }                   \
+  extern "C" void _mlir_##P##_cuda_load_to_device(void** a) { module_load_to_device(a); }
+
+GSB200_MODULE_HOOKS(gemm_i8_std)
+GSB200_MODULE_HOOKS(gemm_i8_rotary_N1536_K512_H8D64R64S1024)
+GSB200_MODULE_HOOKS(gemm_i8_rotary_N1536_K512_H8D64R64S2048)
+GSB200_MODULE_HOOKS(gemm_i8_dual_silu_N2048_K512)

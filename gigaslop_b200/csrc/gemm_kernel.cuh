@@ -21,7 +21,9 @@
 //
 //   warp 0      TMA producer   global -> 128B-swizzled smem (no multicast)
 //   warp 1      TMEM owner + single-thread tcgen05.mma issue
-//   warps 2..9  epilogue: tcgen05.ld (thread = accumulator row) -> math ->
+//   warps 2,3   idle; they complete the first warpgroup, which gives its registers to the epilogue
+//               (setmaxnreg: 56 per thread for warps 0-3, 224 for the two epilogue warpgroups)
+//   warps 4..11 epilogue: tcgen05.ld (thread = accumulator row) -> math ->
 //               swizzled smem staging -> TMA store (per-warp 32 x 32 fp16 boxes, issued in pairs)
 //
 // Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue of tile i overlaps
@@ -43,7 +45,10 @@ constexpr int UMMA_K = 32;         // K bytes per tcgen05.mma for 8-bit kinds
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_WARPS = 8;
-constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+constexpr int FRONT_WARPS = 4;                          // warp 0 producer, warp 1 MMA, warps 2-3 idle (one warpgroup)
+constexpr int GEMM_THREADS = 32 * (FRONT_WARPS + EPI_WARPS);
+constexpr int FRONT_REGS = 56;                          // register budgets after setmaxnreg (per thread)
+constexpr int EPI_REGS = 224;
 constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
 constexpr int RES_MAX_KBLOCKS = 4;                      // resident operand (W slice or A block): up to K = 512
@@ -202,6 +207,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The register re-split sits inside each role's branch: code placed after the point where the two
+  // branches meet would be compiled for the smaller budget.
+  if (warp < FRONT_WARPS) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FRONT_REGS));
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -298,9 +307,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (ok) umma_commit(&acc_full[as]);     // accumulator complete
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
     // ------------------------------ epilogue ----------------------------------
-    const int e = warp - 2;                // 0..7
+    const int e = warp - FRONT_WARPS;      // 0..7
     const int q = warp & 3;                // TMEM lane quarter this warp may read
     const int grp = e >> 2;                // column half of the tile handled by this warp
     uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's pair of staging boxes
@@ -469,16 +480,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
               }
             } else if constexpr (EPI == EPI_ROTARY) {
-              // one 64-wide head per step: x0 = columns 0..31, x1 = columns 32..63 of the head; the two
-              // 32-column halves go to two staging boxes that are open at the same time
-#pragma unroll 1
-              for (int c = 0; c < WARP_OUT_COLS; c += 64) {
+              // two 64-wide heads per warp and tile: x0 = columns 0..31, x1 = columns 32..63 of a head.  All four
+              // 32-column accumulator slices are fetched up front; each head leaves as one pair of boxes.
+              constexpr int NHEAD = WARP_OUT_COLS / 64;
+              uint32_t v[2 * NHEAD][32];
+#pragma unroll
+              for (int ci = 0; ci < 2 * NHEAD; ++ci) tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, v[ci]);
+              tmem_ld_wait();
+#pragma unroll
+              for (int hd = 0; hd < NHEAD; ++hd) {
+                const int c = hd * 64;
                 const int n = n0 + wcol0 + c;
                 if (n >= p.N) break;
-                uint32_t v0[32], v1[32];
-                tmem_ld_32x32b_x32(t_row + wcol0 + c, v0);
-                tmem_ld_32x32b_x32(t_row + wcol0 + c + 32, v1);
-                tmem_ld_wait();
+                const uint32_t* v0 = v[2 * hd];
+                const uint32_t* v1 = v[2 * hd + 1];
                 pair_begin();
                 auto put2 = [&](int piece, uint4 lo, uint4 hi) { put(0, n, piece, lo); put(1, n + 32, piece, hi); };
                 if (n < p.rot_cols) {
