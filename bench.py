@@ -25,6 +25,9 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the QKV+rotary GEMM at the bench's full size,
+# from the ncu capture summarised in profiles/gemm_i8_rotary_config2.md (35.5 MB + 148.1 MB)
+GEMM_DRAM_TRAFFIC = 183.6e6
 METRIC = "w8a8_qkv_rotary_gemm_tops"
 UNIT = "TOPS"
 
@@ -260,7 +263,7 @@ def run_native(args):
                         "frac_of_2x_bf16_" + which: ops_step / (gemm_avg_ms * 1e-3) / 1e12 / (2 * bf16_peak),
                         "quantise_plus_launch_gaps_ms": ms_step - gemm_avg_ms, "gemm_ms": gemm_avg_ms},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "traffic": None, "peak_source": which,
+                     "frac": achieved / hbm_peak, "traffic": GEMM_DRAM_TRAFFIC, "peak_source": which,
                      "kernel": "gemm_tcgen05_kernel<i8, rotary>", "bytes_per_launch": gemm_bytes},
         "cpu_baseline": {"value": 2.0 * cpu_rows * N * K / cpu_sec / 1e12, "unit": UNIT, "cores": os.cpu_count() or 1,
                          "kind": "port", "sample": f"{cpu_rows} of 65536 rows, best of 4 (quantize_tensor + rotary_ref, torch CPU fp32)"},
