@@ -31,6 +31,11 @@ int32_t gsb200_ptq_fp8(const void* x, int32_t x_dtype, int64_t ldx, uint8_t* q, 
   return launch_ptq(x, x_dtype, ldx, q, ldq, scale, M, K, torch_formulation ? 2 : 1, S(stream));
 }
 
+int32_t gsb200_ptq_mxfp8(const void* x, int32_t x_dtype, int64_t ldx, uint8_t* q, int64_t ldq, uint8_t* scales,
+                         int64_t ld_scales, int64_t M, int32_t K, gsb200_stream_t stream) {
+  return launch_ptq_mx(x, x_dtype, ldx, q, ldq, scales, ld_scales, M, K, S(stream));
+}
+
 static GemmArgs base_args(int kind, int epi, const void* A, int64_t lda, const void* B0, const void* B1, int64_t ldb,
                           void* C, int64_t ldc, const float* sa, const float* sb0, const float* sb1, int64_t M,
                           int32_t N, int32_t K, int32_t flags) {
@@ -108,6 +113,17 @@ int32_t gsb200_dual_gemm_fp8_silu_f16(const uint8_t* A, int64_t lda, const uint8
   return launch_gemm(base_args(KIND_F8, EPI_SILU, A, lda, B_gate, B_up, ldb, C, ldc, scale_a, scale_b_gate, scale_b_up,
                                M, N, K, flags),
                      S(stream));
+}
+
+int32_t gsb200_dual_gemm_fp8_silu_mxfp8(const uint8_t* A, int64_t lda, const uint8_t* B_gate, const uint8_t* B_up,
+                                        int64_t ldb, uint8_t* out_fp8, int64_t ld_out, uint8_t* out_scale,
+                                        int64_t ld_scale, const float* scale_a, const float* scale_b_gate,
+                                        const float* scale_b_up, int64_t M, int32_t N, int32_t K, int32_t flags,
+                                        gsb200_stream_t stream) {
+  GemmArgs a = base_args(KIND_F8, EPI_SILU_MX, A, lda, B_gate, B_up, ldb, out_fp8, ld_out, scale_a, scale_b_gate,
+                         scale_b_up, M, N, K, flags);
+  a.out_scale = out_scale; a.ld_scale = ld_scale;
+  return launch_gemm(a, S(stream));
 }
 
 }  // extern "C"

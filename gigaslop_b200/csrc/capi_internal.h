@@ -15,6 +15,8 @@ inline int32_t cuda_status(cudaError_t e, const char* what) {
   return static_cast<int32_t>(e);
 }
 
+int32_t launch_ptq_mx(const void* x, int x_dtype, long long ldx, uint8_t* q, long long ldq, uint8_t* scales,
+                      long long lds, long long M, int K, cudaStream_t st);
 int32_t launch_ptq(const void* x, int x_dtype, long long ldx, void* q, long long ldq, float* scale, long long M,
                    int K, int fmt, cudaStream_t st);
 
@@ -24,6 +26,7 @@ struct GemmArgs {
   const void* A; long long lda;
   const void* B0; const void* B1; long long ldb;
   void* C; long long ldc;
+  uint8_t* out_scale; long long ld_scale;   // MXFP8 output: E8M0 scales [M, N/32]
   const float* scale_a; const float* scale_b0; const float* scale_b1;
   const float* sin_tab; const float* cos_tab;
   long long M; int N; int K;

@@ -77,7 +77,7 @@ int32_t ensure_device() {
   cudaError_t errs[] = {
       set_attr<KIND_I8, EPI_I32>(),     set_attr<KIND_I8, EPI_DEQUANT>(), set_attr<KIND_I8, EPI_ROTARY>(),
       set_attr<KIND_I8, EPI_SILU>(),    set_attr<KIND_F8, EPI_DEQUANT>(), set_attr<KIND_F8, EPI_ROTARY>(),
-      set_attr<KIND_F8, EPI_SILU>()};
+      set_attr<KIND_F8, EPI_SILU>(),    set_attr<KIND_F8, EPI_SILU_MX>()};
   for (cudaError_t er : errs)
     if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
   if (!encode_fn()) {
@@ -114,7 +114,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   if (!aligned16(a.A) || !aligned16(a.B0) || !aligned16(a.C)) return GSB200_ERR_BAD_ARG;
   if (a.K % 16 != 0 || a.lda < a.K || a.ldb < a.K || a.lda % 16 != 0 || a.ldb % 16 != 0) return GSB200_ERR_BAD_ARG;
   if (a.ldc < a.N) return GSB200_ERR_BAD_ARG;
-  const bool dual = a.epi == EPI_SILU;
+  const bool dual = a.epi == EPI_SILU || a.epi == EPI_SILU_MX;
   if (a.epi == EPI_I32) {
     if (a.N % 4 != 0 || a.ldc % 4 != 0) return GSB200_ERR_BAD_ARG;
   } else {
@@ -124,6 +124,10 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   }
   if (dual) {
     if (!a.B1 || !aligned16(a.B1) || !a.scale_b1 || (reinterpret_cast<uintptr_t>(a.scale_b1) & 15))
+      return GSB200_ERR_BAD_ARG;
+  }
+  if (a.epi == EPI_SILU_MX) {
+    if (a.kind != KIND_F8 || a.N % 32 != 0 || !a.out_scale || a.ld_scale < a.N / 32 || a.ldc % 16 != 0)
       return GSB200_ERR_BAD_ARG;
   }
   int rot_cols = 0;
@@ -144,6 +148,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.n_blocks = (a.N + out_cols_per_tile - 1) / out_cols_per_tile;
   p.k_blocks = (a.K + BK - 1) / BK;
   p.C = a.C; p.ldc = a.ldc;
+  p.out_scale = a.out_scale; p.ld_scale = a.ld_scale;
   p.scale_a = a.scale_a; p.scale_b0 = a.scale_b0; p.scale_b1 = a.scale_b1;
   p.sin_tab = a.sin_tab; p.cos_tab = a.cos_tab;
   p.seqlen = a.seqlen > 0 ? a.seqlen : 1;
@@ -159,7 +164,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   bool ok = make_map_2d(&ta, u8, 1, a.A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
   ok = ok && make_map_2d(&tb0, u8, 1, a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
   ok = ok && make_map_2d(&tb1, u8, 1, dual ? a.B1 : a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
-  if (a.epi != EPI_I32)
+  if (a.epi != EPI_I32 && a.epi != EPI_SILU_MX)
     ok = ok && make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.C, (uint64_t)a.M, (uint64_t)a.N,
                            (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
   else
@@ -199,6 +204,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
       case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_SILU_MX: e = launch_inst<KIND_F8, EPI_SILU_MX>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else {

@@ -6,6 +6,7 @@
 //   EPI_DEQUANT  f16( acc * sA[m] * sB[n] )                   per-token x per-channel dequant
 //   EPI_ROTARY   dequant, then rotate-half on the Q|K columns  (QKV projection)
 //   EPI_SILU     f16( silu(gate) * up ), gate|up in one UMMA   (SwiGLU dual GEMM)
+//   EPI_SILU_MX  the same product emitted as MXFP8: E4M3 elements + one E8M0 scale per 32 output columns
 //
 // Three schedules share the epilogue (tiles are 128 rows x 256 accumulator columns):
 //
@@ -30,11 +31,13 @@
 // the MMAs of tile i+1.  The epilogue reads nothing from global memory inside its column loop:
 // per-channel scales sit in shared memory, the per-token scale is prefetched one tile ahead.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "ptx.cuh"
 
 namespace gsb {
 
-enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3 };
+enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3, EPI_SILU_MX = 4 };
 enum : int { KIND_I8 = 0, KIND_F8 = 1 };
 enum : int { SCHED_STREAM = 0, SCHED_WRES = 1, SCHED_ARES = 2 };
 
@@ -88,6 +91,8 @@ struct GemmParams {
   int n_groups;                // WRES: number of row-block groups (grid = n_groups * n_blocks)
   int m_major;                 // STREAM: a CTA walks all column blocks of a row block before the next (ARES always does)
   void* C;                     // output base (direct-store path and int32 output)
+  uint8_t* out_scale;          // EPI_SILU_MX: E8M0 scales [M, N/32]
+  long long ld_scale;          //              row stride of out_scale in bytes
   long long ldc;               // output row stride in elements
   const float* scale_a;        // [M]
   const float* scale_b0;       // [N]   (dual: gate)
@@ -190,7 +195,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr int OUT_COLS_PER_TILE = (EPI == EPI_SILU) ? BN / 2 : BN;
+  constexpr bool DUAL = (EPI == EPI_SILU || EPI == EPI_SILU_MX);
+  constexpr int OUT_COLS_PER_TILE = DUAL ? BN / 2 : BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -217,7 +223,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       int s = 0; uint32_t ph = 0; bool ok = true;
       if constexpr (WRES) {
         const int n0 = (blockIdx.x % p.n_blocks) * OUT_COLS_PER_TILE;
-        const int n1 = (EPI == EPI_SILU) ? n0 : n0 + BN / 2;
+        const int n1 = DUAL ? n0 : n0 + BN / 2;
         mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           uint8_t* sb = res_base + kb * B_STAGE_BYTES;
@@ -230,7 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       for (int it = 0; ok && !(p.ablate & 4) && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
         const int m0 = m_blk * BM;
         const int n0 = n_blk * OUT_COLS_PER_TILE;
-        const int n1 = (EPI == EPI_SILU) ? n0 : n0 + BN / 2;
+        const int n1 = DUAL ? n0 : n0 + BN / 2;
         if (ARES && n_blk == 0 && it != 0) rph ^= 1;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if constexpr (ARES) {
@@ -373,7 +379,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (!WRES || it == 0) {
           // per-channel scales of this warp group's columns (dual: 64 gate | 64 up): fetched now, parked in
           // shared memory after the accumulator wait (see below)
-          if constexpr (EPI == EPI_SILU) {
+          if constexpr (DUAL) {
             const int n = n0 + wcol0 + (lane & 15) * 4;
             const float* src = (lane < 16) ? p.scale_b0 : p.scale_b1;
             if (n + 4 <= p.N) sbv = __ldg(reinterpret_cast<const float4*>(src + n));
@@ -393,7 +399,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
       if constexpr (EPI != EPI_I32) {
         if (!WRES || it == 0) {
-          if constexpr (EPI == EPI_SILU) *reinterpret_cast<float4*>(sc + (lane < 16 ? 0 : 64) + (lane & 15) * 4) = sbv;
+          if constexpr (DUAL) *reinterpret_cast<float4*>(sc + (lane < 16 ? 0 : 64) + (lane & 15) * 4) = sbv;
           else *reinterpret_cast<float4*>(sc + lane * 4) = sbv;
           __syncwarp();
         }
@@ -415,6 +421,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               for (int j = 0; j < 32; j += 4)
                 if (n0 + col + j + 4 <= p.N)
                   *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          }
+        } else if constexpr (EPI == EPI_SILU_MX) {
+          // SwiGLU product quantised per 32 output columns: e = biased exponent of the block maximum,
+          // scale byte = clamp(e - 8, 0, 254) (value 2^(byte-127)), elements = e4m3_rn_satfinite(v * 2^(127-byte)).
+          // A thread holds whole 32-column blocks of its row, so the block maximum needs no exchange.
+          const uint64_t sa2 = pk2(sa, sa);
+          constexpr int NSUB = WARP_OUT_COLS / 32;
+          uint32_t g[NSUB][32], u[NSUB][32];
+#pragma unroll
+          for (int ci = 0; ci < NSUB; ++ci) {
+            tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, g[ci]);
+            tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0 + ci * 32, u[ci]);
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < NSUB; ++h) {
+            const int c = h * 32;
+            const int n = n0 + wcol0 + c;
+            if (n + 32 <= p.N) {
+              float o[32];
+              float amax = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const uint64_t sg = *reinterpret_cast<const uint64_t*>(sc + c + j);
+                const uint64_t su = *reinterpret_cast<const uint64_t*>(sc + 64 + c + j);
+                float g0, g1, u0, u1;
+                upk2(dequant2<KIND>(g[h][j], g[h][j + 1], sa2, sg), g0, g1);
+                upk2(dequant2<KIND>(u[h][j], u[h][j + 1], sa2, su), u0, u1);
+                o[j] = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                o[j + 1] = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                amax = fmaxf(amax, fmaxf(fabsf(o[j]), fabsf(o[j + 1])));
+              }
+              int eb = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+              eb = max(0, min(254, eb));
+              const float inv = __uint_as_float((uint32_t)(254 - eb) << 23);
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * j] * inv, o[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * j + 2] * inv, o[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                w[j] = lo | (hi << 16);
+              }
+              if (row_ok) {
+                uint8_t* dst = reinterpret_cast<uint8_t*>(p.C) + (long long)row * p.ldc + n;
+                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                p.out_scale[(long long)row * p.ld_scale + (n >> 5)] = (uint8_t)eb;
+              }
             }
           }
         } else {

@@ -156,6 +156,57 @@ static cudaError_t launch_fmt(const void* x, long long ldx, void* q, long long l
   return cudaGetLastError();
 }
 
+// ---- MXFP8 activation quantiser: E4M3 elements + one E8M0 scale per 32 consecutive elements of a row -------
+// scale byte = clamp(biased_exponent(block max) - 8, 0, 254), elements = e4m3_rn_satfinite(x * 2^(127-byte)).
+// A lane owns 8 consecutive elements, so a 32-element block lives in 4 neighbouring lanes (two xor-shuffles).
+template <typename Tin>
+__global__ void __launch_bounds__(QUANT_WARPS * 32)
+ptq_mx_kernel(const Tin* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+              uint8_t* __restrict__ scales, long long lds, long long M, int K) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * QUANT_WARPS + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const Tin* xr = x + row * ldx;
+  const int nvec = K >> 3;                         // K % 32 == 0 -> nvec % 4 == 0: the 4 lanes of a block agree on `v < nvec`
+  for (int v0 = 0; v0 < nvec; v0 += 32) {
+    const int v = v0 + lane;
+    float vals[8];
+    float amax = 0.f;
+    if (v < nvec) {
+      load8<Tin>(xr + v * 8, vals);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vals[j]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (v < nvec) {
+      int eb = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 8;
+      eb = max(0, min(254, eb));
+      const float inv = __uint_as_float((uint32_t)(254 - eb) << 23);
+      *reinterpret_cast<uint2*>(q + row * ldq + v * 8) = pack_e4m3<0>(vals, inv);
+      if ((lane & 3) == 0) scales[row * lds + (v >> 2)] = (uint8_t)eb;
+    }
+  }
+}
+
+int32_t launch_ptq_mx(const void* x, int x_dtype, long long ldx, uint8_t* q, long long ldq, uint8_t* scales,
+                      long long lds, long long M, int K, cudaStream_t st) {
+  if (M == 0) return GSB200_OK;
+  if (!x || !q || !scales || M < 0 || K <= 0 || K % 32 != 0) return GSB200_ERR_BAD_ARG;
+  if (ldx < K || ldq < K || ldq % 8 != 0 || lds < K / 32) return GSB200_ERR_BAD_ARG;
+  if (x_dtype != GSB200_F16 && x_dtype != GSB200_F32) return GSB200_ERR_BAD_ARG;
+  const int esz = x_dtype == GSB200_F16 ? 2 : 4;
+  if ((ldx * esz) % 16 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+    return GSB200_ERR_BAD_ARG;
+  if ((M + QUANT_WARPS - 1) / QUANT_WARPS > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
+  const unsigned blocks = (unsigned)((M + QUANT_WARPS - 1) / QUANT_WARPS);
+  if (x_dtype == GSB200_F16)
+    ptq_mx_kernel<__half><<<blocks, QUANT_WARPS * 32, 0, st>>>(static_cast<const __half*>(x), ldx, q, ldq, scales, lds, M, K);
+  else
+    ptq_mx_kernel<float><<<blocks, QUANT_WARPS * 32, 0, st>>>(static_cast<const float*>(x), ldx, q, ldq, scales, lds, M, K);
+  return cuda_status(cudaGetLastError(), "ptq_mx launch");
+}
+
 int32_t launch_ptq(const void* x, int x_dtype, long long ldx, void* q, long long ldq, float* scale, long long M, int K,
                    int fmt, cudaStream_t st) {
   if (M == 0) return GSB200_OK;

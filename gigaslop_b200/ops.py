@@ -155,3 +155,30 @@ def dual_gemm_fp8_silu(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=N
     """FP8 SwiGLU dual GEMM (fly/rdna_fp8_dual_gemm_silu.py compile_fp8_dual_gemm_silu)."""
     return _dual(lib().gsb200_dual_gemm_fp8_silu_f16, "dual_gemm_fp8_silu", A, B_gate, B_up, scale_a,
                  scale_b_gate, scale_b_up, out, flags, _F8)
+
+
+def mxfp8_quantize(x, out=None, out_scale=None):
+    """Activations [M,K] fp16/fp32 -> (float8_e4m3fn [M,K], uint8 E8M0 scales [M,K/32]); one scale per 32 elements."""
+    _need_cuda(x)
+    x = _rowmajor(x, "x")
+    M, K = x.shape
+    q = out if out is not None else torch.empty((M, K), dtype=torch.float8_e4m3fn, device=x.device)
+    s = out_scale if out_scale is not None else torch.empty((M, K // 32), dtype=torch.uint8, device=x.device)
+    check(lib().gsb200_ptq_mxfp8(x.data_ptr(), _dt(x), x.stride(0), q.data_ptr(), q.stride(0), s.data_ptr(),
+                                 s.stride(0), M, K, _stream()), "mxfp8_quantize")
+    return q, s
+
+
+def dual_gemm_fp8_silu_mxfp8(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=None, out_scale=None, flags=0):
+    """FP8 SwiGLU dual GEMM emitting MXFP8 (elements + E8M0 scale per 32 output columns); the interface of
+    fp8_dual_silu_mxfp8_wrapper (fly/export_fp8_dual_gemm_silu_mxfp8.py:206-236)."""
+    M, N, K = _check_ab(A, B_gate, _F8)
+    _check_ab(A, B_up, _F8)
+    _need_cuda(scale_a, scale_b_gate, scale_b_up)
+    q = out if out is not None else torch.empty((M, N), dtype=torch.float8_e4m3fn, device=A.device)
+    s = out_scale if out_scale is not None else torch.empty((M, N // 32), dtype=torch.uint8, device=A.device)
+    check(lib().gsb200_dual_gemm_fp8_silu_mxfp8(
+        A.data_ptr(), A.stride(0), B_gate.data_ptr(), B_up.data_ptr(), B_gate.stride(0), q.data_ptr(), q.stride(0),
+        s.data_ptr(), s.stride(0), scale_a.data_ptr(), scale_b_gate.data_ptr(), scale_b_up.data_ptr(), M, N, K, flags,
+        _stream()), "dual_gemm_fp8_silu_mxfp8")
+    return q, s

@@ -115,6 +115,24 @@ int32_t gsb200_dual_gemm_fp8_silu_f16(const uint8_t* A, int64_t lda, const uint8
                                       const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,
                                       int32_t K, int32_t flags, gsb200_stream_t stream);
 
+/* MXFP8 (OCP microscaling): E4M3 elements with one E8M0 scale (value 2^(byte-127)) per 32 consecutive
+ * elements; byte = clamp(biased fp32 exponent of the block maximum - 8, 0, 254), elements are
+ * e4m3_rn_satfinite(v * 2^(127-byte)).  The reference ships only the interface of its MXFP8 kernel
+ * (fly/export_fp8_dual_gemm_silu_mxfp8.py:145-236; the kernel module is absent), so this rule is this
+ * library's own choice (the OCP default) -- parity unpinned.
+ *
+ * gsb200_ptq_mxfp8: activations fp16/fp32 [M,K] -> E4M3 [M,K] + scales uint8 [M,K/32].  K % 32 == 0.
+ * gsb200_dual_gemm_fp8_silu_mxfp8: the SwiGLU dual GEMM (per-token x per-channel scaled FP8 inputs) emitting
+ * MXFP8 directly: out_fp8 [M,N] + out_scale uint8 [M,N/32] row-major -- fp8_dual_silu_mxfp8_wrapper
+ * (fly/export_fp8_dual_gemm_silu_mxfp8.py:206-236).  N % 32 == 0, ld_out % 16 == 0. */
+int32_t gsb200_ptq_mxfp8(const void* x, int32_t x_dtype, int64_t ldx, uint8_t* q, int64_t ldq, uint8_t* scales,
+                         int64_t ld_scales, int64_t M, int32_t K, gsb200_stream_t stream);
+int32_t gsb200_dual_gemm_fp8_silu_mxfp8(const uint8_t* A, int64_t lda, const uint8_t* B_gate, const uint8_t* B_up,
+                                        int64_t ldb, uint8_t* out_fp8, int64_t ld_out, uint8_t* out_scale,
+                                        int64_t ld_scale, const float* scale_a, const float* scale_b_gate,
+                                        const float* scale_b_up, int64_t M, int32_t N, int32_t K, int32_t flags,
+                                        gsb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
