@@ -9,4 +9,6 @@ from .ops import (  # noqa: F401
     gemm_fp8_rotary, dual_gemm_i8_silu, dual_gemm_fp8_silu, mxfp8_quantize, dual_gemm_fp8_silu_mxfp8,
 )
 
+from .lstm import lstm_layer, lstm_scratch, lstm_stack  # noqa: F401,E402
+
 __version__ = "0.1.0"

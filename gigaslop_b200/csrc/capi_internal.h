@@ -1,5 +1,6 @@
 // Declarations shared by the translation units of libgigaslop_b200.
 #pragma once
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -34,6 +35,16 @@ struct GemmArgs {
   int flags;
 };
 int32_t launch_gemm(const GemmArgs& a, cudaStream_t st);
+struct LstmLayerArgs {
+  const __half* ih; long long ld_ih;        // [T*B, 4H] fp16 hoisted input projection, row = t*B + b
+  const uint8_t* w_hh; long long ld_w;      // [4H, H] E4M3, K-major
+  const float* s_hh; const float* bias;     // [4H]; bias may be null
+  const uint8_t* h0; const __half* c0;      // [B, H] initial state or null
+  __half* h_out; uint8_t* h8_out; __half* c_last;
+  long long T, B; int H; int reverse;
+};
+size_t lstm_scratch_bytes(long long B, int H);
+int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_bytes, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached)
 int32_t read_clear_status(uint32_t out[4]);

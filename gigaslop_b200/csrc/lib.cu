@@ -2,4 +2,5 @@
 // word and the inline PTX helpers are shared without relocatable device code.
 #include "quant.cu"
 #include "gemm.cu"
+#include "lstm.cu"
 #include "capi.cu"

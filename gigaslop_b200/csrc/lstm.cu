@@ -1,0 +1,359 @@
+// Recurrent half of the LSTM layer: T sequential steps
+//     gates[b, 4H] = ih[t, b, 4H] + (h_{t-1} . W_hh^T) * (s_hh[n] / 448) + bias[n]      (gate blocks i | f | g | o)
+//     c_t = sigmoid(f) * c_{t-1} + sigmoid(i) * tanh(g);   h_t = sigmoid(o) * tanh(c_t)
+// in ONE persistent cooperative kernel (the reference replays two launches per step from a graph,
+// fly/bench_factored_lstm.py:106-121).  `ih` is the hoisted input projection for all timesteps (an FP8 GEMM of
+// this library); h feeds the recurrent GEMM as E4M3 at the fixed scale 1/448 (the reference's convention for a
+// value bounded by 1, fly/rdna_fp8_factored_lstm.py:321-326); c and the emitted h are fp16.
+//
+// Decomposition: CTA (g, s) owns 128 batch rows (row group g) x 32 hidden units (slice s) = 128 gate columns.
+// Its W_hh slice (128 rows x H bytes) stays in shared memory for the whole layer, c_t stays in registers.
+// Batch rows are independent, so only the H/32 CTAs of a row group exchange data: each step every CTA
+// writes its 128 x 32 piece of h_t (E4M3) to a double-buffered global scratch and bumps its step counter;
+// the others poll the counters (bounded), pull the full 128 x H tile into 128B-swizzled shared memory and
+// run 128 x 128 x H on the tensor core (tcgen05 kind::f8f6f4, fp32 accumulators in TMEM).  The next step's ih tile
+// is prefetched by TMA while the current step computes.  The step is latency-bound (0.3 us of tensor time).
+#include <cooperative_groups.h>
+#include <cuda_fp8.h>
+
+#include "capi_internal.h"
+#include "ptx.cuh"
+
+namespace gsb {
+
+constexpr int LSTM_THREADS = 256;            // 8 warps: all load / do gate math; warp 0 lane 0 also issues TMA + MMA
+constexpr int LSTM_ROWS = 128;               // batch rows per CTA (UMMA M)
+constexpr int LSTM_HS = 32;                  // hidden units per CTA
+constexpr int LSTM_NCOL = 4 * LSTM_HS;       // gate columns per CTA (UMMA N)
+constexpr int LSTM_MAX_KB = 4;               // H <= 512
+constexpr int LSTM_KB_BYTES = LSTM_ROWS * 128;                 // one 128-byte K block of a 128-row operand tile
+constexpr int LSTM_IH_BYTES = LSTM_ROWS * LSTM_NCOL * 2;       // 32 KiB: four 128 x 32 fp16 boxes
+constexpr int LSTM_SMEM_W = 0;
+constexpr int LSTM_SMEM_H = LSTM_SMEM_W + LSTM_MAX_KB * LSTM_KB_BYTES;
+constexpr int LSTM_SMEM_IH = LSTM_SMEM_H + LSTM_MAX_KB * LSTM_KB_BYTES;
+constexpr int LSTM_SMEM_SC = LSTM_SMEM_IH + 2 * LSTM_IH_BYTES;   // 128 scales + 128 biases (fp32)
+constexpr int LSTM_SMEM_BAR = LSTM_SMEM_SC + 1024;
+constexpr int LSTM_SMEM_USED = LSTM_SMEM_BAR + 128;
+constexpr int LSTM_SMEM_BYTES = LSTM_SMEM_USED + 1024;           // + alignment slack
+static_assert(LSTM_SMEM_BYTES > 116 * 1024, "one CTA per SM");
+
+struct LstmParams {
+  int T, B, H;
+  int reverse;                 // 1: iterate t = T-1 .. 0
+  int k_blocks;                // ceil(H / 128)
+  int slices;                  // H / 32
+  const float* s_hh;           // [4H] per-channel scales of W_hh
+  const float* bias;           // [4H] or null (b_ih + b_hh)
+  const uint8_t* h0;           // [B, H] E4M3 at scale 1/448, or null (zeros)
+  const __half* c0;            // [B, H] or null (zeros)
+  __half* h_out;               // [T*B, H] fp16, row = t*B + b, or null
+  uint8_t* h8_out;             // [T*B, H] E4M3 at scale 1/448 (input of the next layer's projection), or null
+  __half* c_last;              // [B, H] final cell state, or null
+  uint8_t* hbuf;               // scratch: [2][B][H] E4M3, h of the previous / current step
+  unsigned int* flags;         // scratch: [row groups][slices] step counters, zero at launch
+};
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ float tanh_f(float x) {
+  const float e = __expf(-2.0f * fabsf(x));                   // in (0, 1]: no overflow
+  return copysignf(__fdividef(1.0f - e, 1.0f + e), x);
+}
+
+__global__ void __launch_bounds__(LSTM_THREADS, 1)
+lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_ih,
+                      const LstmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* w_s = smem + LSTM_SMEM_W;
+  uint8_t* h_s = smem + LSTM_SMEM_H;
+  uint8_t* ih_s = smem + LSTM_SMEM_IH;
+  float* sc_s = reinterpret_cast<float*>(smem + LSTM_SMEM_SC);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LSTM_SMEM_BAR);
+  uint64_t* w_full = bars;               // W slice landed
+  uint64_t* ih_full = bars + 1;          // [2] ih tile of a step landed
+  uint64_t* mma_done = bars + 3;         // accumulator of this step complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = blockIdx.x / p.slices;        // row group
+  const int slc = blockIdx.x % p.slices;        // hidden slice
+  const int row0 = grp * LSTM_ROWS;
+  const int hid0 = slc * LSTM_HS;
+  const int H = p.H, B = p.B;
+
+  if (tid == 0) {
+    mbar_init(w_full, 1); mbar_init(&ih_full[0], 1); mbar_init(&ih_full[1], 1); mbar_init(mma_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_w); prefetch_tmap(&tm_ih);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, LSTM_NCOL); tmem_relinquish(); }
+  // per-channel scale (with the 1/448 of h folded in) and bias of this CTA's 128 gate columns
+  if (tid < LSTM_NCOL) {
+    const int n = (tid >> 5) * H + hid0 + (tid & 31);
+    sc_s[tid] = __ldg(p.s_hh + n) * (1.0f / 448.0f);
+    sc_s[LSTM_NCOL + tid] = p.bias ? __ldg(p.bias + n) : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto step_t = [&](int s) { return p.reverse ? p.T - 1 - s : s; };
+  auto issue_ih = [&](int s) {   // one thread: TMA the four gate boxes of step s into buffer s & 1
+    uint8_t* dst = ih_s + (s & 1) * LSTM_IH_BYTES;
+    mbar_arrive_expect_tx(&ih_full[s & 1], LSTM_IH_BYTES);
+    const int r = step_t(s) * B + row0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) tma_load_2d(dst + g * (LSTM_ROWS * LSTM_HS * 2), &tm_ih, &ih_full[s & 1], g * H + hid0, r);
+  };
+  if (tid == 0) {
+    mbar_arrive_expect_tx(w_full, p.k_blocks * LSTM_KB_BYTES);
+    for (int kb = 0; kb < p.k_blocks; ++kb)
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        tma_load_2d(w_s + kb * LSTM_KB_BYTES + g * (LSTM_HS * 128), &tm_w, w_full, kb * 128, g * H + hid0);
+    issue_ih(0);
+    if (p.T > 1) issue_ih(1);
+  }
+
+  // this thread's part of the tile: row (TMEM lane) q*32 + lane, hidden units half*16 .. +15 of the slice
+  const int q = warp & 3, half = warp >> 2;
+  const int r_loc = q * 32 + lane;
+  const int row = row0 + r_loc;
+  const bool row_ok = row < B;
+  float c[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    c[j] = (p.c0 && row_ok) ? __half2float(p.c0[(long long)row * H + hid0 + half * 16 + j]) : 0.f;
+
+  bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10);
+  const int chunks_per_row = p.k_blocks * 8;                 // 16-byte pieces of a (zero-padded) h row
+  unsigned int* my_flags = p.flags + grp * p.slices;
+
+  for (int s = 0; s < p.T; ++s) {
+    // ---- 1. wait until every slice of this row group has published h_{s-1} -----------------------------
+    const uint8_t* h_prev = (s == 0) ? p.h0 : p.hbuf + (size_t)((s + 1) & 1) * B * H;
+    if (s > 0 && tid < p.slices) {
+      long long t0 = clock64();
+      const long long budget = g_status[2] ? (long long)g_status[2] : kDefaultSpinBudget;
+      while (ld_acquire_gpu(my_flags + tid) < (unsigned int)s) {
+        if (*abort_flag) break;
+        if (clock64() - t0 > budget) {
+          *abort_flag = 1;
+          atomicOr(&g_status[0], ST_TIMEOUT_LSTM);
+          g_status[1] = (unsigned int)s;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (*abort_flag || !ok) break;
+    // ---- 2. pull the 128 x H tile of h_{s-1} into the swizzled K-major operand layout ------------------
+    for (int id = tid; id < LSTM_ROWS * chunks_per_row; id += LSTM_THREADS) {
+      const int r = id / chunks_per_row, cc = id % chunks_per_row;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h_prev && row0 + r < B && cc * 16 < H) v = __ldcg(reinterpret_cast<const uint4*>(h_prev + (size_t)(row0 + r) * H + cc * 16));
+      const int kb = cc >> 3, ck = cc & 7;
+      *reinterpret_cast<uint4*>(h_s + kb * LSTM_KB_BYTES + r * 128 + ((ck ^ (r & 7)) << 4)) = v;
+    }
+    fence_proxy_async_smem();
+    __syncthreads();
+    // ---- 3. gates += h . W^T on the tensor core ----------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after();
+      constexpr uint32_t idesc = umma_idesc(1, 0, 0, LSTM_ROWS, LSTM_NCOL);
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(h_s + kb * LSTM_KB_BYTES));
+        const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(w_s + kb * LSTM_KB_BYTES));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f8(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+      }
+      umma_commit(mma_done);
+    }
+    // ---- 4. gate math on this thread's row ---------------------------------------------------------------
+    ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20) &&
+         mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      uint32_t acc[4][16];
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * LSTM_HS + half * 16, acc[g]);
+      tmem_ld_wait();
+      const uint8_t* ihb = ih_s + (s & 1) * LSTM_IH_BYTES;
+      float hv[16];
+#pragma unroll
+      for (int j0 = 0; j0 < 16; j0 += 8) {
+        float pre[4][8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          // 8 fp16 of gate g: one 16-byte piece of this row in the 64-byte-swizzled box
+          const int piece = half * 2 + (j0 >> 3);
+          const uint4 raw = *reinterpret_cast<const uint4*>(ihb + g * (LSTM_ROWS * LSTM_HS * 2) + r_loc * 64 +
+                                                            ((piece ^ ((r_loc >> 1) & 3)) << 4));
+          const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h2[i]);
+            const int col = g * LSTM_HS + half * 16 + j0 + 2 * i;
+            pre[g][2 * i] = fmaf(__uint_as_float(acc[g][j0 + 2 * i]), sc_s[col], f.x + sc_s[LSTM_NCOL + col]);
+            pre[g][2 * i + 1] = fmaf(__uint_as_float(acc[g][j0 + 2 * i + 1]), sc_s[col + 1], f.y + sc_s[LSTM_NCOL + col + 1]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float ig = sigmoid_f(pre[0][i]), fg = sigmoid_f(pre[1][i]), gg = tanh_f(pre[2][i]), og = sigmoid_f(pre[3][i]);
+          const float cn = fmaf(fg, c[j0 + i], ig * gg);
+          hv[j0 + i] = og * tanh_f(cn);
+          c[j0 + i] = __half2float(__float2half_rn(cn));        // the cell state is carried in fp16
+        }
+      }
+      if (row_ok) {
+        uint32_t w8[4], w16[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i] * 448.f, hv[4 * i + 1] * 448.f), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i + 2] * 448.f, hv[4 * i + 3] * 448.f), __NV_SATFINITE, __NV_E4M3);
+          w8[i] = lo | (hi << 16);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w16[i] = pack_half2(hv[2 * i], hv[2 * i + 1]);
+        const size_t off = (size_t)row * H + hid0 + half * 16;
+        *reinterpret_cast<uint4*>(p.hbuf + (size_t)(s & 1) * B * H + off) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        const size_t toff = (size_t)step_t(s) * B * H + off;
+        if (p.h8_out) *reinterpret_cast<uint4*>(p.h8_out + toff) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        if (p.h_out) {
+          *reinterpret_cast<uint4*>(p.h_out + toff) = make_uint4(w16[0], w16[1], w16[2], w16[3]);
+          *reinterpret_cast<uint4*>(p.h_out + toff + 8) = make_uint4(w16[4], w16[5], w16[6], w16[7]);
+        }
+      }
+      __threadfence();                 // this thread's piece of h_s is visible device-wide before the counter moves
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (!ok || *abort_flag) break;
+    // ---- 5. publish, and prefetch the ih tile two steps ahead into the buffer just consumed --------------
+    if (tid == 0) {
+      st_release_gpu(my_flags + slc, (unsigned int)(s + 1));
+      if (s + 2 < p.T) issue_ih(s + 2);
+    }
+  }
+
+  if (p.c_last && row_ok) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) p.c_last[(long long)row * H + hid0 + half * 16 + j] = __float2half_rn(c[j]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, LSTM_NCOL); }
+}
+
+// ---- host -------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFnL)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+size_t lstm_scratch_bytes(long long B, int H) {
+  const size_t hbuf = ((size_t)2 * B * H + 255) & ~(size_t)255;
+  const size_t flags = (size_t)((B + LSTM_ROWS - 1) / LSTM_ROWS) * (H / LSTM_HS) * sizeof(unsigned int);
+  return hbuf + ((flags + 255) & ~(size_t)255);
+}
+
+int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (a.T == 0 || a.B == 0) return GSB200_OK;
+  if (a.T < 0 || a.B < 0 || a.H <= 0 || a.H % LSTM_HS != 0 || a.H > LSTM_MAX_KB * 128) return GSB200_ERR_UNSUPPORTED;
+  if (!a.ih || !a.w_hh || !a.s_hh || !scratch) return GSB200_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a.ih) & 15) || (reinterpret_cast<uintptr_t>(a.w_hh) & 15) ||
+      (reinterpret_cast<uintptr_t>(scratch) & 255))
+    return GSB200_ERR_BAD_ARG;
+  if (a.ld_ih < 4 * a.H || a.ld_ih % 8 != 0 || a.H % 16 != 0) return GSB200_ERR_BAD_ARG;
+  if ((a.h_out && (reinterpret_cast<uintptr_t>(a.h_out) & 15)) || (a.h8_out && (reinterpret_cast<uintptr_t>(a.h8_out) & 15)) ||
+      (a.h0 && (reinterpret_cast<uintptr_t>(a.h0) & 15)))
+    return GSB200_ERR_BAD_ARG;
+  if ((long long)a.T * a.B > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
+  if (scratch_bytes < lstm_scratch_bytes(a.B, a.H)) return GSB200_ERR_BAD_ARG;
+  int32_t rc = ensure_device();
+  if (rc != GSB200_OK) return rc;
+
+  const int groups = (int)((a.B + LSTM_ROWS - 1) / LSTM_ROWS);
+  const int slices = a.H / LSTM_HS;
+  const int grid = groups * slices;
+  if (grid > sm_count()) return GSB200_ERR_UNSUPPORTED;     // every CTA must be resident: they wait on one another
+
+  static bool attr_done[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(lstm_recurrent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LSTM_SMEM_BYTES);
+    if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(lstm)");
+    attr_done[dev] = true;
+  }
+
+  LstmParams p{};
+  p.T = (int)a.T; p.B = (int)a.B; p.H = a.H; p.reverse = a.reverse ? 1 : 0;
+  p.k_blocks = (a.H + 127) / 128; p.slices = slices;
+  p.s_hh = a.s_hh; p.bias = a.bias; p.h0 = a.h0; p.c0 = a.c0;
+  p.h_out = a.h_out; p.h8_out = a.h8_out; p.c_last = a.c_last;
+  const size_t hbuf_bytes = ((size_t)2 * a.B * a.H + 255) & ~(size_t)255;
+  p.hbuf = static_cast<uint8_t*>(scratch);
+  p.flags = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(scratch) + hbuf_bytes);
+  cudaError_t e = cudaMemsetAsync(p.flags, 0, (size_t)grid * sizeof(unsigned int), st);
+  if (e != cudaSuccess) return cuda_status(e, "lstm flags memset");
+
+  void* fnp = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fnp, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return GSB200_ERR_DEVICE;
+  EncodeTiledFnL enc = reinterpret_cast<EncodeTiledFnL>(fnp);
+  CUtensorMap tw, tih;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)a.H, (cuuint64_t)4 * a.H};
+    cuuint64_t strides[1] = {(cuuint64_t)a.ld_w};
+    cuuint32_t box[2] = {128, LSTM_HS};
+    cuuint32_t es[2] = {1, 1};
+    if (a.ld_w < a.H || a.ld_w % 16 != 0) return GSB200_ERR_BAD_ARG;
+    if (enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.w_hh), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return GSB200_ERR_BAD_ARG;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)4 * a.H, (cuuint64_t)a.T * a.B};
+    cuuint64_t strides[1] = {(cuuint64_t)a.ld_ih * 2};
+    cuuint32_t box[2] = {LSTM_HS, LSTM_ROWS};
+    cuuint32_t es[2] = {1, 1};
+    if (enc(&tih, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(a.ih), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return GSB200_ERR_BAD_ARG;
+  }
+  void* args[3] = {&tw, &tih, &p};
+  e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(lstm_recurrent_kernel), dim3(grid), dim3(LSTM_THREADS), args,
+                                  LSTM_SMEM_BYTES, st);
+  return cuda_status(e, "lstm launch");
+}
+
+}  // namespace gsb

@@ -1,0 +1,49 @@
+"""Host side of the LSTM stack: per layer, the hoisted input projection (an FP8 GEMM over all T*B rows) and
+the persistent recurrent kernel; layers alternate direction and feed each other E4M3 ``h`` at scale 1/448."""
+import torch
+
+from ._lib import check, lib
+from .ops import _stream, gemm_fp8
+
+OUT_SCALE = 1.0 / 448.0
+
+
+def lstm_scratch(B, H, device):
+    """Scratch buffer (h exchange + step counters) for :func:`lstm_layer`; reusable across layers and calls
+    that do not overlap on the device."""
+    n = int(lib().gsb200_lstm_scratch_bytes(B, H))
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def lstm_layer(ih, W_hh, s_hh, T, B, bias=None, reverse=False, h0=None, c0=None, scratch=None,
+               want_h16=True, want_h8=True, want_c=False):
+    """Recurrent half of one layer.  ``ih`` fp16 ``[T*B, 4H]`` (row = t*B + b), ``W_hh`` E4M3 ``[4H, H]``.
+    Returns (h16 ``[T*B,H]`` or None, h8 ``[T*B,H]`` or None, c_last ``[B,H]`` or None)."""
+    H = W_hh.shape[1]
+    dev = ih.device
+    if scratch is None:
+        scratch = lstm_scratch(B, H, dev)
+    h16 = torch.empty((T * B, H), dtype=torch.float16, device=dev) if want_h16 else None
+    h8 = torch.empty((T * B, H), dtype=torch.float8_e4m3fn, device=dev) if want_h8 else None
+    c_last = torch.empty((B, H), dtype=torch.float16, device=dev) if want_c else None
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    check(lib().gsb200_lstm_layer_fp8(ih.data_ptr(), ih.stride(0), W_hh.data_ptr(), W_hh.stride(0), s_hh.data_ptr(),
+                                      ptr(bias), ptr(h0), ptr(c0), ptr(h16), ptr(h8), ptr(c_last), T, B, H,
+                                      1 if reverse else 0, scratch.data_ptr(), scratch.numel(), _stream()), "lstm_layer")
+    return h16, h8, c_last
+
+
+def lstm_stack(x_fp8, sx, layers, T, B, reverse_first=True, scratch=None):
+    """Stack of layers (dicts with W_ih, s_ih, b, W_hh, s_hh); even layers run reversed when ``reverse_first``.
+    ``x_fp8`` E4M3 ``[T*B, C]`` with per-row scales ``sx``.  Returns the last layer's fp16 ``h`` ``[T*B, H]``."""
+    h16 = None
+    for li, L in enumerate(layers):
+        rev = (li % 2 == 0) == reverse_first
+        ih = gemm_fp8(x_fp8, L["W_ih"], sx, L["s_ih"])                # hoisted projection for all timesteps
+        last = li == len(layers) - 1
+        h16, h8, _ = lstm_layer(ih, L["W_hh"], L["s_hh"], T, B, bias=L["b"], reverse=rev, scratch=scratch,
+                                want_h16=last, want_h8=not last)
+        if not last:
+            x_fp8 = h8
+            sx = torch.full((T * B,), OUT_SCALE, dtype=torch.float32, device=h8.device)
+    return h16

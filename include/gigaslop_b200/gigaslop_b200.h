@@ -133,6 +133,24 @@ int32_t gsb200_dual_gemm_fp8_silu_mxfp8(const uint8_t* A, int64_t lda, const uin
                                         const float* scale_b_up, int64_t M, int32_t N, int32_t K, int32_t flags,
                                         gsb200_stream_t stream);
 
+/* LSTM layer, recurrent half: T sequential steps in one persistent cooperative kernel.
+ *   gates[b,4H] = ih[t,b,:] + (h_{t-1} . W_hh^T) * (s_hh[n]/448) + bias[n]   (gate blocks i|f|g|o, each H wide)
+ *   c_t = sigmoid(f) c_{t-1} + sigmoid(i) tanh(g),  h_t = sigmoid(o) tanh(c_t)
+ * ih is the hoisted input projection of all timesteps ([T*B, 4H] fp16, row = t*B + b; produce it with
+ * gsb200_gemm_fp8_f16 over M = T*B rows).  h enters the recurrent GEMM as E4M3 at the fixed scale 1/448 (the
+ * convention of fly/rdna_fp8_factored_lstm.py:321-326); c and the emitted h are fp16.  reverse != 0 walks
+ * t = T-1..0.  Outputs (each may be null): h_out fp16 [T*B,H], h8_out E4M3 [T*B,H] (next layer's input, row
+ * scale 1/448), c_last fp16 [B,H].  The reference drives its (low-rank, hard-gate) cell as two launches per step
+ * from a graph (fly/bench_factored_lstm.py:82-85,106-121, fp8_factored_lstm_wrapper
+ * fly/export_fp8_factored_lstm.py:158-182); the full-rank sigmoid/tanh cell here is the benchmark's (config 5).
+ * Needs H % 32 == 0, H <= 512, ceil(B/128) * H/32 <= number of SMs, and caller-provided scratch of
+ * gsb200_lstm_scratch_bytes(B, H) bytes (256-byte aligned; h exchange buffer + step counters). */
+int64_t gsb200_lstm_scratch_bytes(int64_t B, int32_t H);
+int32_t gsb200_lstm_layer_fp8(const void* ih, int64_t ld_ih, const uint8_t* w_hh, int64_t ld_w, const float* s_hh,
+                              const float* bias, const uint8_t* h0, const void* c0, void* h_out, uint8_t* h8_out,
+                              void* c_last, int64_t T, int64_t B, int32_t H, int32_t reverse, void* scratch,
+                              int64_t scratch_bytes, gsb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

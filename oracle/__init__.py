@@ -32,5 +32,5 @@ from .mx import (  # noqa: F401
 )
 from .lstm import (  # noqa: F401
     factored_gemm_ref, down_proj_ref, factored_lstm_step_ref,
-    lstm_fullrank_step_ref, lstm_fullrank_layer_ref, lstm_fullrank_stack_ref,
+    lstm_fullrank_step_ref, lstm_fullrank_recurrent_ref, lstm_fullrank_layer_ref, lstm_fullrank_stack_ref,
 )

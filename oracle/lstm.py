@@ -82,23 +82,29 @@ def lstm_fullrank_step_ref(ih_t, h_fp8, c, W_hh_fp8, s_hh, bias=None):
     return h_new.to(torch.float16), _q_h(h_new), c_new.to(torch.float16)
 
 
-def lstm_fullrank_layer_ref(x_fp8, sx, W_ih_fp8, s_ih, b, W_hh_fp8, s_hh, reverse, T, B):
-    """One layer over T steps.  ``x_fp8`` E4M3 ``[T*B, C]`` with per-row scale
-    ``sx[T*B]`` (row = t*B + b); hoisted projection rounded to fp16 like the
-    device GEMM output.  Returns h fp16 ``[T*B,H]`` and its E4M3 image."""
+def lstm_fullrank_recurrent_ref(ih, W_hh_fp8, s_hh, bias, T, B, reverse, h0_fp8=None, c0=None):
+    """T steps over a given hoisted projection ``ih`` fp16 ``[T*B, 4H]`` (row = t*B + b).
+    Returns (h fp16 ``[T*B,H]``, its E4M3 image, final c fp16)."""
     H = W_hh_fp8.shape[1]
-    acc = (x_fp8.double() @ W_ih_fp8.double().t()).float()
-    ih = (acc * (sx[:, None] * s_ih[None, :]) + b[None, :]).to(torch.float16)
-    h8 = torch.zeros(B, H).to(torch.float8_e4m3fn)
-    c = torch.zeros(B, H, dtype=torch.float16)
+    h8 = h0_fp8 if h0_fp8 is not None else torch.zeros(B, H).to(torch.float8_e4m3fn)
+    c = c0 if c0 is not None else torch.zeros(B, H, dtype=torch.float16)
     out16 = torch.empty(T * B, H, dtype=torch.float16)
     out8 = torch.empty(T * B, H, dtype=torch.float8_e4m3fn)
     order = range(T - 1, -1, -1) if reverse else range(T)
     for t in order:
-        h16, h8, c = lstm_fullrank_step_ref(ih[t * B:(t + 1) * B], h8, c, W_hh_fp8, s_hh)
+        h16, h8, c = lstm_fullrank_step_ref(ih[t * B:(t + 1) * B], h8, c, W_hh_fp8, s_hh, bias)
         out16[t * B:(t + 1) * B] = h16
         out8[t * B:(t + 1) * B] = h8
     return out16, out8, c
+
+
+def lstm_fullrank_layer_ref(x_fp8, sx, W_ih_fp8, s_ih, b, W_hh_fp8, s_hh, reverse, T, B):
+    """One layer over T steps.  ``x_fp8`` E4M3 ``[T*B, C]`` with per-row scale ``sx[T*B]`` (row = t*B + b);
+    hoisted projection ``(acc * sx) * s_ih`` rounded to fp16 like the device GEMM output; the bias is added
+    inside the recurrence.  Returns h fp16 ``[T*B,H]``, its E4M3 image and the final c."""
+    acc = (x_fp8.double() @ W_ih_fp8.double().t()).float()
+    ih = (acc * sx[:, None] * s_ih[None, :]).to(torch.float16)
+    return lstm_fullrank_recurrent_ref(ih, W_hh_fp8, s_hh, b, T, B, reverse)
 
 
 def lstm_fullrank_stack_ref(x_fp8, sx, layers, T, B, reverse_first=True):

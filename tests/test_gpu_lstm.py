@@ -1,0 +1,82 @@
+"""GPU checks of the persistent LSTM recurrence and the layer stack (full-rank sigmoid/tanh cell of the
+benchmark stack: parity unpinned by the reference, the oracle is this repository's CPU statement with the
+same rounding points).  h and c live in [-1, 1] / O(1), so the gate is an absolute one."""
+import pytest
+import torch
+
+import oracle
+from util import need_lib, rand_scales
+
+pytestmark = pytest.mark.gpu
+
+
+def make_layer(gen, H, C):
+    W_ih = ((torch.rand(4 * H, C, generator=gen) * 2 - 1) * 0.1 * 448).to(torch.float8_e4m3fn)
+    W_hh = ((torch.rand(4 * H, H, generator=gen) * 2 - 1) * 0.1 * 448).to(torch.float8_e4m3fn)
+    s = torch.full((4 * H,), 1.0 / 448.0) * (0.9 + 0.2 * torch.rand(4 * H, generator=gen))
+    s2 = torch.full((4 * H,), 1.0 / 448.0) * (0.9 + 0.2 * torch.rand(4 * H, generator=gen))
+    b = 0.05 * torch.randn(4 * H, generator=gen)
+    return dict(W_ih=W_ih, s_ih=s, b=b, W_hh=W_hh, s_hh=s2)
+
+
+def cuda_layer(L):
+    return {k: v.cuda() for k, v in L.items()}
+
+
+def check_h(got, ref, what, tol=0.03, mean_tol=3e-3):
+    err = (got.float().cpu() - ref.float()).abs()
+    assert float(err.max()) <= tol, f"{what}: max abs err {float(err.max())}"
+    assert float(err.mean()) <= mean_tol, f"{what}: mean abs err {float(err.mean())}"
+
+
+@pytest.mark.parametrize("T,B,H,reverse,init", [(12, 130, 64, False, False), (40, 256, 384, True, True),
+                                                (7, 128, 32, False, True), (25, 512, 384, False, False)])
+def test_recurrent_kernel_vs_oracle(T, B, H, reverse, init):
+    g = need_lib()
+    gen = torch.Generator().manual_seed(T * 7 + B + H)
+    L = make_layer(gen, H, 64)
+    ih = (torch.randn(T * B, 4 * H, generator=gen) * 0.5).half()
+    h0 = ((torch.rand(B, H, generator=gen) * 2 - 1) * 448).to(torch.float8_e4m3fn) if init else None
+    c0 = (torch.randn(B, H, generator=gen) * 0.3).half() if init else None
+    r16, r8, rc = oracle.lstm_fullrank_recurrent_ref(ih, L["W_hh"], L["s_hh"], L["b"], T, B, reverse, h0, c0)
+    h16, h8, c_last = g.lstm_layer(ih.cuda(), L["W_hh"].cuda(), L["s_hh"].cuda(), T, B, bias=L["b"].cuda(), reverse=reverse,
+                                   h0=h0.cuda() if init else None, c0=c0.cuda() if init else None, want_c=True)
+    torch.cuda.synchronize()
+    assert g.device_status()[0] == 0
+    check_h(h16, r16, "h fp16")
+    check_h(h8.float() / 448.0, r8.float() / 448.0, "h e4m3", tol=0.05)
+    check_h(c_last, rc, "final c", tol=0.05)
+
+
+def test_two_layer_stack_vs_oracle():
+    g = need_lib()
+    gen = torch.Generator().manual_seed(55)
+    T, B, C, H = 16, 128, 64, 128
+    x = torch.randn(T * B, C, generator=gen)
+    x8, sx = oracle.fp8_quantize_per_token(x)
+    layers = [make_layer(gen, H, C), make_layer(gen, H, H)]
+    ref = oracle.lstm_fullrank_stack_ref(x8, sx, layers, T, B, reverse_first=True)
+    out = g.lstm_stack(x8.cuda(), sx.cuda(), [cuda_layer(L) for L in layers], T, B, reverse_first=True)
+    check_h(out, ref, "stack output", tol=0.05, mean_tol=5e-3)
+
+
+def test_long_sequence_drift():
+    """2000 steps at H=384 (the benchmark's layer shape, one 128-row group): the error must stay bounded."""
+    g = need_lib()
+    gen = torch.Generator().manual_seed(2000)
+    T, B, H = 2000, 128, 384
+    L = make_layer(gen, H, 64)
+    ih = (torch.randn(T * B, 4 * H, generator=gen) * 0.5).half()
+    r16, _, rc = oracle.lstm_fullrank_recurrent_ref(ih, L["W_hh"], L["s_hh"], L["b"], T, B, False)
+    h16, _, c_last = g.lstm_layer(ih.cuda(), L["W_hh"].cuda(), L["s_hh"].cuda(), T, B, bias=L["b"].cuda(), want_c=True)
+    tail = slice((T - 50) * B, T * B)
+    check_h(h16[tail], r16[tail], "h, last 50 steps", tol=0.06, mean_tol=5e-3)
+    check_h(c_last, rc, "c after 2000 steps", tol=0.1, mean_tol=8e-3)
+
+
+def test_lstm_rejects_unsupported_shapes():
+    g = need_lib()
+    ih = torch.zeros(4 * 8, 4 * 48, dtype=torch.float16, device="cuda")
+    W = torch.zeros(4 * 48, 48, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+    with pytest.raises(RuntimeError):
+        g.lstm_layer(ih, W, torch.ones(4 * 48, device="cuda"), 4, 8)        # H % 32 != 0
