@@ -33,6 +33,7 @@ SIGNATURES = {
                                           _i32, _i32, _i32, _i32, _i64, _i32, _p]),
     "gsb200_lstm_scratch_bytes": (_i64, [_i64, _i32]),
     "gsb200_lstm_layer_fp8": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _i64, _p]),
+    "gsb200_lstm_layer_fp8_static": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
     "gsb200_ptq_mxfp8": (_i32, [_p, _i32, _i64, _p, _i64, _p, _i64, _i64, _i32, _p]),
     "gsb200_dual_gemm_fp8_silu_mxfp8": (_i32, [_p, _i64, _p, _p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_dual_gemm_fp8_silu_f16": (_i32, [_p, _i64, _p, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),

@@ -142,6 +142,17 @@ int32_t gsb200_lstm_layer_fp8(const void* ih, int64_t ld_ih, const uint8_t* w_hh
   return launch_lstm_layer(a, scratch, scratch_bytes < 0 ? 0 : static_cast<size_t>(scratch_bytes), S(stream));
 }
 
+int32_t gsb200_lstm_layer_fp8_static(const void* ih, int64_t ld_ih, const uint8_t* w_hh, int64_t ld_w,
+                                     const float* s_hh, const float* bias, const uint8_t* h0, const void* c0,
+                                     void* h_out, uint8_t* h8_out, void* c_last, int64_t T, int64_t B, int32_t H,
+                                     int32_t reverse, gsb200_stream_t stream) {
+  LstmLayerArgs a{};
+  a.ih = static_cast<const __half*>(ih); a.ld_ih = ld_ih; a.w_hh = w_hh; a.ld_w = ld_w; a.s_hh = s_hh; a.bias = bias;
+  a.h0 = h0; a.c0 = static_cast<const __half*>(c0); a.h_out = static_cast<__half*>(h_out); a.h8_out = h8_out;
+  a.c_last = static_cast<__half*>(c_last); a.T = T; a.B = B; a.H = H; a.reverse = reverse;
+  return launch_lstm_layer_static(a, S(stream));
+}
+
 }  // extern "C"
 
 // ---- module hooks named by the reference's generated headers -------------------------------------------

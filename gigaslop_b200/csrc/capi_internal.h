@@ -45,6 +45,7 @@ struct LstmLayerArgs {
 };
 size_t lstm_scratch_bytes(long long B, int H);
 int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_bytes, cudaStream_t st);
+int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached)
 int32_t read_clear_status(uint32_t out[4]);

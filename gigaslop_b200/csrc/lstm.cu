@@ -356,4 +356,38 @@ int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_
   return cuda_status(e, "lstm launch");
 }
 
+// ---- variant for callers that cannot allocate device memory ------------------------------------------------
+// The h exchange buffer and the step counters live in a file-scope device array instead of caller scratch.
+// Limits: B <= 512 and H <= 512 (the benchmark layer is B = 512, H = 384).  Every GPU that loads the library
+// holds these ~513 KiB until the process exits.
+constexpr long long LSTM_STATIC_MAX_B = 512;
+constexpr int LSTM_STATIC_MAX_H = 512;
+constexpr size_t LSTM_STATIC_BYTES = (size_t)2 * LSTM_STATIC_MAX_B * LSTM_STATIC_MAX_H + 1024;
+static __device__ __align__(256) unsigned char g_lstm_static_scratch[LSTM_STATIC_BYTES];
+
+// In host code the array's name is only a stand-in for the symbol, not a device address: the address a kernel
+// can use comes from cudaGetSymbolAddress, looked up once per device with that device current.
+static void* g_lstm_static_ptr[64];
+
+int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st) {
+  if (a.T == 0 || a.B == 0) return GSB200_OK;
+  if (a.B > LSTM_STATIC_MAX_B || a.H > LSTM_STATIC_MAX_H || lstm_scratch_bytes(a.B, a.H) > LSTM_STATIC_BYTES) {
+    fprintf(stderr, "gigaslop_b200: lstm_layer_fp8_static supports B <= %lld and H <= %d (got B = %lld, H = %d); "
+                    "use gsb200_lstm_layer_fp8 with caller scratch for larger shapes\n",
+            LSTM_STATIC_MAX_B, LSTM_STATIC_MAX_H, a.B, a.H);
+    return GSB200_ERR_UNSUPPORTED;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return GSB200_ERR_DEVICE;
+  if (!g_lstm_static_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_lstm_static_scratch);
+    if (e != cudaSuccess || !ptr) return cuda_status(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(lstm scratch)");
+    g_lstm_static_ptr[dev] = ptr;
+  }
+  return launch_lstm_layer(a, g_lstm_static_ptr[dev], LSTM_STATIC_BYTES, st);
+}
+
 }  // namespace gsb

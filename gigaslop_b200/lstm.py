@@ -47,3 +47,21 @@ def lstm_stack(x_fp8, sx, layers, T, B, reverse_first=True, scratch=None):
             x_fp8 = h8
             sx = torch.full((T * B,), OUT_SCALE, dtype=torch.float32, device=h8.device)
     return h16
+
+
+def lstm_layer_static(ih, W_hh, s_hh, T, B, bias=None, reverse=False, h0=None, c0=None,
+                      want_h16=True, want_h8=True, want_c=False):
+    """:func:`lstm_layer` for hosts that must not allocate device memory inside the library call: the kernel's
+    scratch comes from a device array built into the library (B <= 512, H <= 512).  The output tensors are still
+    the caller's; pass preallocated ones through the C ABI directly if torch's allocator is off limits too.
+    Calls on one device share that array and must not overlap."""
+    H = W_hh.shape[1]
+    dev = ih.device
+    h16 = torch.empty((T * B, H), dtype=torch.float16, device=dev) if want_h16 else None
+    h8 = torch.empty((T * B, H), dtype=torch.float8_e4m3fn, device=dev) if want_h8 else None
+    c_last = torch.empty((B, H), dtype=torch.float16, device=dev) if want_c else None
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    check(lib().gsb200_lstm_layer_fp8_static(ih.data_ptr(), ih.stride(0), W_hh.data_ptr(), W_hh.stride(0),
+                                             s_hh.data_ptr(), ptr(bias), ptr(h0), ptr(c0), ptr(h16), ptr(h8),
+                                             ptr(c_last), T, B, H, 1 if reverse else 0, _stream()), "lstm_layer_static")
+    return h16, h8, c_last

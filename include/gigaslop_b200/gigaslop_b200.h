@@ -151,6 +151,26 @@ int32_t gsb200_lstm_layer_fp8(const void* ih, int64_t ld_ih, const uint8_t* w_hh
                               void* c_last, int64_t T, int64_t B, int32_t H, int32_t reverse, void* scratch,
                               int64_t scratch_bytes, gsb200_stream_t stream);
 
+/* The same LSTM layer for hosts that may not allocate device memory.  It has no counterpart in the reference.
+ * Who needs it: an inference server that hands this library a fixed arena and forbids cudaMalloc after start-up,
+ * a plugin running inside another framework's memory pool, a real-time basecalling loop where an allocation (and
+ * the implicit device synchronisation it can bring) in the middle of a run is not acceptable.  Such a caller still
+ * passes its inputs and outputs, but the kernel's scratch (the h exchange buffer and the per-CTA step counters)
+ * comes from a device array built into the library, so this call performs no cudaMalloc / cudaFree and calls no
+ * allocating library routine.
+ * Limits: B <= 512 and H <= 512; anything larger returns GSB200_ERR_UNSUPPORTED with a message on stderr (use
+ * gsb200_lstm_layer_fp8 with your own scratch instead).  Cost: about 513 KiB of device memory on every GPU that
+ * loads the library, held until the process exits.
+ * The first call on each device looks up the array's device address (with that device current); make that first
+ * call before starting any stream capture.  All calls on a device share the one array: the step counters are
+ * cleared at the start of every call, the h buffer keeps the previous call's contents (it is fully rewritten
+ * before it is read), and two calls that overlap on the GPU -- different streams, or different host threads --
+ * would race on it, so keep calls on one device in order. */
+int32_t gsb200_lstm_layer_fp8_static(const void* ih, int64_t ld_ih, const uint8_t* w_hh, int64_t ld_w,
+                                     const float* s_hh, const float* bias, const uint8_t* h0, const void* c0,
+                                     void* h_out, uint8_t* h8_out, void* c_last, int64_t T, int64_t B, int32_t H,
+                                     int32_t reverse, gsb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
