@@ -12,6 +12,7 @@ ERRORS = {-1: "bad argument", -2: "unsupported shape", -3: "device is not sm_100
 F16, F32 = 0, 1
 FLAG_DIRECT_STORE = 1
 FLAG_STREAMING = 2
+FLAG_SCALAR_SCALE_B = 4
 
 _i32, _i64, _p = C.c_int32, C.c_int64, C.c_void_p
 
@@ -31,6 +32,8 @@ SIGNATURES = {
     "gsb200_gemm_fp8_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_gemm_fp8_rotary_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i32, _i32,
                                           _i32, _i32, _i32, _i32, _i64, _i32, _p]),
+    "gsb200_gemm_f16_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _p]),
+    "gsb200_factored_lstm_step": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_lstm_scratch_bytes": (_i64, [_i64, _i32]),
     "gsb200_lstm_layer_fp8": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _i64, _p]),
     "gsb200_lstm_layer_fp8_static": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),

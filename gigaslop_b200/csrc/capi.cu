@@ -126,6 +126,23 @@ int32_t gsb200_dual_gemm_fp8_silu_mxfp8(const uint8_t* A, int64_t lda, const uin
   return launch_gemm(a, S(stream));
 }
 
+int32_t gsb200_gemm_f16_f16(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
+                            const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K, int32_t flags,
+                            gsb200_stream_t stream) {
+  // the kernel family counts K and the operand strides in bytes
+  return launch_gemm(base_args(KIND_F16, EPI_DEQUANT, A, 2 * lda, B, nullptr, 2 * ldb, C, ldc, scale_a, scale_b, nullptr,
+                               M, N, 2 * K, flags),
+                     S(stream));
+}
+
+int32_t gsb200_factored_lstm_step(uint8_t* h_fp8_out, float* c_inout, const void* hh_down, const void* up_hh,
+                                  const float* bias_hh, const void* x_down, const void* up_ih, const float* bias_ih,
+                                  int64_t B, int32_t H, int32_t K_hh, int32_t R, gsb200_stream_t stream) {
+  return launch_factored_lstm_step(h_fp8_out, c_inout, static_cast<const __half*>(hh_down),
+                                   static_cast<const __half*>(up_hh), bias_hh, static_cast<const __half*>(x_down),
+                                   static_cast<const __half*>(up_ih), bias_ih, B, H, K_hh, R, S(stream));
+}
+
 int64_t gsb200_lstm_scratch_bytes(int64_t B, int32_t H) {
   if (B <= 0 || H <= 0) return 0;
   return static_cast<int64_t>(lstm_scratch_bytes(B, H));

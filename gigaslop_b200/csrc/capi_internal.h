@@ -46,6 +46,9 @@ struct LstmLayerArgs {
 size_t lstm_scratch_bytes(long long B, int H);
 int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_bytes, cudaStream_t st);
 int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st);
+int32_t launch_factored_lstm_step(uint8_t* h_out, float* c, const __half* hh_down, const __half* up_hh,
+                                  const float* bias_hh, const __half* x_down, const __half* up_ih, const float* bias_ih,
+                                  long long B, int H, int K_hh, int R, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached)
 int32_t read_clear_status(uint32_t out[4]);

@@ -77,7 +77,7 @@ int32_t ensure_device() {
   cudaError_t errs[] = {
       set_attr<KIND_I8, EPI_I32>(),     set_attr<KIND_I8, EPI_DEQUANT>(), set_attr<KIND_I8, EPI_ROTARY>(),
       set_attr<KIND_I8, EPI_SILU>(),    set_attr<KIND_F8, EPI_DEQUANT>(), set_attr<KIND_F8, EPI_ROTARY>(),
-      set_attr<KIND_F8, EPI_SILU>(),    set_attr<KIND_F8, EPI_SILU_MX>()};
+      set_attr<KIND_F8, EPI_SILU>(),    set_attr<KIND_F8, EPI_SILU_MX>(), set_attr<KIND_F16, EPI_DEQUANT>()};
   for (cudaError_t er : errs)
     if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
   if (!encode_fn()) {
@@ -119,8 +119,10 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     if (a.N % 4 != 0 || a.ldc % 4 != 0) return GSB200_ERR_BAD_ARG;
   } else {
     if (a.N % 8 != 0 || a.ldc % 8 != 0) return GSB200_ERR_BAD_ARG;
-    if (!a.scale_a || !a.scale_b0) return GSB200_ERR_BAD_ARG;
-    if ((reinterpret_cast<uintptr_t>(a.scale_b0) & 15)) return GSB200_ERR_BAD_ARG;
+    if (a.epi != EPI_DEQUANT && (!a.scale_a || !a.scale_b0)) return GSB200_ERR_BAD_ARG;   // plain dequant: null = 1.0
+    const bool scalar_b = (a.flags & GSB200_FLAG_SCALAR_SCALE_B) != 0;
+    if (scalar_b && (a.epi != EPI_DEQUANT || !a.scale_b0)) return GSB200_ERR_BAD_ARG;
+    if (a.scale_b0 && !scalar_b && (reinterpret_cast<uintptr_t>(a.scale_b0) & 15)) return GSB200_ERR_BAD_ARG;
   }
   if (dual) {
     if (!a.B1 || !aligned16(a.B1) || !a.scale_b1 || (reinterpret_cast<uintptr_t>(a.scale_b1) & 15))
@@ -150,6 +152,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.C = a.C; p.ldc = a.ldc;
   p.out_scale = a.out_scale; p.ld_scale = a.ld_scale;
   p.scale_a = a.scale_a; p.scale_b0 = a.scale_b0; p.scale_b1 = a.scale_b1;
+  p.scale_b_scalar = (a.flags & GSB200_FLAG_SCALAR_SCALE_B) ? 1 : 0;
   p.sin_tab = a.sin_tab; p.cos_tab = a.cos_tab;
   p.seqlen = a.seqlen > 0 ? a.seqlen : 1;
   p.rot_cols = rot_cols;
@@ -207,6 +210,9 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
       case EPI_SILU_MX: e = launch_inst<KIND_F8, EPI_SILU_MX>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
+  } else if (a.kind == KIND_F16) {
+    if (a.epi != EPI_DEQUANT) return GSB200_ERR_BAD_ARG;
+    e = launch_inst<KIND_F16, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st);
   } else {
     return GSB200_ERR_BAD_ARG;
   }

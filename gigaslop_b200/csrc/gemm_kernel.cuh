@@ -38,7 +38,7 @@
 namespace gsb {
 
 enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3, EPI_SILU_MX = 4 };
-enum : int { KIND_I8 = 0, KIND_F8 = 1 };
+enum : int { KIND_I8 = 0, KIND_F8 = 1, KIND_F16 = 2 };   // F16: fp16 operands (K counted in bytes = 2 per element), f32 accumulate
 enum : int { SCHED_STREAM = 0, SCHED_WRES = 1, SCHED_ARES = 2 };
 
 constexpr int BM = 128;            // rows per tile (UMMA M)
@@ -97,6 +97,7 @@ struct GemmParams {
   const float* scale_a;        // [M]
   const float* scale_b0;       // [N]   (dual: gate)
   const float* scale_b1;       // [N]   (dual: up)
+  int scale_b_scalar;          // scale_b0 points to ONE value used for every column (scalar-quantised weights)
   const float* sin_tab;        // [seqlen_max, 32]
   const float* cos_tab;
   int seqlen;                  // runtime sequence length: angle row = (row + row_offset) % seqlen
@@ -273,6 +274,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
+      // s8 x s8 -> s32 | e4m3 x e4m3 -> f32 | f16 x f16 -> f32 (format code 0 means e4m3 resp. f16 in its kind)
       constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, BM, BN) : umma_idesc(1, 0, 0, BM, BN);
       int s = 0; uint32_t ph = 0; bool ok = true;
       if (WRES && !(p.ablate & 4)) {
@@ -304,6 +306,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t koff = (uint64_t)((k * UMMA_K) >> 4);
             if constexpr (KIND == KIND_I8) umma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+            else if constexpr (KIND == KIND_F16) umma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
             else umma_f8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
           }
           umma_commit(&empty_bar[s]);          // ring stage reusable once these MMAs retire
@@ -336,7 +339,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if constexpr (EPI != EPI_I32) {
       if (tile_coords<SCHED>(p, 0, m_blk, n_blk)) {
         const int r = m_blk * BM + q * 32 + lane;
-        if (r < p.M) sa_next = __ldg(p.scale_a + r);
+        if (r < p.M) sa_next = p.scale_a ? __ldg(p.scale_a + r) : 1.f;
       }
     }
     for (int it = 0; ok && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
@@ -373,7 +376,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           int nm, nn;
           if (tile_coords<SCHED>(p, it + 1, nm, nn) && nm != m_blk) {
             const int r = nm * BM + q * 32 + lane;
-            sa_next = (r < p.M) ? __ldg(p.scale_a + r) : 0.f;
+            sa_next = (r < p.M) ? (p.scale_a ? __ldg(p.scale_a + r) : 1.f) : 0.f;
           }
         }
         if (!WRES || it == 0) {
@@ -385,7 +388,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (n + 4 <= p.N) sbv = __ldg(reinterpret_cast<const float4*>(src + n));
           } else {
             const int n = n0 + wcol0 + lane * 4;
-            if (n + 4 <= p.N) sbv = __ldg(reinterpret_cast<const float4*>(p.scale_b0 + n));
+            if (n + 4 <= p.N) {
+              if (!p.scale_b0) sbv = make_float4(1.f, 1.f, 1.f, 1.f);                       // no per-channel scale
+              else if (p.scale_b_scalar) { const float v = __ldg(p.scale_b0); sbv = make_float4(v, v, v, v); }
+              else sbv = __ldg(reinterpret_cast<const float4*>(p.scale_b0 + n));
+            }
           }
         }
       }

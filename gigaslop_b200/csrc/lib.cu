@@ -3,4 +3,5 @@
 #include "quant.cu"
 #include "gemm.cu"
 #include "lstm.cu"
+#include "factored.cu"
 #include "capi.cu"

@@ -182,3 +182,38 @@ def dual_gemm_fp8_silu_mxfp8(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up,
         s.data_ptr(), s.stride(0), scale_a.data_ptr(), scale_b_gate.data_ptr(), scale_b_up.data_ptr(), M, N, K, flags,
         _stream()), "dual_gemm_fp8_silu_mxfp8")
     return q, s
+
+
+def gemm_f16(A, B, scale_a=None, scale_b=None, out=None, flags=0):
+    """``(A_f16 . B_f16^T) * sA * sB`` -> fp16, scales optional (compile_f16_down_proj,
+    fly/rdna_fp8_factored_gemm.py:660-843, is this with no scales and B = dn ``[R, C]``)."""
+    M, N, K = _check_ab(A, B, (torch.float16,))
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=A.device)
+    check(lib().gsb200_gemm_f16_f16(A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(), C.stride(0),
+                                    scale_a.data_ptr() if scale_a is not None else None,
+                                    scale_b.data_ptr() if scale_b is not None else None, M, N, K, flags, _stream()),
+          "gemm_f16")
+    return C
+
+
+def fp8_down_proj(x_fp8, scale_x, dn_fp8_rc, scale_dn, out=None):
+    """``x_down_f16[M,R] = (x_fp8 . dn_fp8^T) * sx[m] * s_dn`` with a single scalar weight scale
+    (compile_fp8_down_proj, fly/rdna_fp8_factored_gemm.py:442-651); ``dn`` K-major ``[R, C]``."""
+    return gemm_fp8(x_fp8, dn_fp8_rc, scale_x, scale_dn, out=out, flags=_lib.FLAG_SCALAR_SCALE_B)
+
+
+def factored_lstm_step(h_fp8_out, c_inout, hh_down, up_hh, bias_hh, x_down, up_ih, bias_ih):
+    """One step of the low-rank hard-gate LSTM cell; argument order of fp8_factored_lstm_wrapper
+    (fly/export_fp8_factored_lstm.py:158-182).  ``up_hh`` ``[4H, K_hh]`` and ``up_ih`` ``[4H, R]`` fp16 K-major."""
+    _need_cuda(h_fp8_out, c_inout, hh_down, up_hh, x_down, up_ih)
+    B, K_hh = hh_down.shape
+    H = up_hh.shape[0] // 4
+    R = x_down.shape[1]
+    for t in (hh_down, up_hh, x_down, up_ih, c_inout, h_fp8_out):
+        if not t.is_contiguous():
+            raise ValueError("factored_lstm_step takes contiguous tensors")
+    check(lib().gsb200_factored_lstm_step(h_fp8_out.data_ptr(), c_inout.data_ptr(), hh_down.data_ptr(), up_hh.data_ptr(),
+                                          bias_hh.data_ptr() if bias_hh is not None else None, x_down.data_ptr(),
+                                          up_ih.data_ptr(), bias_ih.data_ptr() if bias_ih is not None else None,
+                                          B, H, K_hh, R, _stream()), "factored_lstm_step")
+    return h_fp8_out, c_inout

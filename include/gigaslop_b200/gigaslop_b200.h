@@ -40,6 +40,7 @@ extern "C" {
 #define GSB200_FLAG_DIRECT_STORE 1   /* diagnostic: epilogue stores straight from registers (no smem + TMA store) */
 #define GSB200_FLAG_ABLATE_STORES 0x100   /* timing ablation, output is NOT written: skip the epilogue's stores */
 #define GSB200_FLAG_ABLATE_EPILOGUE 0x200 /* timing ablation, output is NOT written: skip the epilogue body */
+#define GSB200_FLAG_SCALAR_SCALE_B 4  /* plain dequant GEMMs: scale_b points to ONE fp32 used for every output column */
 #define GSB200_FLAG_STREAMING 2      /* diagnostic: stream both operands even when the weight slice could stay resident */
 
 typedef struct CUstream_st* gsb200_stream_t; /* == cudaStream_t */
@@ -114,6 +115,29 @@ int32_t gsb200_dual_gemm_fp8_silu_f16(const uint8_t* A, int64_t lda, const uint8
                                       int64_t ldb, void* C, int64_t ldc, const float* scale_a,
                                       const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,
                                       int32_t K, int32_t flags, gsb200_stream_t stream);
+
+/* Low-rank ("factored") projections of the reference's LSTM.  Weights K-major [N,K] (see gigaslop_b200.layout for
+ * the conversion from the RDNA pre-shuffle).
+ *   fp8_down_proj_wrapper (fly/export_fp8_down_proj.py:144-155, kernel fly/rdna_fp8_factored_gemm.py:442-651):
+ *       x_down_f16[M,R] = (x_fp8 . dn_fp8^T) * sx[m] * s_dn   ==  gsb200_gemm_fp8_f16(..., scale_b = &s_dn,
+ *       flags = GSB200_FLAG_SCALAR_SCALE_B)
+ *   f16_down_proj_wrapper (fly/export_f16_down_proj.py:128-137, kernel fly/rdna_fp8_factored_gemm.py:660-843):
+ *       x_down_f16[M,R] = x_f16 . dn_f16^T                      ==  gsb200_gemm_f16_f16 with null scales
+ * gsb200_gemm_f16_f16: C_f16 = (A_f16 . B_f16^T)_f32 * sA[m] * sB[n], either scale pointer may be null (= 1).
+ * K % 8 == 0, lda / ldb (elements) % 8 == 0. */
+int32_t gsb200_gemm_f16_f16(const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
+                            const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K,
+                            int32_t flags, gsb200_stream_t stream);
+
+/* One step of the reference's low-rank LSTM cell (compile_fp8_factored_lstm, fly/rdna_fp8_factored_lstm.py:88-351;
+ * fp8_factored_lstm_wrapper, fly/export_fp8_factored_lstm.py:158-182 -- same argument order):
+ *   gates[B,4H] = hh_down[B,K_hh] . up_hh[4H,K_hh]^T + x_down[B,R] . up_ih[4H,R]^T + bias_hh + bias_ih   (f16 operands)
+ *   i,f,o = clamp(0.2 x + 0.5, 0, 1), g = clamp(x, -1, 1) (gate blocks i|f|g|o of H columns);
+ *   c = f c + i g (fp32, in place);  h = o tanh(c) -> E4M3 at the fixed scale 1/448.
+ * H % 32 == 0; K_hh, R multiples of 64 with K_hh + R <= 384; any B (the reference wants B % 32 == 0). */
+int32_t gsb200_factored_lstm_step(uint8_t* h_fp8_out, float* c_inout, const void* hh_down, const void* up_hh,
+                                  const float* bias_hh, const void* x_down, const void* up_ih, const float* bias_ih,
+                                  int64_t B, int32_t H, int32_t K_hh, int32_t R, gsb200_stream_t stream);
 
 /* MXFP8 (OCP microscaling): E4M3 elements with one E8M0 scale (value 2^(byte-127)) per 32 consecutive
  * elements; byte = clamp(biased fp32 exponent of the block maximum - 8, 0, 254), elements are

@@ -141,7 +141,7 @@ def main(ref):
                                 ih=fg_ns["ref_rows"](xr, dict(dn=dn, up=up, bias=bias)).numpy())
 
     # ---- 8. factored LSTM step (reference make_inputs + reference, shrunk) -
-    Hh, Kh, Rr = 128, 32, 32
+    Hh, Kh, Rr = 128, 64, 64
     l_glob = dict(H=Hh, K_HH=Kh, R=Rr, FH=4 * Hh, OUT_SCALE=1.0 / 448.0,
                   fp8_quantize_scalar=s_ns["fp8_quantize_scalar"],
                   preshuffle_b_fp8=f_ns["preshuffle_b_fp8"],
