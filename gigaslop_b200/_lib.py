@@ -34,6 +34,10 @@ SIGNATURES = {
                                           _i32, _i32, _i32, _i32, _i64, _i32, _p]),
     "gsb200_gemm_f16_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_factored_lstm_step": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
+    "gsb200_mx_tiled_scale_bytes": (_i64, [_i64, _i32]),
+    "gsb200_mx_scales_to_tiled": (_i32, [_p, _i64, _i64, _i32, _p, _p]),
+    "gsb200_gemm_mxfp8_f16": (_i32, [_p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i32, _i32, _p]),
+    "gsb200_dual_gemm_mxfp8_silu_f16": (_i32, [_p, _i64, _p, _p, _p, _i64, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
     "gsb200_lstm_scratch_bytes": (_i64, [_i64, _i32]),
     "gsb200_lstm_layer_fp8": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _i64, _p]),
     "gsb200_lstm_layer_fp8_static": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),

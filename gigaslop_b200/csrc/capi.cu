@@ -143,6 +143,30 @@ int32_t gsb200_factored_lstm_step(uint8_t* h_fp8_out, float* c_inout, const void
                                    static_cast<const __half*>(up_ih), bias_ih, B, H, K_hh, R, S(stream));
 }
 
+int64_t gsb200_mx_tiled_scale_bytes(int64_t rows, int32_t K) {
+  if (rows <= 0 || K <= 0 || K % 128 != 0) return 0;
+  return static_cast<int64_t>(mx_tiled_scale_bytes(rows, K));
+}
+
+int32_t gsb200_mx_scales_to_tiled(const uint8_t* scales, int64_t ld, int64_t rows, int32_t K, uint8_t* tiled,
+                                  gsb200_stream_t stream) {
+  return launch_mx_scales_to_tiled(scales, ld, rows, K, tiled, S(stream));
+}
+
+int32_t gsb200_gemm_mxfp8_f16(const uint8_t* A, int64_t lda, const uint8_t* sfa_tiled, const uint8_t* B, int64_t ldb,
+                              const uint8_t* sfb_tiled, void* C, int64_t ldc, int64_t M, int32_t N, int32_t K,
+                              gsb200_stream_t stream) {
+  return launch_mx_gemm(false, A, lda, sfa_tiled, B, nullptr, ldb, sfb_tiled, nullptr, C, ldc, M, N, K, S(stream));
+}
+
+int32_t gsb200_dual_gemm_mxfp8_silu_f16(const uint8_t* A, int64_t lda, const uint8_t* sfa_tiled, const uint8_t* B_gate,
+                                        const uint8_t* B_up, int64_t ldb, const uint8_t* sfb_gate_tiled,
+                                        const uint8_t* sfb_up_tiled, void* C, int64_t ldc, int64_t M, int32_t N,
+                                        int32_t K, gsb200_stream_t stream) {
+  return launch_mx_gemm(true, A, lda, sfa_tiled, B_gate, B_up, ldb, sfb_gate_tiled, sfb_up_tiled, C, ldc, M, N, K,
+                        S(stream));
+}
+
 int64_t gsb200_lstm_scratch_bytes(int64_t B, int32_t H) {
   if (B <= 0 || H <= 0) return 0;
   return static_cast<int64_t>(lstm_scratch_bytes(B, H));

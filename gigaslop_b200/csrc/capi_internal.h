@@ -49,6 +49,11 @@ int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st);
 int32_t launch_factored_lstm_step(uint8_t* h_out, float* c, const __half* hh_down, const __half* up_hh,
                                   const float* bias_hh, const __half* x_down, const __half* up_ih, const float* bias_ih,
                                   long long B, int H, int K_hh, int R, cudaStream_t st);
+size_t mx_tiled_scale_bytes(long long rows, int K);
+int32_t launch_mx_scales_to_tiled(const uint8_t* src, long long ld, long long rows, int K, uint8_t* dst, cudaStream_t st);
+int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t* sfa, const uint8_t* B0,
+                       const uint8_t* B1, long long ldb, const uint8_t* sfb0, const uint8_t* sfb1, void* C,
+                       long long ldc, long long M, int N, int K, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached)
 int32_t read_clear_status(uint32_t out[4]);

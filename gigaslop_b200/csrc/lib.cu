@@ -4,4 +4,5 @@
 #include "gemm.cu"
 #include "lstm.cu"
 #include "factored.cu"
+#include "mx_gemm.cu"
 #include "capi.cu"

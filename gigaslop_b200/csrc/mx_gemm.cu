@@ -1,0 +1,322 @@
+// Block-scaled MXFP8 GEMMs on tcgen05 kind::mxf8f6f4: both operands are E4M3 with one E8M0 scale per 32
+// consecutive K elements (per row of A, per row of W), fp32 accumulation in TMEM, fp16 output.
+//
+//   plain : C[M,N]      = A . W^T                      (e.g. the down-projection fed by an MXFP8 activation)
+//   dual  : C[M,N]      = silu(A . Wg^T) * (A . Wu^T)  (SwiGLU)
+//
+// Scale factors travel in the 128 x 4 tile order the tensor core consumes: for a matrix with R rows and
+// K columns the byte for (row r, 32-block b) lives at
+//     ((r / 128) * (K / 128) + b / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + (b % 4)
+// (rows padded to 128, K a multiple of 128).  One such 512-byte tile is exactly what one 128-byte K stage of
+// 128 rows needs; it is bulk-copied into shared memory next to the operand tiles and moved to TMEM with
+// tcgen05.cp.32x128b.warpx4 by the MMA thread, in order with the MMAs that read it.  The instruction
+// descriptor's scale ids select the byte (the 32-block inside the stage) for each K = 32 MMA.
+//
+// Tiles are 128 rows x 128 accumulator columns; two accumulator stages (256 TMEM columns) overlap the
+// epilogue with the next tile; the scale factors use 12 further columns.  The dual form issues two N = 64
+// MMAs per K step (gate -> columns 0..63, up -> 64..127) so each keeps its own scale tile.
+#include "capi_internal.h"
+#include "ptx.cuh"
+
+namespace gsb {
+
+constexpr int MX_BM = 128, MX_BN = 128, MX_BK = 128;
+constexpr int MX_STAGES = 5;
+constexpr int MX_A_BYTES = MX_BM * MX_BK;            // 16 KiB
+constexpr int MX_B_BYTES = MX_BN * MX_BK;            // 16 KiB
+constexpr int MX_SF_BYTES = 512;
+constexpr int MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 4 * MX_SF_BYTES;   // A | B | SFA | SFB0 | SFB1 | pad  = 34 KiB
+constexpr int MX_EPI_WARPS = 8, MX_FRONT_WARPS = 4;
+constexpr int MX_THREADS = 32 * (MX_EPI_WARPS + MX_FRONT_WARPS);
+constexpr int MX_OUT_BUF = 2048, MX_OUT_BUFS = 2;
+constexpr int MX_SMEM_OUT = MX_STAGES * MX_STAGE_BYTES;
+constexpr int MX_SMEM_BAR = MX_SMEM_OUT + MX_EPI_WARPS * MX_OUT_BUFS * MX_OUT_BUF;
+constexpr int MX_SMEM_BYTES = MX_SMEM_BAR + 256 + 1024;
+constexpr int MX_TMEM_COLS = 512;                    // power of two >= 256 + 12
+constexpr int MX_SF_COL = 256;                       // SFA at +0, SFB0 at +4, SFB1 at +8
+static_assert(MX_SMEM_BYTES > 116 * 1024 && MX_SMEM_BYTES <= 227 * 1024, "one CTA per SM");
+
+struct MxParams {
+  int M, N, K;
+  int m_blocks, n_blocks, k_blocks;
+  const uint8_t* sfa; const uint8_t* sfb0; const uint8_t* sfb1;    // tiled scale factors
+};
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Shared-memory descriptor of one scale tile for tcgen05.cp: 32 rows of 16 bytes, unswizzled K-major, 8-row
+// groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                // descriptor version
+  return d;                              // layout type 0: no swizzle
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(MX_THREADS, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
+               const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_c, const MxParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* out_base = smem + MX_SMEM_OUT;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + MX_SMEM_BAR);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + MX_STAGES;
+  uint64_t* acc_full = bars + 2 * MX_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int OUT_COLS = DUAL ? MX_BN / 2 : MX_BN;          // output columns per tile
+  const long long num_tiles = (long long)p.m_blocks * p.n_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < MX_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], MX_EPI_WARPS); }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1); prefetch_tmap(&tm_c);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, MX_TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0; bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m_blk = (int)(t / p.n_blocks), n_blk = (int)(t % p.n_blocks);
+        const int m0 = m_blk * MX_BM, n0 = n_blk * OUT_COLS;
+        const int nb128 = n0 / 128;                              // scale tile row block of W
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, 0x600 | s)) { ok = false; break; }
+          uint8_t* st = smem + s * MX_STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], MX_A_BYTES + MX_B_BYTES + (DUAL ? 3 : 2) * MX_SF_BYTES);
+          tma_load_2d(st, &tm_a, &full_bar[s], kb * MX_BK, m0);
+          if constexpr (DUAL) {
+            tma_load_2d(st + MX_A_BYTES, &tm_b0, &full_bar[s], kb * MX_BK, n0);                    // 64 gate rows
+            tma_load_2d(st + MX_A_BYTES + MX_B_BYTES / 2, &tm_b1, &full_bar[s], kb * MX_BK, n0);   // 64 up rows
+          } else {
+            tma_load_2d(st + MX_A_BYTES, &tm_b0, &full_bar[s], kb * MX_BK, n0);
+          }
+          uint8_t* sf = st + MX_A_BYTES + MX_B_BYTES;
+          bulk_load(sf, p.sfa + ((size_t)m_blk * p.k_blocks + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[s]);
+          bulk_load(sf + MX_SF_BYTES, p.sfb0 + ((size_t)nb128 * p.k_blocks + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[s]);
+          if constexpr (DUAL)
+            bulk_load(sf + 2 * MX_SF_BYTES, p.sfb1 + ((size_t)nb128 * p.k_blocks + kb) * MX_SF_BYTES, MX_SF_BYTES, &full_bar[s]);
+          if (++s == MX_STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) { long long t0 = clock64(); while (clock64() - t0 < 2000000) { } }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0; bool ok = true; int it = 0;
+      const uint32_t sf_tmem = tmem_base + MX_SF_COL;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
+        const int n0 = (int)(t % p.n_blocks) * OUT_COLS;
+        const uint32_t sfb_sub = (uint32_t)((n0 % 128) / 32);      // dual: which 64-row half of the scale tile
+        if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, 0x700 | as)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * MX_BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, 0x800 | s)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + s * MX_STAGE_BYTES);
+          const uint32_t sf = st + MX_A_BYTES + MX_B_BYTES;
+          tmem_cp_32x128b_warpx4(sf_tmem, sf_smem_desc(sf));
+          tmem_cp_32x128b_warpx4(sf_tmem + 4, sf_smem_desc(sf + MX_SF_BYTES));
+          if constexpr (DUAL) tmem_cp_32x128b_warpx4(sf_tmem + 8, sf_smem_desc(sf + 2 * MX_SF_BYTES));
+          const uint64_t a_desc = umma_smem_desc_sw128(st);
+          const uint64_t b_desc = umma_smem_desc_sw128(st + MX_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t acc = (kb | k) != 0;
+            if constexpr (DUAL) {
+              const uint64_t bu_desc = umma_smem_desc_sw128(st + MX_A_BYTES + MX_B_BYTES / 2);
+              const uint32_t idesc = umma_idesc_mx(0, 0, MX_BM, 64, k, k);
+              umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sf_tmem, sf_tmem + 4 + sfb_sub, acc);
+              umma_mxf8(d_tmem + 64, a_desc + 2 * k, bu_desc + 2 * k, idesc, sf_tmem, sf_tmem + 8 + sfb_sub, acc);
+            } else {
+              const uint32_t idesc = umma_idesc_mx(0, 0, MX_BM, MX_BN, k, k);
+              umma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sf_tmem, sf_tmem + 4, acc);
+            }
+          }
+          umma_commit(&empty_bar[s]);
+          if (++s == MX_STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&acc_full[as]);
+      }
+    }
+  } else if (warp >= MX_FRONT_WARPS) {
+    const int e = warp - MX_FRONT_WARPS, q = warp & 3, half = e >> 2;
+    uint8_t* out_buf = out_base + e * MX_OUT_BUFS * MX_OUT_BUF;
+    uint32_t stg_off[4];
+#pragma unroll
+    for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
+    int it = 0, obuf = 0; bool ok = true;
+    for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
+      const int m0 = (int)(t / p.n_blocks) * MX_BM, n0 = (int)(t % p.n_blocks) * OUT_COLS;
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, 0x900 | as))) { ok = false; break; }
+      tc_fence_after();
+      const int row_base = m0 + q * 32;
+      const uint32_t t_row = tmem_base + as * MX_BN + ((uint32_t)(q * 32) << 16);
+      if (row_base < p.M) {
+        auto emit_box = [&](int n, const uint32_t (&w)[16]) {      // 32 fp16 of this thread's row -> one staged box -> TMA store
+          if (lane == 0) tma_store_wait_read<MX_OUT_BUFS - 1>();
+          __syncwarp();
+          uint8_t* buf = out_buf + obuf * MX_OUT_BUF;
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc)
+            *reinterpret_cast<uint4*>(buf + stg_off[pc]) = make_uint4(w[4 * pc], w[4 * pc + 1], w[4 * pc + 2], w[4 * pc + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) { tma_store_2d(&tm_c, buf, n, row_base); tma_store_commit(); }
+          obuf ^= 1;
+        };
+        if constexpr (DUAL) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(t_row + half * 32, g);
+          tmem_ld_32x32b_x32(t_row + 64 + half * 32, u);
+          tmem_ld_wait();
+          const int n = n0 + half * 32;
+          if (n < p.N) {
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+              w[j] = pack_half2(__fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]),
+                                __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]));
+            }
+            emit_box(n, w);
+          }
+        } else {
+          uint32_t v[2][32];
+          tmem_ld_32x32b_x32(t_row + half * 64, v[0]);
+          tmem_ld_32x32b_x32(t_row + half * 64 + 32, v[1]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int n = n0 + half * 64 + h * 32;
+            if (n < p.N) {
+              uint32_t w[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) w[j] = pack_half2(__uint_as_float(v[h][2 * j]), __uint_as_float(v[h][2 * j + 1]));
+              emit_box(n, w);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[as]);
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, MX_TMEM_COLS); }
+}
+
+// ---- row-major [rows, K/32] scales -> the 128 x 4 tile order (one thread per output byte) -------------------
+__global__ void mx_scales_to_tiled_kernel(const uint8_t* __restrict__ src, long long ld, long long rows, int k32,
+                                          uint8_t* __restrict__ dst, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int kt = k32 / 4;                                  // 128-wide K tiles
+  const long long tile = i / 512; const int in = (int)(i % 512);
+  const long long rb = tile / kt; const int kb = (int)(tile % kt);
+  const int r = (in / 16) + 32 * ((in % 16) / 4);          // row inside the 128-row block
+  const int b = kb * 4 + (in % 4);
+  const long long row = rb * 128 + r;
+  dst[i] = (row < rows) ? src[row * ld + b] : (uint8_t)127;   // padding rows: scale 1.0 on zero data
+}
+
+typedef CUresult (*EncodeTiledFnM)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+size_t mx_tiled_scale_bytes(long long rows, int K) {
+  return (size_t)((rows + 127) / 128) * (size_t)(K / 128) * 512;
+}
+
+int32_t launch_mx_scales_to_tiled(const uint8_t* src, long long ld, long long rows, int K, uint8_t* dst, cudaStream_t st) {
+  if (rows == 0) return GSB200_OK;
+  if (!src || !dst || rows < 0 || K <= 0 || K % 128 != 0 || ld < K / 32) return GSB200_ERR_BAD_ARG;
+  const long long total = (long long)mx_tiled_scale_bytes(rows, K);
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
+  mx_scales_to_tiled_kernel<<<(unsigned)blocks, 256, 0, st>>>(src, ld, rows, K / 32, dst, total);
+  return cuda_status(cudaGetLastError(), "mx scale re-tiling launch");
+}
+
+int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t* sfa, const uint8_t* B0,
+                       const uint8_t* B1, long long ldb, const uint8_t* sfb0, const uint8_t* sfb1, void* C,
+                       long long ldc, long long M, int N, int K, cudaStream_t st) {
+  if (M == 0) return GSB200_OK;
+  if (M < 0 || M > 0x7fffff00ll || N <= 0 || K <= 0) return GSB200_ERR_BAD_ARG;
+  if (!A || !sfa || !B0 || !sfb0 || !C || (dual && (!B1 || !sfb1))) return GSB200_ERR_BAD_ARG;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(B0) |
+                       reinterpret_cast<uintptr_t>(sfb0) | reinterpret_cast<uintptr_t>(C) |
+                       (dual ? (reinterpret_cast<uintptr_t>(B1) | reinterpret_cast<uintptr_t>(sfb1)) : 0);
+  if (al & 15) return GSB200_ERR_BAD_ARG;
+  if (K % 128 != 0 || lda < K || ldb < K || lda % 16 != 0 || ldb % 16 != 0) return GSB200_ERR_BAD_ARG;
+  if (N % 32 != 0 || ldc < N || ldc % 8 != 0) return GSB200_ERR_BAD_ARG;
+  int32_t rc = ensure_device();
+  if (rc != GSB200_OK) return rc;
+  static bool attr_done[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e1 = cudaFuncSetAttribute(mx_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MX_SMEM_BYTES);
+    cudaError_t e2 = cudaFuncSetAttribute(mx_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MX_SMEM_BYTES);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return cuda_status(e1 != cudaSuccess ? e1 : e2, "cudaFuncSetAttribute(mx gemm)");
+    attr_done[dev] = true;
+  }
+  void* fnp = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fnp, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return GSB200_ERR_DEVICE;
+  EncodeTiledFnM enc = reinterpret_cast<EncodeTiledFnM>(fnp);
+  auto map2d = [&](CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows, uint64_t cols,
+                   uint64_t ld, uint32_t bc, uint32_t br, CUtensorMapSwizzle sw) {
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld * (uint64_t)esz};
+    cuuint32_t box[2] = {bc, br};
+    cuuint32_t es[2] = {1, 1};
+    return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  };
+  CUtensorMap ta, tb0, tb1, tc;
+  const uint32_t brows = dual ? 64 : 128;
+  bool ok = map2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && map2d(&tb0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, B0, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 128, brows, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && map2d(&tb1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, dual ? B1 : B0, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 128, brows, CU_TENSOR_MAP_SWIZZLE_128B);
+  ok = ok && map2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+  if (!ok) return GSB200_ERR_BAD_ARG;
+  MxParams p{};
+  p.M = (int)M; p.N = N; p.K = K;
+  const int out_cols = dual ? 64 : 128;
+  p.m_blocks = (int)((M + MX_BM - 1) / MX_BM);
+  p.n_blocks = (N + out_cols - 1) / out_cols;
+  p.k_blocks = K / MX_BK;
+  p.sfa = sfa; p.sfb0 = sfb0; p.sfb1 = sfb1;
+  const long long tiles = (long long)p.m_blocks * p.n_blocks;
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  if (dual) mx_gemm_kernel<true><<<grid, MX_THREADS, MX_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+  else mx_gemm_kernel<false><<<grid, MX_THREADS, MX_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+  return cuda_status(cudaGetLastError(), "mx gemm launch");
+}
+
+}  // namespace gsb

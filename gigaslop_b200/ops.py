@@ -217,3 +217,34 @@ def factored_lstm_step(h_fp8_out, c_inout, hh_down, up_hh, bias_hh, x_down, up_i
                                           up_ih.data_ptr(), bias_ih.data_ptr() if bias_ih is not None else None,
                                           B, H, K_hh, R, _stream()), "factored_lstm_step")
     return h_fp8_out, c_inout
+
+
+def mx_scales_to_tiled(scales, K):
+    """Row-major E8M0 scales ``[rows, K/32]`` -> the 128 x 4 tile order the block-scaled GEMMs take."""
+    _need_cuda(scales)
+    rows = scales.shape[0]
+    out = torch.empty(int(lib().gsb200_mx_tiled_scale_bytes(rows, K)), dtype=torch.uint8, device=scales.device)
+    check(lib().gsb200_mx_scales_to_tiled(scales.data_ptr(), scales.stride(0), rows, K, out.data_ptr(), _stream()),
+          "mx_scales_to_tiled")
+    return out
+
+
+def gemm_mxfp8(A, sfa_tiled, B, sfb_tiled, out=None):
+    """Block-scaled MXFP8 GEMM ``A[M,K] . B[N,K]^T`` (E8M0 scale per 32 K elements on both operands) -> fp16."""
+    M, N, K = _check_ab(A, B, _F8)
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=A.device)
+    check(lib().gsb200_gemm_mxfp8_f16(A.data_ptr(), A.stride(0), sfa_tiled.data_ptr(), B.data_ptr(), B.stride(0),
+                                      sfb_tiled.data_ptr(), C.data_ptr(), C.stride(0), M, N, K, _stream()), "gemm_mxfp8")
+    return C
+
+
+def dual_gemm_mxfp8_silu(A, sfa_tiled, B_gate, B_up, sfb_gate_tiled, sfb_up_tiled, out=None):
+    """Block-scaled MXFP8 SwiGLU dual GEMM ``silu(A.Bg^T) * (A.Bu^T)`` -> fp16."""
+    M, N, K = _check_ab(A, B_gate, _F8)
+    _check_ab(A, B_up, _F8)
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=A.device)
+    check(lib().gsb200_dual_gemm_mxfp8_silu_f16(A.data_ptr(), A.stride(0), sfa_tiled.data_ptr(), B_gate.data_ptr(),
+                                                B_up.data_ptr(), B_gate.stride(0), sfb_gate_tiled.data_ptr(),
+                                                sfb_up_tiled.data_ptr(), C.data_ptr(), C.stride(0), M, N, K, _stream()),
+          "dual_gemm_mxfp8_silu")
+    return C

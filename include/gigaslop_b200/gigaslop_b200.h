@@ -157,6 +157,25 @@ int32_t gsb200_dual_gemm_fp8_silu_mxfp8(const uint8_t* A, int64_t lda, const uin
                                         const float* scale_b_up, int64_t M, int32_t N, int32_t K, int32_t flags,
                                         gsb200_stream_t stream);
 
+/* Block-scaled MXFP8 GEMMs (tcgen05 kind::mxf8f6f4): BOTH operands carry one E8M0 scale per 32 K elements, fp32
+ * accumulate, fp16 out.  This is the "MXFP8 dual-GEMM variant with E8M0 scales per 32-element K-block on both
+ * operands" of the benchmark configuration; the reference has no kernel source for it (see the note above), so
+ * parity is unpinned.  Scale factors are passed in the 128 x 4 tile order of the tensor core: the byte of
+ * (row r, 32-block b) sits at ((r/128)*(K/128) + b/4)*512 + (r%32)*16 + ((r%128)/32)*4 + b%4, rows padded to 128;
+ * gsb200_mx_scales_to_tiled converts row-major [rows, K/32] scales (as written by gsb200_ptq_mxfp8 and
+ * gsb200_dual_gemm_fp8_silu_mxfp8) into gsb200_mx_tiled_scale_bytes(rows, K) bytes of that order.
+ * K % 128 == 0, N % 32 == 0 (dual: gate and up each [N,K]). */
+int64_t gsb200_mx_tiled_scale_bytes(int64_t rows, int32_t K);
+int32_t gsb200_mx_scales_to_tiled(const uint8_t* scales, int64_t ld, int64_t rows, int32_t K, uint8_t* tiled,
+                                  gsb200_stream_t stream);
+int32_t gsb200_gemm_mxfp8_f16(const uint8_t* A, int64_t lda, const uint8_t* sfa_tiled, const uint8_t* B, int64_t ldb,
+                              const uint8_t* sfb_tiled, void* C, int64_t ldc, int64_t M, int32_t N, int32_t K,
+                              gsb200_stream_t stream);
+int32_t gsb200_dual_gemm_mxfp8_silu_f16(const uint8_t* A, int64_t lda, const uint8_t* sfa_tiled, const uint8_t* B_gate,
+                                        const uint8_t* B_up, int64_t ldb, const uint8_t* sfb_gate_tiled,
+                                        const uint8_t* sfb_up_tiled, void* C, int64_t ldc, int64_t M, int32_t N,
+                                        int32_t K, gsb200_stream_t stream);
+
 /* LSTM layer, recurrent half: T sequential steps in one persistent cooperative kernel.
  *   gates[b,4H] = ih[t,b,:] + (h_{t-1} . W_hh^T) * (s_hh[n]/448) + bias[n]   (gate blocks i|f|g|o, each H wide)
  *   c_t = sigmoid(f) c_{t-1} + sigmoid(i) tanh(g),  h_t = sigmoid(o) tanh(c_t)
