@@ -89,3 +89,24 @@ def test_fp8_dual_silu(M, N, K):
     c = g.dual_gemm_fp8_silu(A.cuda(), Wg.cuda(), Wu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda())
     ref = oracle.fp8_dual_silu_ref(A, Wg, Wu, sa, sbg, sbu)
     assert_close(c, ref.half(), atol=float(ref.abs().max()) * 2 ** -9, rtol=2e-2, what="fp8 SwiGLU")
+
+
+def test_reference_style_python_interface():
+    """Callers written against the reference's classes / compile_* factories."""
+    g = need_lib()
+    from gigaslop_b200 import compat
+    gen = torch.Generator().manual_seed(12)
+    M, N, K = 256, 512, 512
+    A = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8)
+    B = torch.randint(-127, 128, (N, K), generator=gen, dtype=torch.int8)
+    sa, sb = rand_scales(gen, M), rand_scales(gen, N)
+    C = torch.zeros(M, N, 1, dtype=torch.float16, device="cuda")
+    compat.TensorOpGemmI8(None, None)(A.cuda()[:, :, None], B.cuda()[:, :, None], C, sa.cuda()[:, None], sb.cuda()[:, None])
+    assert torch.equal(C[:, :, 0].cpu(), oracle.gemm_dequant_exact(A, B, sa, sb))
+    launcher = compat.compile_fp8_gemm(M=M, N=N, K=K)
+    A8, s8 = oracle.fp8_quantize_per_token(torch.randn(M, K, generator=gen))
+    W8 = rand_e4m3(gen, N, K)
+    C2 = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    launcher(C2, A8.cuda(), W8.cuda(), s8.cuda(), sb.cuda(), torch.cuda.current_stream(), M)
+    ref = oracle.fp8_gemm_f16_ref(A8, W8, s8, sb)
+    assert_close(C2, ref.half(), atol=float(ref.abs().max()) * 2 ** -9, rtol=2e-2, what="compile_fp8_gemm launcher")
