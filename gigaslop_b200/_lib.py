@@ -4,7 +4,7 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libgigaslop_b200.so")
+LIB_PATH = os.environ.get("GIGASLOP_B200_LIB") or os.path.join(_PKG, "libgigaslop_b200.so")
 
 OK = 0
 ERRORS = {-1: "bad argument", -2: "unsupported shape", -3: "device is not sm_100", -4: "device-side wait timed out"}

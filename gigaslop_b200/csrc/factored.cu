@@ -68,6 +68,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const long long budget = spin_budget();          // bound of every wait below, fetched once
 
   if (tid == 0) {
     mbar_arrive_expect_tx(full, kbs * 2 * FS_KB_BYTES);
@@ -79,7 +80,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
       for (int g = 0; g < 4; ++g)
         tma_load_2d(w_s + kb * FS_KB_BYTES + g * (FS_HS * 128), hh ? &tm_uhh : &tm_uih, full, k0, g * p.H + hid0);
     }
-    if (mbar_wait(full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x40)) {
+    if (mbar_wait(full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x40, budget)) {
       tc_fence_after();
       constexpr uint32_t idesc = umma_idesc(1, 0, 0, FS_ROWS, FS_NCOL);   // f16 x f16 -> f32
       for (int kb = 0; kb < kbs; ++kb) {
@@ -103,7 +104,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
       c[j] = v.x; c[j + 1] = v.y; c[j + 2] = v.z; c[j + 3] = v.w;
     }
   }
-  const bool ok = __all_sync(0xffffffffu, mbar_wait(mma_done, 0, abort_flag, ST_TIMEOUT_LSTM, 0x50));
+  const bool ok = __all_sync(0xffffffffu, mbar_wait(mma_done, 0, abort_flag, ST_TIMEOUT_LSTM, 0x50, budget));
   if (ok) {
     tc_fence_after();
     uint32_t acc[4][16];

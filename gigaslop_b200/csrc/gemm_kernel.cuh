@@ -47,15 +47,19 @@ constexpr int BK = 128;            // K bytes per smem stage (= one 128B swizzle
 constexpr int UMMA_K = 32;         // K bytes per tcgen05.mma for 8-bit kinds
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = 512;
-constexpr int EPI_WARPS = 8;
+#ifndef GSB_EPI_WARPS
+#define GSB_EPI_WARPS 8
+#endif
+constexpr int EPI_WARPS = GSB_EPI_WARPS;                 // 4, 8 or 16: EPI_WARPS/4 warps share each TMEM lane quarter
+constexpr int EPI_GROUPS = EPI_WARPS / 4;               // column groups of a tile
 constexpr int FRONT_WARPS = 4;                          // warp 0 producer, warp 1 MMA, warps 2-3 idle (one warpgroup)
 constexpr int GEMM_THREADS = 32 * (FRONT_WARPS + EPI_WARPS);
-constexpr int FRONT_REGS = 56;                          // register budgets after setmaxnreg (per thread)
-constexpr int EPI_REGS = 224;
+constexpr int FRONT_REGS = EPI_WARPS > 8 ? 24 : 56;                          // register budgets after setmaxnreg (per thread)
+constexpr int EPI_REGS = EPI_WARPS > 8 ? 112 : 224;
 constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
 constexpr int RES_MAX_KBLOCKS = 4;                      // resident operand (W slice or A block): up to K = 512
-constexpr int NSTAGE = 3;                               // ring depth of every schedule
+constexpr int NSTAGE = EPI_WARPS > 8 ? 2 : 3;           // ring depth of every schedule (16 epilogue warps need the room)
 constexpr int OUT_BOX_ROWS = 32;
 constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
 constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
@@ -72,15 +76,16 @@ struct SmemMap {
   static constexpr int STAGE_BYTES = SCHED == SCHED_WRES ? A_STAGE_BYTES
                                    : SCHED == SCHED_ARES ? B_STAGE_BYTES : A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_OFF = RES_BYTES;
-  static constexpr int OUT_BUFS = SCHED == SCHED_WRES ? 3 : 4;   // 32x32 fp16 staging boxes per epilogue warp
+  static constexpr int OUT_BUFS = EPI_WARPS > 8 ? 2 : (SCHED == SCHED_WRES ? 3 : 4);   // 32x32 fp16 staging boxes per epilogue warp
   static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
-  static constexpr int BAR_OFF = SCALE_OFF + 2 /*groups*/ * 2 /*tile parity*/ * SCALE_SET_BYTES;
+  static constexpr int BAR_OFF = SCALE_OFF + EPI_GROUPS * 2 /*tile parity*/ * SCALE_SET_BYTES;
   static constexpr int USED = BAR_OFF + 256;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
-static_assert(SmemMap<0>::USED <= GEMM_SMEM_BYTES && SmemMap<1>::USED <= GEMM_SMEM_BYTES &&
+static_assert(SmemMap<0>::USED <= GEMM_SMEM_BYTES && (EPI_WARPS > 8 || SmemMap<1>::USED <= GEMM_SMEM_BYTES) &&
               SmemMap<2>::USED <= GEMM_SMEM_BYTES, "shared memory budget");
+constexpr bool WRES_AVAILABLE = SmemMap<1>::USED <= GEMM_SMEM_BYTES;
 static_assert(GEMM_SMEM_BYTES > 116 * 1024, "one CTA per SM is what makes the 512-column TMEM allocation safe");
 
 constexpr unsigned int ST_BAD_SMEM_ALIGN = 1u << 8;
@@ -109,6 +114,9 @@ struct GemmParams {
 
 template <int KIND>
 __device__ __forceinline__ float acc_to_float(uint32_t v) {
+#ifdef GSB_ABL_NOI2F
+  return __uint_as_float(v);
+#endif
   if constexpr (KIND == KIND_I8) return static_cast<float>(static_cast<int32_t>(v));   // cvt.rn.f32.s32
   else return __uint_as_float(v);
 }
@@ -213,6 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const long long budget = spin_budget();          // bound of every wait below, fetched once
 
   // The register re-split sits inside each role's branch: code placed after the point where the two
   // branches meet would be compiled for the smaller budget.
@@ -242,12 +251,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if constexpr (ARES) {
             if (n_blk == 0) {                 // new row block: refill this K piece of A once its last reader retired
-              if (!mbar_wait(&res_empty[kb], rph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x300 | kb)) { ok = false; break; }
+              if (!mbar_wait(&res_empty[kb], rph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x300 | kb, budget)) { ok = false; break; }
               mbar_arrive_expect_tx(&res_full[kb], A_STAGE_BYTES);
               tma_load_2d(res_base + kb * A_STAGE_BYTES, &tm_a, &res_full[kb], kb * BK, m0);
             }
           }
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | s)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | s, budget)) { ok = false; break; }
           uint8_t* st = ring + s * Map::STAGE_BYTES;
           if constexpr (WRES) {
             mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES);
@@ -278,22 +287,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, BM, BN) : umma_idesc(1, 0, 0, BM, BN);
       int s = 0; uint32_t ph = 0; bool ok = true;
       if (WRES && !(p.ablate & 4)) {
-        ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200);
+        ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200, budget);
         tc_fence_after();
       }
       int m_blk, n_blk;
       uint32_t rph = 0;
       for (int it = 0; ok && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
         const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
-        if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as, budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
         if (ARES && n_blk == 0 && it != 0) rph ^= 1;
         for (int kb = 0; kb < p.k_blocks && !(p.ablate & 4); ++kb) {
           if constexpr (ARES) {
-            if (n_blk == 0 && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb)) { ok = false; break; }
+            if (n_blk == 0 && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
           }
-          if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s, budget)) { ok = false; break; }
           tc_fence_after();
           uint32_t a_addr, b_addr;
           const uint32_t st = smem_u32(ring + s * Map::STAGE_BYTES);
@@ -324,7 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int q = warp & 3;                // TMEM lane quarter this warp may read
     const int grp = e >> 2;                // column half of the tile handled by this warp
     uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's pair of staging boxes
-    constexpr int WARP_OUT_COLS = OUT_COLS_PER_TILE / 2;          // output columns per warp per tile (128 / 64)
+    constexpr int WARP_OUT_COLS = OUT_COLS_PER_TILE / EPI_GROUPS;  // output columns per warp per tile
     const int wcol0 = grp * WARP_OUT_COLS;                        // first output column (inside the tile) of this warp
     int obuf = 0; bool ok = true;
     int m_blk, n_blk;
@@ -376,7 +385,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           int nm, nn;
           if (tile_coords<SCHED>(p, it + 1, nm, nn) && nm != m_blk) {
             const int r = nm * BM + q * 32 + lane;
-            sa_next = (r < p.M) ? (p.scale_a ? __ldg(p.scale_a + r) : 1.f) : 0.f;
+            sa_next = (r < p.M) ? ((p.scale_a && !(p.ablate & 128)) ? __ldg(p.scale_a + r) : 1.f) : 0.f;
           }
         }
         if (!WRES || it == 0) {
@@ -398,7 +407,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
 
       // warp-uniform outcome: the tcgen05.ld below needs the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as, budget))) {
         ok = false;
         break;
       }
@@ -415,7 +424,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (row_base < p.M && !(p.ablate & 2)) {
         if constexpr (EPI == EPI_I32) {
           // raw accumulators, direct 16-byte stores
-          constexpr int COLS = BN / 2;
+          constexpr int COLS = BN / EPI_GROUPS;
 #pragma unroll 1
           for (int c = 0; c < COLS; c += 32) {
             uint32_t v[32];
@@ -493,7 +502,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             auto pair_begin = [&]() {
               buf_a = obuf; buf_b = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
               if constexpr (!DIRECT) {
-                if (lane == 0) tma_store_wait_read<OUT_BUFS - 2>();   // the stores that last used these two buffers have read them
+                if (lane == 0 && !(p.ablate & 64)) tma_store_wait_read<OUT_BUFS - 2>();   // the stores that last used these two buffers have read them
                 __syncwarp();
               }
             };
@@ -501,12 +510,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               if constexpr (DIRECT) {
                 if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = o;
               } else {
-                *reinterpret_cast<uint4*>(out_buf + (which ? buf_b : buf_a) * OUT_BUF_BYTES + stg_off[piece]) = o;
+                if (!(p.ablate & 16) || o.x == 0x7fc01234u) *reinterpret_cast<uint4*>(out_buf + (which ? buf_b : buf_a) * OUT_BUF_BYTES + stg_off[piece]) = o;
               }
             };
             auto pair_end = [&](int n_a, int n_b) {
               if constexpr (!DIRECT) {
-                fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
+                if (!(p.ablate & 32)) fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
                 __syncwarp();
                 if (lane == 0 && !(p.ablate & 1)) {
                   tma_store_2d(&tm_c, out_buf + buf_a * OUT_BUF_BYTES, n_a, row_base); tma_store_commit();
@@ -526,7 +535,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
               for (int pr = 0; pr < NSUB / 2; ++pr) {
                 const int n = n0 + wcol0 + pr * 64;
-                if (n < p.N) {
+                if (n < p.N && !(p.ablate & 8)) {
                   pair_begin();
 #pragma unroll
                   for (int h = 0; h < 2; ++h) {

@@ -118,6 +118,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const long long budget = spin_budget();          // bound of every wait below, fetched once
 
   auto step_t = [&](int s) { return p.reverse ? p.T - 1 - s : s; };
   auto issue_ih = [&](int s) {   // one thread: TMA the four gate boxes of step s into buffer s & 1
@@ -147,7 +148,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   for (int j = 0; j < 16; ++j)
     c[j] = (p.c0 && row_ok) ? __half2float(p.c0[(long long)row * H + hid0 + half * 16 + j]) : 0.f;
 
-  bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10);
+  bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10, budget);
   const int chunks_per_row = p.k_blocks * 8;                 // 16-byte pieces of a (zero-padded) h row
   unsigned int* my_flags = p.flags + grp * p.slices;
 
@@ -156,7 +157,6 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     const uint8_t* h_prev = (s == 0) ? p.h0 : p.hbuf + (size_t)((s + 1) & 1) * B * H;
     if (s > 0 && tid < p.slices) {
       long long t0 = clock64();
-      const long long budget = g_status[2] ? (long long)g_status[2] : kDefaultSpinBudget;
       while (ld_acquire_gpu(my_flags + tid) < (unsigned int)s) {
         if (*abort_flag) break;
         if (clock64() - t0 > budget) {
@@ -192,8 +192,8 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       umma_commit(mma_done);
     }
     // ---- 4. gate math on this thread's row ---------------------------------------------------------------
-    ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20) &&
-         mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30);
+    ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20, budget) &&
+         mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30, budget);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();

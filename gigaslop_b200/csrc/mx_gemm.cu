@@ -88,6 +88,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const long long budget = spin_budget();          // bound of every wait below, fetched once
 
   if (warp == 0) {
     if (lane == 0) {
@@ -97,7 +98,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int m0 = m_blk * MX_BM, n0 = n_blk * OUT_COLS;
         const int nb128 = n0 / 128;                              // scale tile row block of W
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, 0x600 | s)) { ok = false; break; }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, 0x600 | s, budget)) { ok = false; break; }
           uint8_t* st = smem + s * MX_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[s], MX_A_BYTES + MX_B_BYTES + (DUAL ? 3 : 2) * MX_SF_BYTES);
           tma_load_2d(st, &tm_a, &full_bar[s], kb * MX_BK, m0);
@@ -125,11 +126,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
         const int n0 = (int)(t % p.n_blocks) * OUT_COLS;
         const uint32_t sfb_sub = (uint32_t)((n0 % 128) / 32);      // dual: which 64-row half of the scale tile
-        if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, 0x700 | as)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, 0x700 | as, budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * MX_BN;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, 0x800 | s)) { ok = false; break; }
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, 0x800 | s, budget)) { ok = false; break; }
           tc_fence_after();
           const uint32_t st = smem_u32(smem + s * MX_STAGE_BYTES);
           const uint32_t sf = st + MX_A_BYTES + MX_B_BYTES;
@@ -167,7 +168,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
       const int m0 = (int)(t / p.n_blocks) * MX_BM, n0 = (int)(t % p.n_blocks) * OUT_COLS;
-      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, 0x900 | as))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, 0x900 | as, budget))) { ok = false; break; }
       tc_fence_after();
       const int row_base = m0 + q * 32;
       const uint32_t t_row = tmem_base + as * MX_BN + ((uint32_t)(q * 32) << 16);

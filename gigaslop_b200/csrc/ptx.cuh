@@ -25,7 +25,10 @@ constexpr unsigned int ST_TIMEOUT_LSTM     = 1u << 3;
 constexpr long long kDefaultSpinBudget = 2000000000ll;   // ~1 s of SM clocks
 // Upper bound (ns) a try_wait may keep the thread suspended before it returns to the polling loop; the
 // hardware wakes it as soon as the phase completes, so a waiting role costs almost no issue slots.
-constexpr unsigned int kTryWaitSuspendNs = 20000;
+#ifndef GSB_TRYWAIT_NS
+#define GSB_TRYWAIT_NS 20000
+#endif
+constexpr unsigned int kTryWaitSuspendNs = GSB_TRYWAIT_NS;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -64,6 +67,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
+#if GSB_TRYWAIT_NS == 0
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+#endif
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -74,12 +87,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Spin budget in SM clocks: read ONCE per thread at kernel start (it lives in global memory; fetching it inside a
+// wait would put an L2 round trip on every blocking hand-off).
+__device__ __forceinline__ long long spin_budget() {
+  const unsigned int v = g_status[2];
+  return v ? (long long)v : kDefaultSpinBudget;
+}
+
 // Bounded wait.  Returns false if the budget ran out or another role already
 // gave up (abort flag in shared memory); the caller must then unwind.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned int fail_code, unsigned int where) {
+                                          unsigned int fail_code, unsigned int where, long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long budget = g_status[2] ? (long long)g_status[2] : kDefaultSpinBudget;
   long long t0 = clock64();
   int spins = 0;
   while (true) {
@@ -246,7 +265,12 @@ __device__ __forceinline__ void upk2(uint64_t r, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r));
 }
 __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+#ifdef GSB_NO_F32X2      // build switch for measuring the packed pipe against two scalar multiplies
+  float a0, a1, b0, b1; upk2(a, a0, a1); upk2(b, b0, b1);
+  return pk2(__fmul_rn(a0, b0), __fmul_rn(a1, b1));
+#else
   uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+#endif
 }
 __device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
   uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
@@ -256,6 +280,9 @@ __device__ __forceinline__ uint64_t fsub2(uint64_t a, uint64_t b) {
 }
 __device__ __forceinline__ uint32_t pack_half2_from(uint64_t v) {
   float lo, hi; upk2(v, lo, hi);
+#ifdef GSB_ABL_NOPACK
+  return __float_as_uint(lo) ^ __float_as_uint(hi);
+#endif
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
