@@ -26,16 +26,6 @@ struct FacStepParams {
   float* c; uint8_t* h_out;
 };
 
-__device__ __forceinline__ void fs_tmem_ld_x16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(FS_THREADS, 1)
 factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __grid_constant__ CUtensorMap tm_xd,
                           const __grid_constant__ CUtensorMap tm_uhh, const __grid_constant__ CUtensorMap tm_uih,
@@ -110,7 +100,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
     uint32_t acc[4][16];
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
-    for (int g = 0; g < 4; ++g) fs_tmem_ld_x16(t_row + g * FS_HS + half * 16, acc[g]);
+    for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * FS_HS + half * 16, acc[g]);
     tmem_ld_wait();
     if (row_ok) {
       float hv[16];

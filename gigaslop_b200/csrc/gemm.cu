@@ -158,7 +158,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.rot_cols = rot_cols;
   p.row_offset = (int)(a.row_offset % p.seqlen);
   p.direct_store = (a.flags & GSB200_FLAG_DIRECT_STORE) ? 1 : 0;
-  p.ablate = (a.flags >> 8) & 255;
+  p.ablate = (a.flags >> 8) & 7;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
 
@@ -181,9 +181,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   int grid;
   p.m_major = 0;
   p.n_groups = 0;
-  if (resident && a.epi != EPI_ROTARY && !WRES_AVAILABLE) {
-    grid = (int)(tiles < sm_count() ? tiles : sm_count());     // build without room for the weight-stationary layout
-  } else if (resident && a.epi != EPI_ROTARY) {
+  if (resident && a.epi != EPI_ROTARY) {
     int groups = sm_count() / p.n_blocks;
     if (groups < 1) groups = 1;
     if (groups > p.m_blocks) groups = p.m_blocks;
@@ -198,23 +196,23 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   cudaError_t e = cudaErrorInvalidValue;
   if (a.kind == KIND_I8) {
     switch (a.epi) {
-      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
-      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
-      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
+      case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else if (a.kind == KIND_F8) {
     switch (a.epi) {
-      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
-      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
-      case EPI_SILU_MX: e = launch_inst<KIND_F8, EPI_SILU_MX>(ta, tb0, tb1, tc, p, grid, resident && (WRES_AVAILABLE || a.epi == EPI_ROTARY), st); break;
+      case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_SILU_MX: e = launch_inst<KIND_F8, EPI_SILU_MX>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }
   } else if (a.kind == KIND_F16) {
     if (a.epi != EPI_DEQUANT) return GSB200_ERR_BAD_ARG;
-    e = launch_inst<KIND_F16, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident && WRES_AVAILABLE, st);
+    e = launch_inst<KIND_F16, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st);
   } else {
     return GSB200_ERR_BAD_ARG;
   }

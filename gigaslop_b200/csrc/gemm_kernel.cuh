@@ -24,12 +24,14 @@
 //   warp 1      TMEM owner + single-thread tcgen05.mma issue
 //   warps 2,3   idle; they complete the first warpgroup, which gives its registers to the epilogue
 //               (setmaxnreg: 56 per thread for warps 0-3, 224 for the two epilogue warpgroups)
-//   warps 4..11 epilogue: tcgen05.ld (thread = accumulator row) -> math ->
+//   warps 4..11 epilogue, two sets of four warps that take alternate tiles: tcgen05.ld (thread =
+//               accumulator row, next chunk in flight during the math of the current) -> math ->
 //               swizzled smem staging -> TMA store (per-warp 32 x 32 fp16 boxes, issued in pairs)
 //
-// Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue of tile i overlaps
-// the MMAs of tile i+1.  The epilogue reads nothing from global memory inside its column loop:
-// per-channel scales sit in shared memory, the per-token scale is prefetched one tile ahead.
+// Two 256-column accumulator stages fill the 512 TMEM columns (stage s belongs to epilogue set s), so
+// the epilogue of tile i overlaps the MMAs of tile i+1 and the epilogue of tile i-1.  The epilogue reads
+// nothing from global memory inside its column loop: per-channel scales sit in shared memory, the
+// per-token scale and the next tile's channel scales are fetched one tile ahead.
 #pragma once
 #include <cuda_fp8.h>
 
@@ -47,23 +49,19 @@ constexpr int BK = 128;            // K bytes per smem stage (= one 128B swizzle
 constexpr int UMMA_K = 32;         // K bytes per tcgen05.mma for 8-bit kinds
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = 512;
-#ifndef GSB_EPI_WARPS
-#define GSB_EPI_WARPS 8
-#endif
-constexpr int EPI_WARPS = GSB_EPI_WARPS;                 // 4, 8 or 16: EPI_WARPS/4 warps share each TMEM lane quarter
-constexpr int EPI_GROUPS = EPI_WARPS / 4;               // column groups of a tile
+constexpr int EPI_WARPS = 8;                            // two sets of 4 warps; set s drains accumulator stage s
 constexpr int FRONT_WARPS = 4;                          // warp 0 producer, warp 1 MMA, warps 2-3 idle (one warpgroup)
 constexpr int GEMM_THREADS = 32 * (FRONT_WARPS + EPI_WARPS);
-constexpr int FRONT_REGS = EPI_WARPS > 8 ? 24 : 56;                          // register budgets after setmaxnreg (per thread)
-constexpr int EPI_REGS = EPI_WARPS > 8 ? 112 : 224;
+constexpr int FRONT_REGS = 56;                          // register budgets after setmaxnreg (per thread)
+constexpr int EPI_REGS = 224;
 constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
 constexpr int RES_MAX_KBLOCKS = 4;                      // resident operand (W slice or A block): up to K = 512
-constexpr int NSTAGE = EPI_WARPS > 8 ? 2 : 3;           // ring depth of every schedule (16 epilogue warps need the room)
+constexpr int NSTAGE = 3;                               // ring depth of every schedule
 constexpr int OUT_BOX_ROWS = 32;
 constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
 constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
-constexpr int SCALE_SET_BYTES = 512;                    // 128 fp32 per-channel scales: the columns of one warp group
+constexpr int SCALE_SET_FLOATS = BN;                    // per-channel scales of one tile, indexed by accumulator column
 
 // Shared-memory map (offsets from a 1 KiB-aligned base).
 //   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales][barriers]
@@ -76,16 +74,15 @@ struct SmemMap {
   static constexpr int STAGE_BYTES = SCHED == SCHED_WRES ? A_STAGE_BYTES
                                    : SCHED == SCHED_ARES ? B_STAGE_BYTES : A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_OFF = RES_BYTES;
-  static constexpr int OUT_BUFS = EPI_WARPS > 8 ? 2 : (SCHED == SCHED_WRES ? 3 : 4);   // 32x32 fp16 staging boxes per epilogue warp
+  static constexpr int OUT_BUFS = SCHED == SCHED_WRES ? 3 : 4;   // 32x32 fp16 staging boxes per epilogue warp
   static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
-  static constexpr int BAR_OFF = SCALE_OFF + EPI_GROUPS * 2 /*tile parity*/ * SCALE_SET_BYTES;
+  static constexpr int BAR_OFF = SCALE_OFF + 2 /*sets*/ * SCALE_SET_FLOATS * 4;
   static constexpr int USED = BAR_OFF + 256;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
-static_assert(SmemMap<0>::USED <= GEMM_SMEM_BYTES && (EPI_WARPS > 8 || SmemMap<1>::USED <= GEMM_SMEM_BYTES) &&
+static_assert(SmemMap<0>::USED <= GEMM_SMEM_BYTES && SmemMap<1>::USED <= GEMM_SMEM_BYTES &&
               SmemMap<2>::USED <= GEMM_SMEM_BYTES, "shared memory budget");
-constexpr bool WRES_AVAILABLE = SmemMap<1>::USED <= GEMM_SMEM_BYTES;
 static_assert(GEMM_SMEM_BYTES > 116 * 1024, "one CTA per SM is what makes the 512-column TMEM allocation safe");
 
 constexpr unsigned int ST_BAD_SMEM_ALIGN = 1u << 8;
@@ -114,9 +111,6 @@ struct GemmParams {
 
 template <int KIND>
 __device__ __forceinline__ float acc_to_float(uint32_t v) {
-#ifdef GSB_ABL_NOI2F
-  return __uint_as_float(v);
-#endif
   if constexpr (KIND == KIND_I8) return static_cast<float>(static_cast<int32_t>(v));   // cvt.rn.f32.s32
   else return __uint_as_float(v);
 }
@@ -126,20 +120,20 @@ __device__ __forceinline__ float acc_to_float(uint32_t v) {
 // the product (cute/ampere_gemm_i8_quant_rmem.py:603,727); FP8 applies them left to right
 // (fly/rdna_fp8_preshuffle_gemm.py:392-396).  sa2 = (sA, sA), sb2 = (sB[n], sB[n+1]).
 template <int KIND>
-__device__ __forceinline__ uint64_t dequant2(uint32_t a0, uint32_t a1, uint64_t sa2, uint64_t sb2) {
-  const uint64_t acc = pk2(acc_to_float<KIND>(a0), acc_to_float<KIND>(a1));
+__device__ __forceinline__ float2 dequant2(uint32_t a0, uint32_t a1, float2 sa2, float2 sb2) {
+  const float2 acc = pk2(acc_to_float<KIND>(a0), acc_to_float<KIND>(a1));
   if constexpr (KIND == KIND_I8) return fmul2(acc, fmul2(sa2, sb2));
   else return fmul2(fmul2(acc, sa2), sb2);
 }
 
 // 8 consecutive columns -> 8 fp16 (one 16-byte piece).  s01/s23 hold the 8 per-channel scales as pairs.
 template <int KIND>
-__device__ __forceinline__ uint4 dequant_piece(const uint32_t* v, uint64_t sa2, ulonglong2 s_lo, ulonglong2 s_hi) {
+__device__ __forceinline__ uint4 dequant_piece(const uint32_t* v, float2 sa2, float4 s_lo, float4 s_hi) {
   uint4 o;
-  o.x = pack_half2_from(dequant2<KIND>(v[0], v[1], sa2, s_lo.x));
-  o.y = pack_half2_from(dequant2<KIND>(v[2], v[3], sa2, s_lo.y));
-  o.z = pack_half2_from(dequant2<KIND>(v[4], v[5], sa2, s_hi.x));
-  o.w = pack_half2_from(dequant2<KIND>(v[6], v[7], sa2, s_hi.y));
+  o.x = pack_half2_from(dequant2<KIND>(v[0], v[1], sa2, make_float2(s_lo.x, s_lo.y)));
+  o.y = pack_half2_from(dequant2<KIND>(v[2], v[3], sa2, make_float2(s_lo.z, s_lo.w)));
+  o.z = pack_half2_from(dequant2<KIND>(v[4], v[5], sa2, make_float2(s_hi.x, s_hi.y)));
+  o.w = pack_half2_from(dequant2<KIND>(v[6], v[7], sa2, make_float2(s_hi.z, s_hi.w)));
   return o;
 }
 
@@ -209,7 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
+    for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS / 2); }
     for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], 1); mbar_init(&res_empty[s], 1); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -329,30 +323,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
     // ------------------------------ epilogue ----------------------------------
+    // Two sets of four warps.  Set s owns accumulator stage s, i.e. this CTA's tiles s, s + 2, ...: while one
+    // set converts and stores a tile the other is already reading the next one, so TMEM reads, arithmetic
+    // and output stores of neighbouring tiles overlap instead of running in phase.  A warp covers the 32
+    // rows of its TMEM lane quarter and all 256 accumulator columns, in chunks: the TMEM load of chunk i+1
+    // is in flight during the arithmetic of chunk i, and the stage goes back to the MMA warp as soon as the
+    // last chunk sits in registers.
     const int e = warp - FRONT_WARPS;      // 0..7
     const int q = warp & 3;                // TMEM lane quarter this warp may read
-    const int grp = e >> 2;                // column half of the tile handled by this warp
-    uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's pair of staging boxes
-    constexpr int WARP_OUT_COLS = OUT_COLS_PER_TILE / EPI_GROUPS;  // output columns per warp per tile
-    const int wcol0 = grp * WARP_OUT_COLS;                        // first output column (inside the tile) of this warp
-    int obuf = 0; bool ok = true;
+    const int set = e >> 2;                // accumulator stage drained by this warp
+    const uint32_t set_bar = 1 + set;      // named barrier of the set (barrier 0 is __syncthreads)
+    const int tset = q * 32 + lane;        // thread index inside the set
+    uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's staging boxes
+    float* sc = scale_base + set * SCALE_SET_FLOATS;              // this set's per-channel scales, by accumulator column
+    int obuf = 0;
     int m_blk, n_blk;
-    // per-row state, fetched once per row block and kept in registers across its column blocks; the
-    // token scale of the NEXT row block is prefetched while the current tile is processed
+    // per-row state, fetched once per row block and kept in registers across its column blocks; the token
+    // scale and the channel scales of the set's NEXT tile are fetched while the current tile is processed
     float sa = 0.f, sa_next = 0.f;
-    uint64_t sn2[16], cs2[16];             // sin / cos row of this thread's token as fp32 pairs
+    float2 sb_next = make_float2(0.f, 0.f);
+    float2 sn2[16], cs2[16];             // sin / cos row of this thread's token as fp32 pairs
     int cur_m_blk = -1;
     uint32_t stg_off[4];                   // byte offsets of the 4 pieces of this thread's row in a swizzled staging box
 #pragma unroll
     for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
+
+    // channel scales of accumulator columns 2*tset, 2*tset+1 of the tile whose first output column is n0
+    // (dual GEMM: accumulator columns 0..127 are gate, 128..255 up, both for output columns n0..n0+127)
+    auto fetch_scales = [&](int n0) -> float2 {
+      int c = 2 * tset;
+      const float* src = p.scale_b0;
+      if constexpr (DUAL) { if (c >= BN / 2) { c -= BN / 2; src = p.scale_b1; } }
+      const int n = n0 + c;
+      if (n + 2 > p.N) return make_float2(0.f, 0.f);
+      if (!src) return make_float2(1.f, 1.f);                            // no per-channel scale
+      if (p.scale_b_scalar) { const float v = __ldg(src); return make_float2(v, v); }
+      return __ldg(reinterpret_cast<const float2*>(src + n));
+    };
     if constexpr (EPI != EPI_I32) {
-      if (tile_coords<SCHED>(p, 0, m_blk, n_blk)) {
+      if (tile_coords<SCHED>(p, set, m_blk, n_blk)) {
         const int r = m_blk * BM + q * 32 + lane;
         if (r < p.M) sa_next = p.scale_a ? __ldg(p.scale_a + r) : 1.f;
+        sb_next = fetch_scales(n_blk * OUT_COLS_PER_TILE);
       }
     }
-    for (int it = 0; ok && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
-      const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
+    for (int it = set; tile_coords<SCHED>(p, it, m_blk, n_blk); it += 2) {
+      const uint32_t aph = (it >> 1) & 1;
       const int m0 = m_blk * BM;
       const int n0 = n_blk * OUT_COLS_PER_TILE;
       const int row_base = m0 + q * 32;
@@ -360,77 +376,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool row_ok = row < p.M;
 
       // ---- per-tile prologue: everything that comes from global memory, before the accumulator wait ----
-      float4 sbv = make_float4(0.f, 0.f, 0.f, 0.f);
-      // The four warps of a column group share one scale set per tile parity (they all write the same
-      // values).  A set is rewritten only after the accumulator wait of a tile two steps later, which
-      // cannot complete before every warp has released -- hence finished reading -- the older tile.
-      float* sc = scale_base + (grp * 2 + (WRES ? 0 : (it & 1))) * (SCALE_SET_BYTES / 4);
       if constexpr (EPI != EPI_I32) {
         if (m_blk != cur_m_blk) {
           cur_m_blk = m_blk;
           sa = sa_next;
           if constexpr (EPI == EPI_ROTARY) {
             const int pos = row_ok ? (int)(((long long)row + p.row_offset) % p.seqlen) : 0;
-            const ulonglong2* s4 = reinterpret_cast<const ulonglong2*>(p.sin_tab + (long long)pos * 32);
-            const ulonglong2* c4 = reinterpret_cast<const ulonglong2*>(p.cos_tab + (long long)pos * 32);
+            const float4* s4 = reinterpret_cast<const float4*>(p.sin_tab + (long long)pos * 32);
+            const float4* c4 = reinterpret_cast<const float4*>(p.cos_tab + (long long)pos * 32);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const ulonglong2 a = __ldg(s4 + j), b = __ldg(c4 + j);
-              sn2[2 * j] = a.x; sn2[2 * j + 1] = a.y;
-              cs2[2 * j] = b.x; cs2[2 * j + 1] = b.y;
+              const float4 a = __ldg(s4 + j), b = __ldg(c4 + j);
+              sn2[2 * j] = make_float2(a.x, a.y); sn2[2 * j + 1] = make_float2(a.z, a.w);
+              cs2[2 * j] = make_float2(b.x, b.y); cs2[2 * j + 1] = make_float2(b.z, b.w);
             }
           }
         }
-        {
-          int nm, nn;
-          if (tile_coords<SCHED>(p, it + 1, nm, nn) && nm != m_blk) {
+        if (!WRES || it == set) {          // a weight-stationary CTA keeps one column block: its scales never change
+          // every warp of the set has passed its last read of the previous tile's scales
+          if (it != set) named_barrier_sync(set_bar, 128);
+          *reinterpret_cast<float2*>(sc + 2 * tset) = sb_next;
+        }
+        int nm, nn;
+        if (tile_coords<SCHED>(p, it + 2, nm, nn)) {
+          if (nm != m_blk) {
             const int r = nm * BM + q * 32 + lane;
-            sa_next = (r < p.M) ? ((p.scale_a && !(p.ablate & 128)) ? __ldg(p.scale_a + r) : 1.f) : 0.f;
+            sa_next = (r < p.M) ? (p.scale_a ? __ldg(p.scale_a + r) : 1.f) : 0.f;
           }
-        }
-        if (!WRES || it == 0) {
-          // per-channel scales of this warp group's columns (dual: 64 gate | 64 up): fetched now, parked in
-          // shared memory after the accumulator wait (see below)
-          if constexpr (DUAL) {
-            const int n = n0 + wcol0 + (lane & 15) * 4;
-            const float* src = (lane < 16) ? p.scale_b0 : p.scale_b1;
-            if (n + 4 <= p.N) sbv = __ldg(reinterpret_cast<const float4*>(src + n));
-          } else {
-            const int n = n0 + wcol0 + lane * 4;
-            if (n + 4 <= p.N) {
-              if (!p.scale_b0) sbv = make_float4(1.f, 1.f, 1.f, 1.f);                       // no per-channel scale
-              else if (p.scale_b_scalar) { const float v = __ldg(p.scale_b0); sbv = make_float4(v, v, v, v); }
-              else sbv = __ldg(reinterpret_cast<const float4*>(p.scale_b0 + n));
-            }
-          }
+          if (!WRES) sb_next = fetch_scales(nn * OUT_COLS_PER_TILE);
         }
       }
 
-      // warp-uniform outcome: the tcgen05.ld below needs the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as, budget))) {
-        ok = false;
-        break;
-      }
+      // The set agrees on the outcome of the bounded wait, so it either works on or leaves as a whole and
+      // no warp is left behind at a later barrier; the same barrier publishes the scales written above.
+      const bool got = mbar_wait(&acc_full[set], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | set, budget);
+      if (!named_barrier_and(set_bar, 128, got)) break;
       tc_fence_after();
-      const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
-      if constexpr (EPI != EPI_I32) {
-        if (!WRES || it == 0) {
-          if constexpr (DUAL) *reinterpret_cast<float4*>(sc + (lane < 16 ? 0 : 64) + (lane & 15) * 4) = sbv;
-          else *reinterpret_cast<float4*>(sc + lane * 4) = sbv;
-          __syncwarp();
-        }
-      }
+      const uint32_t t_row = tmem_base + set * BN + ((uint32_t)(q * 32) << 16);
+      // hand the accumulator stage back to the MMA warp: called once per tile, right after the wait that
+      // brought this warp's last accumulator chunk into registers
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[set]);
+      };
 
       if (row_base < p.M && !(p.ablate & 2)) {
         if constexpr (EPI == EPI_I32) {
           // raw accumulators, direct 16-byte stores
-          constexpr int COLS = BN / EPI_GROUPS;
-#pragma unroll 1
-          for (int c = 0; c < COLS; c += 32) {
-            uint32_t v[32];
-            const int col = grp * COLS + c;
-            tmem_ld_32x32b_x32(t_row + col, v);
-            tmem_ld_wait();
+          auto emit = [&](const uint32_t (&v)[32], int col) {
             if (row_ok) {
               int32_t* dst = reinterpret_cast<int32_t*>(p.C) + (long long)row * p.ldc + n0 + col;
 #pragma unroll
@@ -438,36 +432,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 if (n0 + col + j + 4 <= p.N)
                   *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
+          };
+          uint32_t va[32], vb[32];
+          tmem_ld_32x32b_x32(t_row, va);
+#pragma unroll
+          for (int c = 0; c < BN; c += 64) {
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(t_row + c + 32, vb);
+            emit(va, c);
+            tmem_ld_wait();
+            if (c + 64 < BN) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
+            emit(vb, c + 32);
           }
         } else if constexpr (EPI == EPI_SILU_MX) {
           // SwiGLU product quantised per 32 output columns: e = biased exponent of the block maximum,
           // scale byte = clamp(e - 8, 0, 254) (value 2^(byte-127)), elements = e4m3_rn_satfinite(v * 2^(127-byte)).
           // A thread holds whole 32-column blocks of its row, so the block maximum needs no exchange.
-          const uint64_t sa2 = pk2(sa, sa);
-          constexpr int NSUB = WARP_OUT_COLS / 32;
-          uint32_t g[NSUB][32], u[NSUB][32];
-#pragma unroll
-          for (int ci = 0; ci < NSUB; ++ci) {
-            tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, g[ci]);
-            tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0 + ci * 32, u[ci]);
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int h = 0; h < NSUB; ++h) {
-            const int c = h * 32;
-            const int n = n0 + wcol0 + c;
+          const float2 sa2 = pk2(sa, sa);
+          auto emit = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c) {
+            const int n = n0 + c;
             if (n + 32 <= p.N) {
               float o[32];
               float amax = 0.f;
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
-                const uint64_t sg = *reinterpret_cast<const uint64_t*>(sc + c + j);
-                const uint64_t su = *reinterpret_cast<const uint64_t*>(sc + 64 + c + j);
-                float g0, g1, u0, u1;
-                upk2(dequant2<KIND>(g[h][j], g[h][j + 1], sa2, sg), g0, g1);
-                upk2(dequant2<KIND>(u[h][j], u[h][j + 1], sa2, su), u0, u1);
-                o[j] = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
-                o[j + 1] = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                const float2 sg = *reinterpret_cast<const float2*>(sc + c + j);
+                const float2 su = *reinterpret_cast<const float2*>(sc + BN / 2 + c + j);
+                const float2 gv = dequant2<KIND>(g[j], g[j + 1], sa2, sg);
+                const float2 uv = dequant2<KIND>(u[j], u[j + 1], sa2, su);
+                o[j] = __fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x;
+                o[j + 1] = __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y;
                 amax = fmaxf(amax, fmaxf(fabsf(o[j]), fabsf(o[j + 1])));
               }
               int eb = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 8;
@@ -487,9 +481,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 p.out_scale[(long long)row * p.ld_scale + (n >> 5)] = (uint8_t)eb;
               }
             }
+          };
+          uint32_t ga[32], ua[32], gb[32], ub[32];
+          tmem_ld_32x32b_x32(t_row, ga);
+          tmem_ld_32x32b_x32(t_row + BN / 2, ua);
+#pragma unroll
+          for (int c = 0; c < BN / 2; c += 64) {
+            tmem_ld_wait();
+            tmem_ld_32x32b_x32(t_row + c + 32, gb);
+            tmem_ld_32x32b_x32(t_row + BN / 2 + c + 32, ub);
+            emit(ga, ua, c);
+            tmem_ld_wait();
+            if (c + 64 < BN / 2) {
+              tmem_ld_32x32b_x32(t_row + c + 64, ga);
+              tmem_ld_32x32b_x32(t_row + BN / 2 + c + 64, ua);
+            } else {
+              release();
+            }
+            emit(gb, ub, c + 32);
           }
         } else {
-          const uint64_t sa2 = pk2(sa, sa);
+          const float2 sa2 = pk2(sa, sa);
           // The body exists twice: the product path (swizzled staging + TMA store) and a diagnostic path
           // that stores straight from registers; the choice is made once per tile.
           auto run_tile = [&](auto direct_tag) {
@@ -502,7 +514,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             auto pair_begin = [&]() {
               buf_a = obuf; buf_b = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
               if constexpr (!DIRECT) {
-                if (lane == 0 && !(p.ablate & 64)) tma_store_wait_read<OUT_BUFS - 2>();   // the stores that last used these two buffers have read them
+                if (lane == 0) tma_store_wait_read<OUT_BUFS - 2>();   // the stores that last used these two buffers have read them
                 __syncwarp();
               }
             };
@@ -510,12 +522,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               if constexpr (DIRECT) {
                 if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = o;
               } else {
-                if (!(p.ablate & 16) || o.x == 0x7fc01234u) *reinterpret_cast<uint4*>(out_buf + (which ? buf_b : buf_a) * OUT_BUF_BYTES + stg_off[piece]) = o;
+                *reinterpret_cast<uint4*>(out_buf + (which ? buf_b : buf_a) * OUT_BUF_BYTES + stg_off[piece]) = o;
               }
             };
             auto pair_end = [&](int n_a, int n_b) {
               if constexpr (!DIRECT) {
-                if (!(p.ablate & 32)) fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
+                fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
                 __syncwarp();
                 if (lane == 0 && !(p.ablate & 1)) {
                   tma_store_2d(&tm_c, out_buf + buf_a * OUT_BUF_BYTES, n_a, row_base); tma_store_commit();
@@ -526,132 +538,149 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             };
 
             if constexpr (EPI == EPI_DEQUANT) {
-              // all of this warp's accumulator columns are fetched with back-to-back TMEM loads and one wait
-              constexpr int NSUB = WARP_OUT_COLS / 32;
-              uint32_t v[NSUB][32];
-#pragma unroll
-              for (int ci = 0; ci < NSUB; ++ci) tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, v[ci]);
-              tmem_ld_wait();
-#pragma unroll
-              for (int pr = 0; pr < NSUB / 2; ++pr) {
-                const int n = n0 + wcol0 + pr * 64;
-                if (n < p.N && !(p.ablate & 8)) {
+              // chunks of 64 columns = one pair of boxes
+              auto ld64 = [&](int col, uint32_t (&v)[2][32]) {
+                tmem_ld_32x32b_x32(t_row + col, v[0]);
+                tmem_ld_32x32b_x32(t_row + col + 32, v[1]);
+              };
+              auto emit = [&](const uint32_t (&v)[2][32], int c) {
+                const int n = n0 + c;
+                if (n < p.N) {
                   pair_begin();
 #pragma unroll
                   for (int h = 0; h < 2; ++h) {
-                    const int c = pr * 64 + h * 32;
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
-                      const ulonglong2 s_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
-                      const ulonglong2 s_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
-                      put(h, n + h * 32, j >> 3, dequant_piece<KIND>(&v[pr * 2 + h][j], sa2, s_lo, s_hi));
+                      const float4 s_lo = *reinterpret_cast<const float4*>(sc + c + h * 32 + j);
+                      const float4 s_hi = *reinterpret_cast<const float4*>(sc + c + h * 32 + j + 4);
+                      put(h, n + h * 32, j >> 3, dequant_piece<KIND>(&v[h][j], sa2, s_lo, s_hi));
                     }
                   }
                   pair_end(n, n + 32);
                 }
+              };
+              uint32_t va[2][32], vb[2][32];
+              ld64(0, va);
+#pragma unroll
+              for (int c = 0; c < BN; c += 128) {
+                tmem_ld_wait();
+                ld64(c + 64, vb);
+                emit(va, c);
+                tmem_ld_wait();
+                if (c + 128 < BN) ld64(c + 128, va); else release();
+                emit(vb, c + 64);
               }
             } else if constexpr (EPI == EPI_ROTARY) {
-              // two 64-wide heads per warp and tile: x0 = columns 0..31, x1 = columns 32..63 of a head.  All four
-              // 32-column accumulator slices are fetched up front; each head leaves as one pair of boxes.
-              constexpr int NHEAD = WARP_OUT_COLS / 64;
-              uint32_t v[2 * NHEAD][32];
-#pragma unroll
-              for (int ci = 0; ci < 2 * NHEAD; ++ci) tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, v[ci]);
-              tmem_ld_wait();
-#pragma unroll
-              for (int hd = 0; hd < NHEAD; ++hd) {
-                const int c = hd * 64;
-                const int n = n0 + wcol0 + c;
-                if (n >= p.N) break;
-                const uint32_t* v0 = v[2 * hd];
-                const uint32_t* v1 = v[2 * hd + 1];
-                pair_begin();
-                auto put2 = [&](int piece, uint4 lo, uint4 hi) { put(0, n, piece, lo); put(1, n + 32, piece, hi); };
+              // 64-wide heads, x0 = columns 0..31, x1 = columns 32..63 of a head.  A chunk is half a head:
+              // 16 columns of x0 and the matching 16 of x1, i.e. two pieces of each of the head's two boxes.
+              auto ldh = [&](int c, int hh, uint32_t (&x0)[16], uint32_t (&x1)[16]) {
+                tmem_ld_32x32b_x16(t_row + c + hh * 16, x0);
+                tmem_ld_32x32b_x16(t_row + c + hh * 16 + 32, x1);
+              };
+              // c = accumulator column of the head, hh = which half of x0 / x1 (a compile-time constant at each call)
+              auto emit = [&](const uint32_t (&v0)[16], const uint32_t (&v1)[16], int c, int hh) {
+                const int n = n0 + c;
+                if (n >= p.N) return;
+                if (hh == 0) pair_begin();
+                const float* s0 = sc + c + hh * 16;
+                const float* s1 = s0 + 32;
                 if (n < p.rot_cols) {
 #pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    const ulonglong2 a_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
-                    const ulonglong2 a_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
-                    const ulonglong2 b_lo = *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j);
-                    const ulonglong2 b_hi = *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j + 4);
-                    const uint64_t sb0[4] = {a_lo.x, a_lo.y, a_hi.x, a_hi.y};
-                    const uint64_t sb1[4] = {b_lo.x, b_lo.y, b_hi.x, b_hi.y};
+                  for (int j = 0; j < 16; j += 8) {
+                    const float4 a_lo = *reinterpret_cast<const float4*>(s0 + j);
+                    const float4 a_hi = *reinterpret_cast<const float4*>(s0 + j + 4);
+                    const float4 b_lo = *reinterpret_cast<const float4*>(s1 + j);
+                    const float4 b_hi = *reinterpret_cast<const float4*>(s1 + j + 4);
+                    const float2 sb0[4] = {{a_lo.x, a_lo.y}, {a_lo.z, a_lo.w}, {a_hi.x, a_hi.y}, {a_hi.z, a_hi.w}};
+                    const float2 sb1[4] = {{b_lo.x, b_lo.y}, {b_lo.z, b_lo.w}, {b_hi.x, b_hi.y}, {b_hi.z, b_hi.w}};
                     uint32_t o0[4], o1[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                      const uint64_t x0 = dequant2<KIND>(v0[j + 2 * i], v0[j + 2 * i + 1], sa2, sb0[i]);
-                      const uint64_t x1 = dequant2<KIND>(v1[j + 2 * i], v1[j + 2 * i + 1], sa2, sb1[i]);
-                      const uint64_t c2 = cs2[(j >> 1) + i], s2 = sn2[(j >> 1) + i];
+                      const float2 x0 = dequant2<KIND>(v0[j + 2 * i], v0[j + 2 * i + 1], sa2, sb0[i]);
+                      const float2 x1 = dequant2<KIND>(v1[j + 2 * i], v1[j + 2 * i + 1], sa2, sb1[i]);
+                      const float2 c2 = cs2[hh * 8 + (j >> 1) + i], s2 = sn2[hh * 8 + (j >> 1) + i];
                       // Separately rounded products and sums: reproducible bit for bit on a CPU.  The final
                       // add / subtract is scalar on purpose: a packed multiply feeding a packed add was seen
                       // to be contracted into a fused multiply-add, which rounds once instead of twice.
-                      float p0, p1, q0, q1, r0, r1, t0, t1;
-                      upk2(fmul2(x0, c2), p0, p1); upk2(fmul2(x1, s2), q0, q1);
-                      upk2(fmul2(x0, s2), r0, r1); upk2(fmul2(x1, c2), t0, t1);
-                      o0[i] = pack_half2(__fsub_rn(p0, q0), __fsub_rn(p1, q1));
-                      o1[i] = pack_half2(__fadd_rn(r0, t0), __fadd_rn(r1, t1));
+                      const float2 pa = fmul2(x0, c2), qa = fmul2(x1, s2), ra = fmul2(x0, s2), ta = fmul2(x1, c2);
+                      o0[i] = pack_half2(__fsub_rn(pa.x, qa.x), __fsub_rn(pa.y, qa.y));
+                      o1[i] = pack_half2(__fadd_rn(ra.x, ta.x), __fadd_rn(ra.y, ta.y));
                     }
-                    put2(j >> 3, make_uint4(o0[0], o0[1], o0[2], o0[3]), make_uint4(o1[0], o1[1], o1[2], o1[3]));
+                    put(0, n, hh * 2 + (j >> 3), make_uint4(o0[0], o0[1], o0[2], o0[3]));
+                    put(1, n + 32, hh * 2 + (j >> 3), make_uint4(o1[0], o1[1], o1[2], o1[3]));
                   }
                 } else {
 #pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    put2(j >> 3,
-                         dequant_piece<KIND>(&v0[j], sa2, *reinterpret_cast<const ulonglong2*>(sc + c + j),
-                                             *reinterpret_cast<const ulonglong2*>(sc + c + j + 4)),
-                         dequant_piece<KIND>(&v1[j], sa2, *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j),
-                                             *reinterpret_cast<const ulonglong2*>(sc + c + 32 + j + 4)));
+                  for (int j = 0; j < 16; j += 8) {
+                    put(0, n, hh * 2 + (j >> 3),
+                        dequant_piece<KIND>(&v0[j], sa2, *reinterpret_cast<const float4*>(s0 + j),
+                                            *reinterpret_cast<const float4*>(s0 + j + 4)));
+                    put(1, n + 32, hh * 2 + (j >> 3),
+                        dequant_piece<KIND>(&v1[j], sa2, *reinterpret_cast<const float4*>(s1 + j),
+                                            *reinterpret_cast<const float4*>(s1 + j + 4)));
                   }
                 }
-                pair_end(n, n + 32);
+                if (hh == 1) pair_end(n, n + 32);
+              };
+              uint32_t xa0[16], xa1[16], xb0[16], xb1[16];
+              ldh(0, 0, xa0, xa1);
+              // one head per trip and not unrolled: the body is large, and a fully unrolled tile does not fit
+              // the instruction cache (the warps then stall on instruction fetch)
+#pragma unroll 1
+              for (int c = 0; c < BN; c += 64) {
+                tmem_ld_wait();
+                ldh(c, 1, xb0, xb1);
+                emit(xa0, xa1, c, 0);
+                tmem_ld_wait();
+                if (c + 64 < BN) ldh(c + 64, 0, xa0, xa1); else release();
+                emit(xb0, xb1, c, 1);
               }
-            } else {   // EPI_SILU: gate at accumulator column c, up at BN/2 + c
-              constexpr int NSUB = WARP_OUT_COLS / 32;      // 2 boxes = one pair
-              uint32_t g[NSUB][32], u[NSUB][32];
+            } else {   // EPI_SILU: gate at accumulator column c, up at BN/2 + c; a chunk is one 32-column output box
+              auto ldgu = [&](int c, uint32_t (&g)[32], uint32_t (&u)[32]) {
+                tmem_ld_32x32b_x32(t_row + c, g);
+                tmem_ld_32x32b_x32(t_row + BN / 2 + c, u);
+              };
+              auto emit = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c, int which) {
+                const int n = n0 + c;
 #pragma unroll
-              for (int ci = 0; ci < NSUB; ++ci) {
-                tmem_ld_32x32b_x32(t_row + wcol0 + ci * 32, g[ci]);
-                tmem_ld_32x32b_x32(t_row + BN / 2 + wcol0 + ci * 32, u[ci]);
-              }
-              tmem_ld_wait();
-              const int n = n0 + wcol0;
-              if (n < p.N) {
-                pair_begin();
+                for (int j = 0; j < 32; j += 8) {
+                  const float4 g_lo = *reinterpret_cast<const float4*>(sc + c + j);
+                  const float4 g_hi = *reinterpret_cast<const float4*>(sc + c + j + 4);
+                  const float4 u_lo = *reinterpret_cast<const float4*>(sc + BN / 2 + c + j);
+                  const float4 u_hi = *reinterpret_cast<const float4*>(sc + BN / 2 + c + j + 4);
+                  const float2 sg[4] = {{g_lo.x, g_lo.y}, {g_lo.z, g_lo.w}, {g_hi.x, g_hi.y}, {g_hi.z, g_hi.w}};
+                  const float2 su[4] = {{u_lo.x, u_lo.y}, {u_lo.z, u_lo.w}, {u_hi.x, u_hi.y}, {u_hi.z, u_hi.w}};
+                  uint32_t o[4];
 #pragma unroll
-                for (int h = 0; h < NSUB; ++h) {
-                  const int c = h * 32;
-#pragma unroll
-                  for (int j = 0; j < 32; j += 8) {
-                    const ulonglong2 g_lo = *reinterpret_cast<const ulonglong2*>(sc + c + j);
-                    const ulonglong2 g_hi = *reinterpret_cast<const ulonglong2*>(sc + c + j + 4);
-                    const ulonglong2 u_lo = *reinterpret_cast<const ulonglong2*>(sc + 64 + c + j);
-                    const ulonglong2 u_hi = *reinterpret_cast<const ulonglong2*>(sc + 64 + c + j + 4);
-                    const uint64_t sg[4] = {g_lo.x, g_lo.y, g_hi.x, g_hi.y};
-                    const uint64_t su[4] = {u_lo.x, u_lo.y, u_hi.x, u_hi.y};
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                      float g0, g1;
-                      upk2(dequant2<KIND>(g[h][j + 2 * i], g[h][j + 2 * i + 1], sa2, sg[i]), g0, g1);
-                      const uint64_t up = dequant2<KIND>(u[h][j + 2 * i], u[h][j + 2 * i + 1], sa2, su[i]);
-                      // silu(gate) = gate / (1 + exp(-gate)); exp and the division use the fast hardware approximations
-                      const uint64_t sl = pk2(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
-                      o[i] = pack_half2_from(fmul2(sl, up));
-                    }
-                    put(h, n + h * 32, j >> 3, make_uint4(o[0], o[1], o[2], o[3]));
+                  for (int i = 0; i < 4; ++i) {
+                    const float2 gv = dequant2<KIND>(g[j + 2 * i], g[j + 2 * i + 1], sa2, sg[i]);
+                    const float2 up = dequant2<KIND>(u[j + 2 * i], u[j + 2 * i + 1], sa2, su[i]);
+                    // silu(gate) = gate / (1 + exp(-gate)); exp and the division use the fast hardware approximations
+                    const float2 sl = pk2(__fdividef(gv.x, 1.0f + __expf(-gv.x)), __fdividef(gv.y, 1.0f + __expf(-gv.y)));
+                    o[i] = pack_half2_from(fmul2(sl, up));
                   }
+                  put(which, n, j >> 3, make_uint4(o[0], o[1], o[2], o[3]));
                 }
-                pair_end(n, n + 32);
+              };
+              uint32_t ga[32], ua[32], gb[32], ub[32];
+              ldgu(0, ga, ua);
+#pragma unroll
+              for (int c = 0; c < BN / 2; c += 64) {
+                const bool live = n0 + c < p.N;
+                tmem_ld_wait();
+                ldgu(c + 32, gb, ub);
+                if (live) { pair_begin(); emit(ga, ua, c, 0); }
+                tmem_ld_wait();
+                if (c + 64 < BN / 2) ldgu(c + 64, ga, ua); else release();
+                if (live) { emit(gb, ub, c + 32, 1); pair_end(n0 + c, n0 + c + 32); }
               }
             }
           };
           if (p.direct_store) run_tile(true_tag{}); else run_tile(false_tag{});
         }
+      } else {
+        release();
       }
-      // hand the accumulator stage back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[as]);
     }
     if (lane == 0) tma_store_wait_all<0>();
   }

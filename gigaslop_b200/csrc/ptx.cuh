@@ -25,10 +25,7 @@ constexpr unsigned int ST_TIMEOUT_LSTM     = 1u << 3;
 constexpr long long kDefaultSpinBudget = 2000000000ll;   // ~1 s of SM clocks
 // Upper bound (ns) a try_wait may keep the thread suspended before it returns to the polling loop; the
 // hardware wakes it as soon as the phase completes, so a waiting role costs almost no issue slots.
-#ifndef GSB_TRYWAIT_NS
-#define GSB_TRYWAIT_NS 20000
-#endif
-constexpr unsigned int kTryWaitSuspendNs = GSB_TRYWAIT_NS;
+constexpr unsigned int kTryWaitSuspendNs = 20000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -67,16 +64,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-#if GSB_TRYWAIT_NS == 0
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-#endif
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -255,41 +242,46 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---- packed fp32 pairs (sm_100 f32x2 pipe): each op is two IEEE round-to-nearest results ---------
-__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
-  uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r;
-}
-__device__ __forceinline__ void upk2(uint64_t r, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r));
-}
-__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
-#ifdef GSB_NO_F32X2      // build switch for measuring the packed pipe against two scalar multiplies
-  float a0, a1, b0, b1; upk2(a, a0, a1); upk2(b, b0, b1);
-  return pk2(__fmul_rn(a0, b0), __fmul_rn(a1, b1));
-#else
-  uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
-#endif
-}
-__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
-  uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
-}
-__device__ __forceinline__ uint64_t fsub2(uint64_t a, uint64_t b) {
-  uint64_t d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
-}
-__device__ __forceinline__ uint32_t pack_half2_from(uint64_t v) {
-  float lo, hi; upk2(v, lo, hi);
-#ifdef GSB_ABL_NOPACK
-  return __float_as_uint(lo) ^ __float_as_uint(hi);
-#endif
-  __half2 h = __floats2half2_rn(lo, hi);
+// The compiler intrinsics are used rather than inline PTX so that register pairs are allocated by the
+// compiler (64-bit inline-asm operands cost extra moves) and nothing is contracted into a fused multiply-add.
+__device__ __forceinline__ float2 pk2(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fsub2(float2 a, float2 b) { return __fadd2_rn(a, make_float2(-b.x, -b.y)); }
+__device__ __forceinline__ uint32_t pack_half2_from(float2 v) {
+  __half2 h = __float22half2_rn(v);
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // ---- misc -----------------------------------------------------------------------
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Barrier over `nthreads` threads that also ANDs a predicate: every participant gets the same answer,
+// so a group of warps can agree to leave a loop together (nobody is left waiting at a later barrier).
+__device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %3, 0;\n\t"
+      "bar.red.and.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
