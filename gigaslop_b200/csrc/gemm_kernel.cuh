@@ -24,14 +24,14 @@
 //   warp 1      TMEM owner + single-thread tcgen05.mma issue
 //   warps 2,3   idle; they complete the first warpgroup, which gives its registers to the epilogue
 //               (setmaxnreg: 56 per thread for warps 0-3, 224 for the two epilogue warpgroups)
-//   warps 4..11 epilogue, two sets of four warps that take alternate tiles: tcgen05.ld (thread =
-//               accumulator row, next chunk in flight during the math of the current) -> math ->
-//               swizzled smem staging -> TMA store (per-warp 32 x 32 fp16 boxes, issued in pairs)
+//   warps 4..11 epilogue, free-running (no barrier between them): tcgen05.ld (thread = accumulator row,
+//               next chunk in flight during the math of the current) -> math -> swizzled smem staging
+//               -> TMA store (per-warp 32 x 32 fp16 boxes, issued in pairs)
 //
-// Two 256-column accumulator stages fill the 512 TMEM columns (stage s belongs to epilogue set s), so
-// the epilogue of tile i overlaps the MMAs of tile i+1 and the epilogue of tile i-1.  The epilogue reads
-// nothing from global memory inside its column loop: per-channel scales sit in shared memory, the
-// per-token scale and the next tile's channel scales are fetched one tile ahead.
+// Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue of tile i overlaps the
+// MMAs of tile i+1; a warp returns its part of a stage as soon as its last chunk is in registers.  The
+// epilogue reads nothing from global memory inside its column loop: per-channel scales sit in shared
+// memory, the per-token scale and the next tile's channel scales are fetched one tile ahead.
 #pragma once
 #include <cuda_fp8.h>
 
@@ -49,7 +49,7 @@ constexpr int BK = 128;            // K bytes per smem stage (= one 128B swizzle
 constexpr int UMMA_K = 32;         // K bytes per tcgen05.mma for 8-bit kinds
 constexpr int ACC_STAGES = 2;
 constexpr int TMEM_COLS = 512;
-constexpr int EPI_WARPS = 8;                            // two sets of 4 warps; set s drains accumulator stage s
+constexpr int EPI_WARPS = 8;                            // warp e: TMEM lane quarter e % 4, column half e / 4
 constexpr int FRONT_WARPS = 4;                          // warp 0 producer, warp 1 MMA, warps 2-3 idle (one warpgroup)
 constexpr int GEMM_THREADS = 32 * (FRONT_WARPS + EPI_WARPS);
 constexpr int FRONT_REGS = 56;                          // register budgets after setmaxnreg (per thread)
@@ -61,12 +61,12 @@ constexpr int NSTAGE = 3;                               // ring depth of every s
 constexpr int OUT_BOX_ROWS = 32;
 constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
 constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
-constexpr int SCALE_SET_FLOATS = BN;                    // per-channel scales of one tile, indexed by accumulator column
+constexpr int SCALE_SET_BYTES = 512;                    // 128 fp32 channel scales: the columns one epilogue warp handles
 
 // Shared-memory map (offsets from a 1 KiB-aligned base).
-//   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales][barriers]
-//   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales][barriers]
-//   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 4 x 2 KiB][scales][barriers]
+//   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales 8 x 512 B][barriers]
+//   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales 2 x 512 B][barriers]
+//   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 3 x 2 KiB][scales 8 x 512 B][barriers]
 template <int SCHED>
 struct SmemMap {
   static constexpr int RES_BYTES = SCHED == SCHED_WRES ? RES_MAX_KBLOCKS * B_STAGE_BYTES
@@ -74,10 +74,11 @@ struct SmemMap {
   static constexpr int STAGE_BYTES = SCHED == SCHED_WRES ? A_STAGE_BYTES
                                    : SCHED == SCHED_ARES ? B_STAGE_BYTES : A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_OFF = RES_BYTES;
-  static constexpr int OUT_BUFS = SCHED == SCHED_WRES ? 3 : 4;   // 32x32 fp16 staging boxes per epilogue warp
+  static constexpr int OUT_BUFS = SCHED == SCHED_STREAM ? 4 : 3;   // 32x32 fp16 staging boxes per epilogue warp
+  static constexpr int SCALE_SETS = SCHED == SCHED_WRES ? 2 : EPI_WARPS;   // shared per column half, or private per warp
   static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
-  static constexpr int BAR_OFF = SCALE_OFF + 2 /*sets*/ * SCALE_SET_FLOATS * 4;
+  static constexpr int BAR_OFF = SCALE_OFF + SCALE_SETS * SCALE_SET_BYTES;
   static constexpr int USED = BAR_OFF + 256;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
@@ -143,29 +144,36 @@ __device__ __forceinline__ uint4 dequant_piece(const uint32_t* v, float2 sa2, fl
 struct true_tag { static constexpr bool value = true; };
 struct false_tag { static constexpr bool value = false; };
 
-// Tile -> (row block, column block) for this CTA's `it`-th tile.  Returns false past the end.
+// A CTA's walk over its tiles (row block m, column block n), advanced without divisions:
 //   WRES:               fixed column block, row blocks group, group + n_groups, ...
 //   ARES, STREAM m_major: row blocks cta, cta + grid, ...; all column blocks of one before the next
 //   STREAM:             tiles cta, cta + grid, ... with the column block fastest
 template <int SCHED>
-__device__ __forceinline__ bool tile_coords(const GemmParams& p, int it, int& m_blk, int& n_blk) {
-  if constexpr (SCHED == SCHED_WRES) {
-    n_blk = blockIdx.x % p.n_blocks;
-    m_blk = blockIdx.x / p.n_blocks + it * p.n_groups;
-    return m_blk < p.m_blocks;
-  } else {
-    if (SCHED == SCHED_ARES || p.m_major) {
-      n_blk = it % p.n_blocks;
-      m_blk = blockIdx.x + (it / p.n_blocks) * gridDim.x;
-      return m_blk < p.m_blocks;
+struct TileWalk {
+  int m, n;
+  int dm, dn;      // STREAM with the column block fastest: what one step of `grid` tiles adds
+  __device__ __forceinline__ void start(const GemmParams& p) {
+    dm = dn = 0;
+    if constexpr (SCHED == SCHED_WRES) {
+      n = blockIdx.x % p.n_blocks; m = blockIdx.x / p.n_blocks;
+    } else {
+      if (SCHED == SCHED_ARES || p.m_major) { n = 0; m = blockIdx.x; }
+      else {
+        m = blockIdx.x / p.n_blocks; n = blockIdx.x % p.n_blocks;
+        dm = gridDim.x / p.n_blocks; dn = gridDim.x % p.n_blocks;
+      }
     }
-    const long long t = (long long)blockIdx.x + (long long)it * gridDim.x;
-    if (t >= (long long)p.m_blocks * p.n_blocks) return false;
-    m_blk = (int)(t / p.n_blocks);
-    n_blk = (int)(t % p.n_blocks);
-    return true;
   }
-}
+  __device__ __forceinline__ bool valid(const GemmParams& p) const { return m < p.m_blocks; }
+  __device__ __forceinline__ void next(const GemmParams& p) {
+    if constexpr (SCHED == SCHED_WRES) {
+      m += p.n_groups;
+    } else {
+      if (SCHED == SCHED_ARES || p.m_major) { if (++n == p.n_blocks) { n = 0; m += gridDim.x; } }
+      else { m += dm; n += dn; if (n >= p.n_blocks) { n -= p.n_blocks; ++m; } }
+    }
+  }
+};
 
 template <int KIND, int EPI, int SCHED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -203,7 +211,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS / 2); }
+    for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
     for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], 1); mbar_init(&res_empty[s], 1); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -235,13 +243,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &res_full[0], kb * BK, n1);
         }
       }
-      int m_blk, n_blk;
       uint32_t rph = 0;                       // ARES: phase of the resident-A barriers, flips per row block
-      for (int it = 0; ok && !(p.ablate & 4) && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
+      int rot = 0;                            // WRES: it % n_blocks, which CTA of a group asks for the L2 prefetch
+      TileWalk<SCHED> tw; tw.start(p);
+      for (int it = 0; ok && !(p.ablate & 4) && tw.valid(p); ++it, tw.next(p)) {
+        const int m_blk = tw.m, n_blk = tw.n;
         const int m0 = m_blk * BM;
         const int n0 = n_blk * OUT_COLS_PER_TILE;
         const int n1 = DUAL ? n0 : n0 + BN / 2;
         if (ARES && n_blk == 0 && it != 0) rph ^= 1;
+        // A comes from HBM with a latency the small ring cannot cover: ask for it in L2 well ahead.
+        //   WRES: the row block two tiles on (one CTA of the group asks, the others find it in L2)
+        //   ARES: this CTA's next row block, at the start of the current one
+        if constexpr (WRES) {
+          const int pm = m_blk + 2 * p.n_groups;
+          if (pm < p.m_blocks && rot == n_blk)
+            for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, pm * BM);
+          if (++rot == p.n_blocks) rot = 0;
+        } else if constexpr (ARES) {
+          if (n_blk == 0 && m_blk + (int)gridDim.x < p.m_blocks)
+            for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, (m_blk + (int)gridDim.x) * BM);
+        }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if constexpr (ARES) {
             if (n_blk == 0) {                 // new row block: refill this K piece of A once its last reader retired
@@ -284,9 +306,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200, budget);
         tc_fence_after();
       }
-      int m_blk, n_blk;
       uint32_t rph = 0;
-      for (int it = 0; ok && tile_coords<SCHED>(p, it, m_blk, n_blk); ++it) {
+      TileWalk<SCHED> tw; tw.start(p);
+      for (int it = 0; ok && tw.valid(p); ++it, tw.next(p)) {
+        const int n_blk = tw.n;
         const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as, budget)) { ok = false; break; }
         tc_fence_after();
@@ -323,52 +346,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
     // ------------------------------ epilogue ----------------------------------
-    // Two sets of four warps.  Set s owns accumulator stage s, i.e. this CTA's tiles s, s + 2, ...: while one
-    // set converts and stores a tile the other is already reading the next one, so TMEM reads, arithmetic
-    // and output stores of neighbouring tiles overlap instead of running in phase.  A warp covers the 32
-    // rows of its TMEM lane quarter and all 256 accumulator columns, in chunks: the TMEM load of chunk i+1
-    // is in flight during the arithmetic of chunk i, and the stage goes back to the MMA warp as soon as the
-    // last chunk sits in registers.
+    // Eight free-running warps.  Warp e reads TMEM lane quarter e % 4 (32 rows) and the column half e / 4
+    // of every tile, in chunks: the TMEM load of chunk i+1 is in flight during the arithmetic of chunk i,
+    // and the warp gives the accumulator stage back as soon as its last chunk sits in registers.  Warps
+    // never synchronise with one another: each keeps its own copy of the channel scales it needs.
     const int e = warp - FRONT_WARPS;      // 0..7
     const int q = warp & 3;                // TMEM lane quarter this warp may read
-    const int set = e >> 2;                // accumulator stage drained by this warp
-    const uint32_t set_bar = 1 + set;      // named barrier of the set (barrier 0 is __syncthreads)
-    const int tset = q * 32 + lane;        // thread index inside the set
+    const int half = e >> 2;               // column half of the tile handled by this warp
+    constexpr int WACC = BN / 2;                       // accumulator columns per warp and tile (dual: 64 gate + 64 up)
+    constexpr int WOUT = OUT_COLS_PER_TILE / 2;        // output columns per warp and tile
+    const int wout0 = half * WOUT;                     // first output column of this warp inside the tile
+    const int acol0 = DUAL ? half * (BN / 4) : half * WACC;   // its first accumulator column (dual: of the gate part; up = + BN/2)
     uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's staging boxes
-    float* sc = scale_base + set * SCALE_SET_FLOATS;              // this set's per-channel scales, by accumulator column
+    // channel scales of this warp's columns, indexed by local column (dual: 64 gate | 64 up).  A weight-
+    // stationary CTA never changes column block: the four warps of a half then share one copy, which each of
+    // them writes (identical values) before its first tile.  Otherwise every warp has a private copy.
+    float* sc = scale_base + (WRES ? half : e) * WACC;
     int obuf = 0;
-    int m_blk, n_blk;
     // per-row state, fetched once per row block and kept in registers across its column blocks; the token
-    // scale and the channel scales of the set's NEXT tile are fetched while the current tile is processed
+    // scale and the channel scales of the NEXT tile are fetched while the current tile is processed
     float sa = 0.f, sa_next = 0.f;
-    float2 sb_next = make_float2(0.f, 0.f);
-    float2 sn2[16], cs2[16];             // sin / cos row of this thread's token as fp32 pairs
+    float4 sb_next = make_float4(0.f, 0.f, 0.f, 0.f);
+    float2 sn2[16], cs2[16];               // sin / cos row of this thread's token as fp32 pairs
     int cur_m_blk = -1;
     uint32_t stg_off[4];                   // byte offsets of the 4 pieces of this thread's row in a swizzled staging box
 #pragma unroll
     for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
 
-    // channel scales of accumulator columns 2*tset, 2*tset+1 of the tile whose first output column is n0
-    // (dual GEMM: accumulator columns 0..127 are gate, 128..255 up, both for output columns n0..n0+127)
-    auto fetch_scales = [&](int n0) -> float2 {
-      int c = 2 * tset;
+    // channel scales of local columns 4*lane .. 4*lane+3 for the tile whose first output column is n0
+    auto fetch_scales = [&](int n0) -> float4 {
+      int lc = 4 * lane;
       const float* src = p.scale_b0;
-      if constexpr (DUAL) { if (c >= BN / 2) { c -= BN / 2; src = p.scale_b1; } }
-      const int n = n0 + c;
-      if (n + 2 > p.N) return make_float2(0.f, 0.f);
-      if (!src) return make_float2(1.f, 1.f);                            // no per-channel scale
-      if (p.scale_b_scalar) { const float v = __ldg(src); return make_float2(v, v); }
-      return __ldg(reinterpret_cast<const float2*>(src + n));
+      if constexpr (DUAL) { if (lc >= WACC / 2) { lc -= WACC / 2; src = p.scale_b1; } }
+      const int n = n0 + wout0 + lc;
+      if (n + 4 > p.N) return make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!src) return make_float4(1.f, 1.f, 1.f, 1.f);                    // no per-channel scale
+      if (p.scale_b_scalar) { const float v = ldg_f_here(src); return make_float4(v, v, v, v); }
+      return ldg_f4_here(src + n);
     };
+    TileWalk<SCHED> tw; tw.start(p);
     if constexpr (EPI != EPI_I32) {
-      if (tile_coords<SCHED>(p, set, m_blk, n_blk)) {
-        const int r = m_blk * BM + q * 32 + lane;
+      if (tw.valid(p)) {
+        const int r = tw.m * BM + q * 32 + lane;
         if (r < p.M) sa_next = p.scale_a ? __ldg(p.scale_a + r) : 1.f;
-        sb_next = fetch_scales(n_blk * OUT_COLS_PER_TILE);
+        sb_next = fetch_scales(tw.n * OUT_COLS_PER_TILE);
       }
     }
-    for (int it = set; tile_coords<SCHED>(p, it, m_blk, n_blk); it += 2) {
-      const uint32_t aph = (it >> 1) & 1;
+    for (int it = 0; tw.valid(p); ++it) {
+      const int m_blk = tw.m, n_blk = tw.n;
+      tw.next(p);                            // tw is now the NEXT tile
+      const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
       const int m0 = m_blk * BM;
       const int n0 = n_blk * OUT_COLS_PER_TILE;
       const int row_base = m0 + q * 32;
@@ -392,56 +419,63 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
           }
         }
-        if (!WRES || it == set) {          // a weight-stationary CTA keeps one column block: its scales never change
-          // every warp of the set has passed its last read of the previous tile's scales
-          if (it != set) named_barrier_sync(set_bar, 128);
-          *reinterpret_cast<float2*>(sc + 2 * tset) = sb_next;
+        if (!WRES || it == 0) {
+          __syncwarp();                                   // every lane is past its reads of the previous tile's scales
+          *reinterpret_cast<float4*>(sc + 4 * lane) = sb_next;
+          __syncwarp();
         }
-        int nm, nn;
-        if (tile_coords<SCHED>(p, it + 2, nm, nn)) {
+        if (tw.valid(p)) {
+          const int nm = tw.m, nn = tw.n;
           if (nm != m_blk) {
             const int r = nm * BM + q * 32 + lane;
-            sa_next = (r < p.M) ? (p.scale_a ? __ldg(p.scale_a + r) : 1.f) : 0.f;
+            sa_next = (r < p.M) ? (p.scale_a ? ldg_f_here(p.scale_a + r) : 1.f) : 0.f;
           }
           if (!WRES) sb_next = fetch_scales(nn * OUT_COLS_PER_TILE);
         }
       }
 
-      // The set agrees on the outcome of the bounded wait, so it either works on or leaves as a whole and
-      // no warp is left behind at a later barrier; the same barrier publishes the scales written above.
-      const bool got = mbar_wait(&acc_full[set], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | set, budget);
-      if (!named_barrier_and(set_bar, 128, got)) break;
+      // warp-uniform outcome of the bounded wait: the tcgen05.ld below needs the whole warp
+      const bool got = mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as, budget);
+      uint32_t agreed = __all_sync(0xffffffffu, got) ? 1u : 0u;
+      if (!agreed) break;
+      asm volatile("" : "+r"(agreed));   // opaque from here on: the scale address below must stay dependent on the wait
       tc_fence_after();
-      const uint32_t t_row = tmem_base + set * BN + ((uint32_t)(q * 32) << 16);
+      // Channel scales are read with loads the compiler may move across the staging stores below (plain
+      // loads would be kept in order with every store to shared memory).  The address depends on the
+      // outcome of the wait, so no read can move above it, hence not above the scale stores either.
+      const uint32_t sc_addr = smem_u32(sc) + ((agreed - 1u) << 2);
+      auto scq = [&](int i) { return lds_f4_ro(sc_addr + i * 4); };      // scales of local columns i..i+3
+      auto scp = [&](int i) { return lds_f2_ro(sc_addr + i * 4); };      // ... i, i+1
+      const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16) + acol0;
       // hand the accumulator stage back to the MMA warp: called once per tile, right after the wait that
       // brought this warp's last accumulator chunk into registers
       auto release = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[set]);
+        if (lane == 0) mbar_arrive(&acc_empty[as]);
       };
 
       if (row_base < p.M && !(p.ablate & 2)) {
         if constexpr (EPI == EPI_I32) {
           // raw accumulators, direct 16-byte stores
-          auto emit = [&](const uint32_t (&v)[32], int col) {
+          auto emit = [&](const uint32_t (&v)[32], int c) {
             if (row_ok) {
-              int32_t* dst = reinterpret_cast<int32_t*>(p.C) + (long long)row * p.ldc + n0 + col;
+              const int n = n0 + wout0 + c;
+              int32_t* dst = reinterpret_cast<int32_t*>(p.C) + (long long)row * p.ldc + n;
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
-                if (n0 + col + j + 4 <= p.N)
-                  *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (n + j + 4 <= p.N) *reinterpret_cast<uint4*>(dst + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
             }
           };
           uint32_t va[32], vb[32];
           tmem_ld_32x32b_x32(t_row, va);
 #pragma unroll
-          for (int c = 0; c < BN; c += 64) {
+          for (int c = 0; c < WACC; c += 64) {
             tmem_ld_wait();
             tmem_ld_32x32b_x32(t_row + c + 32, vb);
             emit(va, c);
             tmem_ld_wait();
-            if (c + 64 < BN) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
+            if (c + 64 < WACC) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
             emit(vb, c + 32);
           }
         } else if constexpr (EPI == EPI_SILU_MX) {
@@ -450,16 +484,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           // A thread holds whole 32-column blocks of its row, so the block maximum needs no exchange.
           const float2 sa2 = pk2(sa, sa);
           auto emit = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c) {
-            const int n = n0 + c;
+            const int n = n0 + wout0 + c;
             if (n + 32 <= p.N) {
               float o[32];
               float amax = 0.f;
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
-                const float2 sg = *reinterpret_cast<const float2*>(sc + c + j);
-                const float2 su = *reinterpret_cast<const float2*>(sc + BN / 2 + c + j);
-                const float2 gv = dequant2<KIND>(g[j], g[j + 1], sa2, sg);
-                const float2 uv = dequant2<KIND>(u[j], u[j + 1], sa2, su);
+                const float2 gv = dequant2<KIND>(g[j], g[j + 1], sa2, scp(c + j));
+                const float2 uv = dequant2<KIND>(u[j], u[j + 1], sa2, scp(WACC / 2 + c + j));
                 o[j] = __fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x;
                 o[j + 1] = __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y;
                 amax = fmaxf(amax, fmaxf(fabsf(o[j]), fabsf(o[j + 1])));
@@ -485,21 +517,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           uint32_t ga[32], ua[32], gb[32], ub[32];
           tmem_ld_32x32b_x32(t_row, ga);
           tmem_ld_32x32b_x32(t_row + BN / 2, ua);
-#pragma unroll
-          for (int c = 0; c < BN / 2; c += 64) {
-            tmem_ld_wait();
-            tmem_ld_32x32b_x32(t_row + c + 32, gb);
-            tmem_ld_32x32b_x32(t_row + BN / 2 + c + 32, ub);
-            emit(ga, ua, c);
-            tmem_ld_wait();
-            if (c + 64 < BN / 2) {
-              tmem_ld_32x32b_x32(t_row + c + 64, ga);
-              tmem_ld_32x32b_x32(t_row + BN / 2 + c + 64, ua);
-            } else {
-              release();
-            }
-            emit(gb, ub, c + 32);
-          }
+          tmem_ld_wait();
+          tmem_ld_32x32b_x32(t_row + 32, gb);
+          tmem_ld_32x32b_x32(t_row + BN / 2 + 32, ub);
+          emit(ga, ua, 0);
+          tmem_ld_wait();
+          release();
+          emit(gb, ub, 32);
         } else {
           const float2 sa2 = pk2(sa, sa);
           // The body exists twice: the product path (swizzled staging + TMA store) and a diagnostic path
@@ -538,37 +562,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             };
 
             if constexpr (EPI == EPI_DEQUANT) {
-              // chunks of 64 columns = one pair of boxes
-              auto ld64 = [&](int col, uint32_t (&v)[2][32]) {
-                tmem_ld_32x32b_x32(t_row + col, v[0]);
-                tmem_ld_32x32b_x32(t_row + col + 32, v[1]);
+              // chunks of 32 columns = one box; two chunks leave as a pair
+              auto emit = [&](const uint32_t (&v)[32], int c, int which) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8)
+                  put(which, n0 + wout0 + c, j >> 3, dequant_piece<KIND>(&v[j], sa2, scq(c + j), scq(c + j + 4)));
               };
-              auto emit = [&](const uint32_t (&v)[2][32], int c) {
-                const int n = n0 + c;
-                if (n < p.N) {
-                  pair_begin();
+              uint32_t va[32], vb[32];
+              tmem_ld_32x32b_x32(t_row, va);
 #pragma unroll
-                  for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                      const float4 s_lo = *reinterpret_cast<const float4*>(sc + c + h * 32 + j);
-                      const float4 s_hi = *reinterpret_cast<const float4*>(sc + c + h * 32 + j + 4);
-                      put(h, n + h * 32, j >> 3, dequant_piece<KIND>(&v[h][j], sa2, s_lo, s_hi));
-                    }
-                  }
-                  pair_end(n, n + 32);
-                }
-              };
-              uint32_t va[2][32], vb[2][32];
-              ld64(0, va);
-#pragma unroll
-              for (int c = 0; c < BN; c += 128) {
+              for (int c = 0; c < WACC; c += 64) {
+                const int n = n0 + wout0 + c;
+                const bool live = n < p.N;
                 tmem_ld_wait();
-                ld64(c + 64, vb);
-                emit(va, c);
+                tmem_ld_32x32b_x32(t_row + c + 32, vb);
+                if (live) { pair_begin(); emit(va, c, 0); }
                 tmem_ld_wait();
-                if (c + 128 < BN) ld64(c + 128, va); else release();
-                emit(vb, c + 64);
+                if (c + 64 < WACC) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
+                if (live) { emit(vb, c + 32, 1); pair_end(n, n + 32); }
               }
             } else if constexpr (EPI == EPI_ROTARY) {
               // 64-wide heads, x0 = columns 0..31, x1 = columns 32..63 of a head.  A chunk is half a head:
@@ -577,20 +588,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 tmem_ld_32x32b_x16(t_row + c + hh * 16, x0);
                 tmem_ld_32x32b_x16(t_row + c + hh * 16 + 32, x1);
               };
-              // c = accumulator column of the head, hh = which half of x0 / x1 (a compile-time constant at each call)
+              // c = local column of the head, hh = which half of x0 / x1 (a compile-time constant at each call)
               auto emit = [&](const uint32_t (&v0)[16], const uint32_t (&v1)[16], int c, int hh) {
-                const int n = n0 + c;
+                const int n = n0 + wout0 + c;
                 if (n >= p.N) return;
                 if (hh == 0) pair_begin();
-                const float* s0 = sc + c + hh * 16;
-                const float* s1 = s0 + 32;
+                const int s0 = c + hh * 16;      // scale index of this half of x0; x1 is 32 columns on
+                const int s1 = s0 + 32;
                 if (n < p.rot_cols) {
 #pragma unroll
                   for (int j = 0; j < 16; j += 8) {
-                    const float4 a_lo = *reinterpret_cast<const float4*>(s0 + j);
-                    const float4 a_hi = *reinterpret_cast<const float4*>(s0 + j + 4);
-                    const float4 b_lo = *reinterpret_cast<const float4*>(s1 + j);
-                    const float4 b_hi = *reinterpret_cast<const float4*>(s1 + j + 4);
+                    const float4 a_lo = scq(s0 + j);
+                    const float4 a_hi = scq(s0 + j + 4);
+                    const float4 b_lo = scq(s1 + j);
+                    const float4 b_hi = scq(s1 + j + 4);
                     const float2 sb0[4] = {{a_lo.x, a_lo.y}, {a_lo.z, a_lo.w}, {a_hi.x, a_hi.y}, {a_hi.z, a_hi.w}};
                     const float2 sb1[4] = {{b_lo.x, b_lo.y}, {b_lo.z, b_lo.w}, {b_hi.x, b_hi.y}, {b_hi.z, b_hi.w}};
                     uint32_t o0[4], o1[4];
@@ -612,42 +623,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 } else {
 #pragma unroll
                   for (int j = 0; j < 16; j += 8) {
-                    put(0, n, hh * 2 + (j >> 3),
-                        dequant_piece<KIND>(&v0[j], sa2, *reinterpret_cast<const float4*>(s0 + j),
-                                            *reinterpret_cast<const float4*>(s0 + j + 4)));
-                    put(1, n + 32, hh * 2 + (j >> 3),
-                        dequant_piece<KIND>(&v1[j], sa2, *reinterpret_cast<const float4*>(s1 + j),
-                                            *reinterpret_cast<const float4*>(s1 + j + 4)));
+                    put(0, n, hh * 2 + (j >> 3), dequant_piece<KIND>(&v0[j], sa2, scq(s0 + j), scq(s0 + j + 4)));
+                    put(1, n + 32, hh * 2 + (j >> 3), dequant_piece<KIND>(&v1[j], sa2, scq(s1 + j), scq(s1 + j + 4)));
                   }
                 }
                 if (hh == 1) pair_end(n, n + 32);
               };
               uint32_t xa0[16], xa1[16], xb0[16], xb1[16];
               ldh(0, 0, xa0, xa1);
-              // one head per trip and not unrolled: the body is large, and a fully unrolled tile does not fit
-              // the instruction cache (the warps then stall on instruction fetch)
+              // one head per trip and not unrolled: the body is large, and more straight-line code than the
+              // instruction cache holds makes the warps stall on instruction fetch
 #pragma unroll 1
-              for (int c = 0; c < BN; c += 64) {
+              for (int c = 0; c < WACC; c += 64) {
                 tmem_ld_wait();
                 ldh(c, 1, xb0, xb1);
                 emit(xa0, xa1, c, 0);
                 tmem_ld_wait();
-                if (c + 64 < BN) ldh(c + 64, 0, xa0, xa1); else release();
+                if (c + 64 < WACC) ldh(c + 64, 0, xa0, xa1); else release();
                 emit(xb0, xb1, c, 1);
               }
-            } else {   // EPI_SILU: gate at accumulator column c, up at BN/2 + c; a chunk is one 32-column output box
-              auto ldgu = [&](int c, uint32_t (&g)[32], uint32_t (&u)[32]) {
-                tmem_ld_32x32b_x32(t_row + c, g);
-                tmem_ld_32x32b_x32(t_row + BN / 2 + c, u);
-              };
+            } else {   // EPI_SILU: gate at local column c, up at BN/2 accumulator columns on; a chunk is one 32-column output box
               auto emit = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c, int which) {
-                const int n = n0 + c;
+                const int n = n0 + wout0 + c;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
-                  const float4 g_lo = *reinterpret_cast<const float4*>(sc + c + j);
-                  const float4 g_hi = *reinterpret_cast<const float4*>(sc + c + j + 4);
-                  const float4 u_lo = *reinterpret_cast<const float4*>(sc + BN / 2 + c + j);
-                  const float4 u_hi = *reinterpret_cast<const float4*>(sc + BN / 2 + c + j + 4);
+                  const float4 g_lo = scq(c + j);
+                  const float4 g_hi = scq(c + j + 4);
+                  const float4 u_lo = scq(WACC / 2 + c + j);
+                  const float4 u_hi = scq(WACC / 2 + c + j + 4);
                   const float2 sg[4] = {{g_lo.x, g_lo.y}, {g_lo.z, g_lo.w}, {g_hi.x, g_hi.y}, {g_hi.z, g_hi.w}};
                   const float2 su[4] = {{u_lo.x, u_lo.y}, {u_lo.z, u_lo.w}, {u_hi.x, u_hi.y}, {u_hi.z, u_hi.w}};
                   uint32_t o[4];
@@ -663,17 +666,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 }
               };
               uint32_t ga[32], ua[32], gb[32], ub[32];
-              ldgu(0, ga, ua);
-#pragma unroll
-              for (int c = 0; c < BN / 2; c += 64) {
-                const bool live = n0 + c < p.N;
-                tmem_ld_wait();
-                ldgu(c + 32, gb, ub);
-                if (live) { pair_begin(); emit(ga, ua, c, 0); }
-                tmem_ld_wait();
-                if (c + 64 < BN / 2) ldgu(c + 64, ga, ua); else release();
-                if (live) { emit(gb, ub, c + 32, 1); pair_end(n0 + c, n0 + c + 32); }
-              }
+              const int n = n0 + wout0;
+              const bool live = n < p.N;
+              tmem_ld_32x32b_x32(t_row, ga);
+              tmem_ld_32x32b_x32(t_row + BN / 2, ua);
+              tmem_ld_wait();
+              tmem_ld_32x32b_x32(t_row + 32, gb);
+              tmem_ld_32x32b_x32(t_row + BN / 2 + 32, ub);
+              if (live) { pair_begin(); emit(ga, ua, 0, 0); }
+              tmem_ld_wait();
+              release();
+              if (live) { emit(gb, ub, 32, 1); pair_end(n, n + 32); }
             }
           };
           if (p.direct_store) run_tile(true_tag{}); else run_tile(false_tag{});

@@ -104,6 +104,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ---- TMA --------------------------------------------------------------------
+// Ask the TMA unit to bring one box of a tiled tensor into L2 (no shared-memory destination, no completion).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
@@ -271,7 +276,8 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthread
 }
 // Barrier over `nthreads` threads that also ANDs a predicate: every participant gets the same answer,
 // so a group of warps can agree to leave a loop together (nobody is left waiting at a later barrier).
-__device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t nthreads, bool pred) {
+// Returns 1 when every participant passed a true predicate, else 0.
+__device__ __forceinline__ uint32_t named_barrier_and(uint32_t id, uint32_t nthreads, bool pred) {
   uint32_t r;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
@@ -281,7 +287,33 @@ __device__ __forceinline__ bool named_barrier_and(uint32_t id, uint32_t nthreads
       : "=r"(r)
       : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
       : "memory");
-  return r != 0;
+  return r;
+}
+// Shared-memory reads the compiler may schedule freely: not volatile and without a memory clobber, so they
+// are not ordered against unrelated shared-memory stores.  Only for data that is read-only while the address
+// value is live; derive the address from the result of the synchronisation that published the data, which
+// keeps the reads behind it.
+// Read-only global loads that stay where they are written (volatile): used to start a load a whole tile
+// before its value is needed; the compiler would otherwise be free to sink it to the point of use.
+__device__ __forceinline__ float4 ldg_f4_here(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ldg_f_here(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float4 lds_f4_ro(uint32_t addr) {
+  float4 v;
+  asm("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float2 lds_f2_ro(uint32_t addr) {
+  float2 v;
+  asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
