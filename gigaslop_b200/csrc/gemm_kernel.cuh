@@ -61,12 +61,12 @@ constexpr int NSTAGE = 3;                               // ring depth of every s
 constexpr int OUT_BOX_ROWS = 32;
 constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
 constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
-constexpr int SCALE_SET_BYTES = 512;                    // 128 fp32 channel scales: the columns one epilogue warp handles
+constexpr int SCALE_BUF_BYTES = BN * 4;                 // channel scales of one tile, indexed by accumulator column (dual: gate | up)
 
 // Shared-memory map (offsets from a 1 KiB-aligned base).
-//   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales 8 x 512 B][barriers]
-//   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales 2 x 512 B][barriers]
-//   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 3 x 2 KiB][scales 8 x 512 B][barriers]
+//   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales 6 x 1 KiB][barriers]
+//   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales 1 KiB][barriers]
+//   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 3 x 2 KiB][scales 6 x 1 KiB][barriers]
 template <int SCHED>
 struct SmemMap {
   static constexpr int RES_BYTES = SCHED == SCHED_WRES ? RES_MAX_KBLOCKS * B_STAGE_BYTES
@@ -75,10 +75,15 @@ struct SmemMap {
                                    : SCHED == SCHED_ARES ? B_STAGE_BYTES : A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int RING_OFF = RES_BYTES;
   static constexpr int OUT_BUFS = SCHED == SCHED_STREAM ? 4 : 3;   // 32x32 fp16 staging boxes per epilogue warp
-  static constexpr int SCALE_SETS = SCHED == SCHED_WRES ? 2 : EPI_WARPS;   // shared per column half, or private per warp
+  // Channel-scale buffers, filled by the producer beside each tile's first K block.  A weight-stationary
+  // CTA keeps one column block, hence one buffer.  Otherwise tile j uses buffer j % 6: when the producer
+  // fills it again (tile j + 6) it holds a ring slot the MMA warp freed at most ceil(NSTAGE / k_blocks) <= 3
+  // tiles earlier, the MMA warp of tile t has been given the accumulator stage of tile t - 2 by every
+  // epilogue warp, and a warp that has released tile t - 2 is done with tile t - 3: 3 + 3 = 6.
+  static constexpr int SCALE_BUFS = SCHED == SCHED_WRES ? 1 : 6;
   static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
-  static constexpr int BAR_OFF = SCALE_OFF + SCALE_SETS * SCALE_SET_BYTES;
+  static constexpr int BAR_OFF = SCALE_OFF + SCALE_BUFS * SCALE_BUF_BYTES;
   static constexpr int USED = BAR_OFF + 256;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
@@ -219,6 +224,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (EPI != EPI_I32) prefetch_tmap(&tm_c);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  // Channel scales normally arrive by bulk copy from the producer; without a per-channel vector (none given,
+  // or one scalar for all columns) every buffer is filled with the constant once, here.
+  const bool copy_scales = EPI != EPI_I32 && p.scale_b0 != nullptr && !p.scale_b_scalar;
+  if (EPI != EPI_I32 && !copy_scales) {
+    const float v = p.scale_b0 ? __ldg(p.scale_b0) : 1.f;
+    for (int i = threadIdx.x; i < Map::SCALE_BUFS * BN; i += GEMM_THREADS) scale_base[i] = v;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -233,10 +245,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int s = 0; uint32_t ph = 0; bool ok = true;
+      // channel scales of the tile whose first output column is n0 -> buffer dst, bytes reported to bar
+      auto scale_bytes = [&](int n0) -> uint32_t {
+        return copy_scales ? (uint32_t)((DUAL ? 2 : 1) * min(OUT_COLS_PER_TILE, p.N - n0) * 4) : 0u;
+      };
+      auto load_scales = [&](float* dst, int n0, uint64_t* bar) {
+        if (!copy_scales) return;
+        const uint32_t bytes = (uint32_t)(min(OUT_COLS_PER_TILE, p.N - n0) * 4);
+        bulk_load(dst, p.scale_b0 + n0, bytes, bar);
+        if constexpr (DUAL) bulk_load(dst + BN / 2, p.scale_b1 + n0, bytes, bar);
+      };
+      int sbuf = 0;                           // scale buffer of the current tile
       if constexpr (WRES) {
         const int n0 = (blockIdx.x % p.n_blocks) * OUT_COLS_PER_TILE;
         const int n1 = DUAL ? n0 : n0 + BN / 2;
-        mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES);
+        mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES + scale_bytes(n0));
+        load_scales(scale_base, n0, &res_full[0]);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           uint8_t* sb = res_base + kb * B_STAGE_BYTES;
           tma_load_2d(sb, &tm_b0, &res_full[0], kb * BK, n0);
@@ -274,22 +298,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | s, budget)) { ok = false; break; }
           uint8_t* st = ring + s * Map::STAGE_BYTES;
+          const uint32_t sc_bytes = (!WRES && kb == 0) ? scale_bytes(n0) : 0u;   // the scales ride on the first K block
           if constexpr (WRES) {
             mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES);
             tma_load_2d(st, &tm_a, &full_bar[s], kb * BK, m0);
           } else if constexpr (ARES) {
-            mbar_arrive_expect_tx(&full_bar[s], B_STAGE_BYTES);
+            mbar_arrive_expect_tx(&full_bar[s], B_STAGE_BYTES + sc_bytes);
+            if (kb == 0) load_scales(scale_base + sbuf * BN, n0, &full_bar[s]);
             tma_load_2d(st, &tm_b0, &full_bar[s], kb * BK, n0);
             tma_load_2d(st + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
           } else {
             uint8_t* sb = st + A_STAGE_BYTES;
-            mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES);
+            mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES + sc_bytes);
+            if (kb == 0) load_scales(scale_base + sbuf * BN, n0, &full_bar[s]);
             tma_load_2d(st, &tm_a, &full_bar[s], kb * BK, m0);
             tma_load_2d(sb, &tm_b0, &full_bar[s], kb * BK, n0);
             tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
           }
           if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
+        if (!WRES && ++sbuf == Map::SCALE_BUFS) sbuf = 0;
       }
       if (!ok) {                       // give copies already in flight time to land before the CTA exits
         long long t0 = clock64();
@@ -358,38 +386,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int wout0 = half * WOUT;                     // first output column of this warp inside the tile
     const int acol0 = DUAL ? half * (BN / 4) : half * WACC;   // its first accumulator column (dual: of the gate part; up = + BN/2)
     uint8_t* out_buf = out_base + e * OUT_BUFS * OUT_BUF_BYTES;   // this warp's staging boxes
-    // channel scales of this warp's columns, indexed by local column (dual: 64 gate | 64 up).  A weight-
-    // stationary CTA never changes column block: the four warps of a half then share one copy, which each of
-    // them writes (identical values) before its first tile.  Otherwise every warp has a private copy.
-    float* sc = scale_base + (WRES ? half : e) * WACC;
     int obuf = 0;
+    int sbuf = 0;                          // channel-scale buffer of the current tile (the producer fills them in turn)
     // per-row state, fetched once per row block and kept in registers across its column blocks; the token
     // scale and the channel scales of the NEXT tile are fetched while the current tile is processed
     float sa = 0.f, sa_next = 0.f;
-    float4 sb_next = make_float4(0.f, 0.f, 0.f, 0.f);
     float2 sn2[16], cs2[16];               // sin / cos row of this thread's token as fp32 pairs
     int cur_m_blk = -1;
+    int trig_m_blk = -1;                   // row block whose sin / cos rows are in sn2 / cs2
+    bool trig_scaled = false;              // ... already multiplied by the token scale
     uint32_t stg_off[4];                   // byte offsets of the 4 pieces of this thread's row in a swizzled staging box
 #pragma unroll
     for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
 
-    // channel scales of local columns 4*lane .. 4*lane+3 for the tile whose first output column is n0
-    auto fetch_scales = [&](int n0) -> float4 {
-      int lc = 4 * lane;
-      const float* src = p.scale_b0;
-      if constexpr (DUAL) { if (lc >= WACC / 2) { lc -= WACC / 2; src = p.scale_b1; } }
-      const int n = n0 + wout0 + lc;
-      if (n + 4 > p.N) return make_float4(0.f, 0.f, 0.f, 0.f);
-      if (!src) return make_float4(1.f, 1.f, 1.f, 1.f);                    // no per-channel scale
-      if (p.scale_b_scalar) { const float v = ldg_f_here(src); return make_float4(v, v, v, v); }
-      return ldg_f4_here(src + n);
-    };
     TileWalk<SCHED> tw; tw.start(p);
     if constexpr (EPI != EPI_I32) {
       if (tw.valid(p)) {
         const int r = tw.m * BM + q * 32 + lane;
         if (r < p.M) sa_next = p.scale_a ? __ldg(p.scale_a + r) : 1.f;
-        sb_next = fetch_scales(tw.n * OUT_COLS_PER_TILE);
       }
     }
     for (int it = 0; tw.valid(p); ++it) {
@@ -407,30 +421,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (m_blk != cur_m_blk) {
           cur_m_blk = m_blk;
           sa = sa_next;
-          if constexpr (EPI == EPI_ROTARY) {
-            const int pos = row_ok ? (int)(((long long)row + p.row_offset) % p.seqlen) : 0;
-            const float4* s4 = reinterpret_cast<const float4*>(p.sin_tab + (long long)pos * 32);
-            const float4* c4 = reinterpret_cast<const float4*>(p.cos_tab + (long long)pos * 32);
+        }
+        if constexpr (EPI == EPI_ROTARY) {
+          // The angle rows cost 16 scattered 16-byte loads per thread.  Once this warp's columns lie past the
+          // rotated ones (the V part of a QKV projection, walked last), the rows of the NEXT row block are
+          // fetched already, a tile or more before they are needed; otherwise at the row block's first tile.
+          int want = m_blk;
+          if (n0 + wout0 >= p.rot_cols && tw.valid(p)) want = tw.m;
+          if (want != trig_m_blk) {
+            trig_m_blk = want;
+            trig_scaled = false;
+            const long long r = (long long)want * BM + q * 32 + lane;
+            const int pos = r < p.M ? (int)((r + p.row_offset) % p.seqlen) : 0;
+            const float* s4 = p.sin_tab + (long long)pos * 32;
+            const float* c4 = p.cos_tab + (long long)pos * 32;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 a = __ldg(s4 + j), b = __ldg(c4 + j);
-              sn2[2 * j] = make_float2(a.x, a.y); sn2[2 * j + 1] = make_float2(a.z, a.w);
-              cs2[2 * j] = make_float2(b.x, b.y); cs2[2 * j + 1] = make_float2(b.z, b.w);
+            for (int j = 0; j < 8; ++j) {     // straight into the registers that hold them: nothing waits for the data here
+              asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(sn2[2 * j].x), "=f"(sn2[2 * j].y), "=f"(sn2[2 * j + 1].x), "=f"(sn2[2 * j + 1].y) : "l"(s4 + 4 * j));
+              asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(cs2[2 * j].x), "=f"(cs2[2 * j].y), "=f"(cs2[2 * j + 1].x), "=f"(cs2[2 * j + 1].y) : "l"(c4 + 4 * j));
             }
           }
-        }
-        if (!WRES || it == 0) {
-          __syncwarp();                                   // every lane is past its reads of the previous tile's scales
-          *reinterpret_cast<float4*>(sc + 4 * lane) = sb_next;
-          __syncwarp();
-        }
-        if (tw.valid(p)) {
-          const int nm = tw.m, nn = tw.n;
-          if (nm != m_blk) {
-            const int r = nm * BM + q * 32 + lane;
-            sa_next = (r < p.M) ? (p.scale_a ? ldg_f_here(p.scale_a + r) : 1.f) : 0.f;
+          // The rotated columns use sin and cos premultiplied by the token scale: folded in once per row block,
+          // at the first tile in which this warp rotates (rows fetched ahead have arrived by then).
+          if (trig_m_blk == m_blk && !trig_scaled && n0 + wout0 < p.rot_cols) {
+            trig_scaled = true;
+            const float2 s2 = pk2(sa, sa);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { sn2[j] = fmul2(sn2[j], s2); cs2[j] = fmul2(cs2[j], s2); }
           }
-          if (!WRES) sb_next = fetch_scales(nn * OUT_COLS_PER_TILE);
+        }
+        if (tw.valid(p) && tw.m != m_blk) {
+          const int r = tw.m * BM + q * 32 + lane;
+          sa_next = (r < p.M) ? (p.scale_a ? ldg_f_here(p.scale_a + r) : 1.f) : 0.f;
         }
       }
 
@@ -440,11 +464,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!agreed) break;
       asm volatile("" : "+r"(agreed));   // opaque from here on: the scale address below must stay dependent on the wait
       tc_fence_after();
-      // Channel scales are read with loads the compiler may move across the staging stores below (plain
-      // loads would be kept in order with every store to shared memory).  The address depends on the
-      // outcome of the wait, so no read can move above it, hence not above the scale stores either.
-      const uint32_t sc_addr = smem_u32(sc) + ((agreed - 1u) << 2);
-      auto scq = [&](int i) { return lds_f4_ro(sc_addr + i * 4); };      // scales of local columns i..i+3
+      // The tile's channel scales landed with its first K block, before the MMAs that have now completed.
+      // They are read with loads the compiler may move across the staging stores below (plain loads would
+      // be kept in order with every store to shared memory); the address depends on the outcome of the
+      // wait, so no read can move above it.  Index = column relative to this warp's first accumulator column.
+      const uint32_t sc_addr = smem_u32(scale_base + sbuf * BN + acol0) + ((agreed - 1u) << 2);
+      if (!WRES && ++sbuf == Map::SCALE_BUFS) sbuf = 0;
+      auto scq = [&](int i) { return lds_f4_ro(sc_addr + i * 4); };      // scales of columns i..i+3
       auto scp = [&](int i) { return lds_f2_ro(sc_addr + i * 4); };      // ... i, i+1
       const uint32_t t_row = tmem_base + as * BN + ((uint32_t)(q * 32) << 16) + acol0;
       // hand the accumulator stage back to the MMA warp: called once per tile, right after the wait that
@@ -491,7 +517,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
                 const float2 gv = dequant2<KIND>(g[j], g[j + 1], sa2, scp(c + j));
-                const float2 uv = dequant2<KIND>(u[j], u[j + 1], sa2, scp(WACC / 2 + c + j));
+                const float2 uv = dequant2<KIND>(u[j], u[j + 1], sa2, scp(BN / 2 + c + j));
                 o[j] = __fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x;
                 o[j + 1] = __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y;
                 amax = fmaxf(amax, fmaxf(fabsf(o[j]), fabsf(o[j + 1])));
@@ -607,15 +633,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                     uint32_t o0[4], o1[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                      const float2 x0 = dequant2<KIND>(v0[j + 2 * i], v0[j + 2 * i + 1], sa2, sb0[i]);
-                      const float2 x1 = dequant2<KIND>(v1[j + 2 * i], v1[j + 2 * i + 1], sa2, sb1[i]);
+                      // y = acc * sB[n];  out0 = y0*(sA cos) - y1*(sA sin),  out1 = y0*(sA sin) + y1*(sA cos), each
+                      // as one rounded product and one fused multiply-add (the CPU model rounds at the same points)
+                      const float2 y0 = fmul2(pk2(acc_to_float<KIND>(v0[j + 2 * i]), acc_to_float<KIND>(v0[j + 2 * i + 1])), sb0[i]);
+                      const float2 y1 = fmul2(pk2(acc_to_float<KIND>(v1[j + 2 * i]), acc_to_float<KIND>(v1[j + 2 * i + 1])), sb1[i]);
                       const float2 c2 = cs2[hh * 8 + (j >> 1) + i], s2 = sn2[hh * 8 + (j >> 1) + i];
-                      // Separately rounded products and sums: reproducible bit for bit on a CPU.  The final
-                      // add / subtract is scalar on purpose: a packed multiply feeding a packed add was seen
-                      // to be contracted into a fused multiply-add, which rounds once instead of twice.
-                      const float2 pa = fmul2(x0, c2), qa = fmul2(x1, s2), ra = fmul2(x0, s2), ta = fmul2(x1, c2);
-                      o0[i] = pack_half2(__fsub_rn(pa.x, qa.x), __fsub_rn(pa.y, qa.y));
-                      o1[i] = pack_half2(__fadd_rn(ra.x, ta.x), __fadd_rn(ra.y, ta.y));
+                      const float2 qa = fmul2(y1, s2), ta = fmul2(y1, c2);
+                      o0[i] = pack_half2_from(__ffma2_rn(y0, c2, make_float2(-qa.x, -qa.y)));
+                      o1[i] = pack_half2_from(__ffma2_rn(y0, s2, ta));
                     }
                     put(0, n, hh * 2 + (j >> 3), make_uint4(o0[0], o0[1], o0[2], o0[3]));
                     put(1, n + 32, hh * 2 + (j >> 3), make_uint4(o1[0], o1[1], o1[2], o1[3]));
@@ -649,8 +674,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 for (int j = 0; j < 32; j += 8) {
                   const float4 g_lo = scq(c + j);
                   const float4 g_hi = scq(c + j + 4);
-                  const float4 u_lo = scq(WACC / 2 + c + j);
-                  const float4 u_hi = scq(WACC / 2 + c + j + 4);
+                  const float4 u_lo = scq(BN / 2 + c + j);
+                  const float4 u_hi = scq(BN / 2 + c + j + 4);
                   const float2 sg[4] = {{g_lo.x, g_lo.y}, {g_lo.z, g_lo.w}, {g_hi.x, g_hi.y}, {g_hi.z, g_hi.w}};
                   const float2 su[4] = {{u_lo.x, u_lo.y}, {u_lo.z, u_lo.w}, {u_hi.x, u_hi.y}, {u_hi.z, u_hi.w}};
                   uint32_t o[4];

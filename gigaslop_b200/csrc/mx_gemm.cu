@@ -42,12 +42,6 @@ struct MxParams {
   const uint8_t* sfa; const uint8_t* sfb0; const uint8_t* sfb1;    // tiled scale factors
 };
 
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-
 // Shared-memory descriptor of one scale tile for tcgen05.cp: 32 rows of 16 bytes, unswizzled K-major, 8-row
 // groups 128 bytes apart.
 __device__ __forceinline__ uint64_t sf_smem_desc(uint32_t addr) {

@@ -104,6 +104,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ---- TMA --------------------------------------------------------------------
+// Untiled bulk copy global -> shared that reports its bytes to an mbarrier.  Both addresses 16-byte aligned,
+// size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 // Ask the TMA unit to bring one box of a tiled tensor into L2 (no shared-memory destination, no completion).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"

@@ -87,14 +87,48 @@ def rotary_ref(A_i8, B_i8, scale_a, scale_b, sin_buf, cos_buf,
     return _rotate(C, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen)
 
 
+def fma_f32(a, b, c):
+    """Correctly rounded fp32 fused multiply-add ``round(a*b + c)`` of float32 tensors.
+
+    The product of two float32 is exact in float64; the sum is rounded to odd in
+    float64 (TwoSum gives the discarded part), which makes the final rounding to
+    float32 the same as rounding the exact value once."""
+    p = a.double() * b.double()
+    cd = c.double().expand_as(p)
+    s = p + cd
+    bb = s - p
+    err = (p - (s - bb)) + (cd - bb)
+    bits = s.contiguous().view(torch.int64)
+    need = (err != 0) & ((bits & 1) == 0)
+    step = torch.where((err > 0) == (s > 0), 1, -1)
+    bits = torch.where(need, bits + step, bits)
+    return bits.view(torch.float64).float()
+
+
 def rotary_exact(A_i8, B_i8, scale_a, scale_b, sin_buf, cos_buf,
                  nhead, head_dim, rotary_dim, seqlen):
-    """Model of the device epilogue: exact int32 acc -> ``f32(acc)*(sA*sB)`` ->
-    rotation with separately rounded products (no fused multiply-add) -> f16.
+    """Model of the device epilogue on the exact int32 accumulator, rounding where the kernel rounds.
+
+    Rotated columns: ``y = f32(acc)*sB[n]``, ``C = sA[m]*cos``, ``S = sA[m]*sin`` (each one
+    rounded fp32 product), then ``out0 = fma(y0, C, -(y1*S))`` and ``out1 = fma(y0, S, y1*C)``
+    with the inner product rounded and the fused multiply-add rounded once.  The other
+    columns are ``f32(acc)*(sA*sB)``.  The result is rounded to f16.
     """
     acc = gemm_i32(A_i8, B_i8).float()
-    C = acc * (scale_a.float()[:, None] * scale_b.float()[None, :])
-    return _rotate(C, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen).to(torch.float16)
+    sa = scale_a.float()[:, None]
+    sb = scale_b.float()[None, :]
+    out = acc * (sa * sb)
+    y = acc * sb
+    rh = rotary_dim // 2
+    seq = torch.arange(acc.shape[0]) % seqlen
+    C = sa * cos_buf[seq].float()
+    S = sa * sin_buf[seq].float()
+    for hs in range(0, 2 * nhead * head_dim, head_dim):
+        y0 = y[:, hs:hs + rh]
+        y1 = y[:, hs + rh:hs + rotary_dim]
+        out[:, hs:hs + rh] = fma_f32(y0, C, -(y1 * S))
+        out[:, hs + rh:hs + rotary_dim] = fma_f32(y0, S, y1 * C)
+    return out.to(torch.float16)
 
 
 def dual_gemm_silu_ref(A_i8, Bg_i8, Bu_i8, scale_a, scale_bg, scale_bu):
