@@ -169,7 +169,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   ok = ok && make_map_2d(&tb1, u8, 1, dual ? a.B1 : a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
   if (a.epi != EPI_I32 && a.epi != EPI_SILU_MX)
     ok = ok && make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.C, (uint64_t)a.M, (uint64_t)a.N,
-                           (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
+                           (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B);
   else
     tc = ta;
   if (!ok) return GSB200_ERR_BAD_ARG;

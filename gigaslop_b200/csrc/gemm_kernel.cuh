@@ -58,8 +58,8 @@ constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
 constexpr int RES_MAX_KBLOCKS = 4;                      // resident operand (W slice or A block): up to K = 512
 constexpr int NSTAGE = 3;                               // ring depth of every schedule
-constexpr int OUT_BOX_ROWS = 32;
-constexpr int OUT_BOX_COLS = 32;                        // fp16 -> 64 B rows, SWIZZLE_64B
+constexpr int OUT_BOX_ROWS = 16;                        // output boxes of 16 rows x 64 fp16: full 128-byte lines,
+constexpr int OUT_BOX_COLS = 64;                        // SWIZZLE_128B; a warp's 32 rows x 64 columns leave as two boxes
 constexpr int OUT_BUF_BYTES = OUT_BOX_ROWS * OUT_BOX_COLS * 2;   // 2 KiB
 constexpr int SCALE_BUF_BYTES = BN * 4;                 // channel scales of one tile, indexed by accumulator column (dual: gate | up)
 
@@ -395,9 +395,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     int cur_m_blk = -1;
     int trig_m_blk = -1;                   // row block whose sin / cos rows are in sn2 / cs2
     bool trig_scaled = false;              // ... already multiplied by the token scale
-    uint32_t stg_off[4];                   // byte offsets of the 4 pieces of this thread's row in a swizzled staging box
+    // A pair of staging boxes holds 32 rows x 64 output columns: lanes 0-15 own the rows of the first box,
+    // lanes 16-31 those of the second.  stg_off = byte offsets of the 8 16-byte pieces of this thread's row in
+    // its box, in the 128-byte swizzle the TMA store expects (conflict-free for 16-byte stores by a warp).
+    uint32_t stg_off[8];
 #pragma unroll
-    for (int pc = 0; pc < 4; ++pc) stg_off[pc] = lane * 64 + ((pc ^ ((lane >> 1) & 3)) << 4);
+    for (int pc = 0; pc < 8; ++pc) stg_off[pc] = (lane & 15) * 128 + ((pc ^ (lane & 7)) << 4);
 
     TileWalk<SCHED> tw; tw.start(p);
     if constexpr (EPI != EPI_I32) {
@@ -572,7 +575,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               if constexpr (DIRECT) {
                 if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = o;
               } else {
-                *reinterpret_cast<uint4*>(out_buf + (which ? buf_b : buf_a) * OUT_BUF_BYTES + stg_off[piece]) = o;
+                *reinterpret_cast<uint4*>(out_buf + (lane < 16 ? buf_a : buf_b) * OUT_BUF_BYTES + stg_off[which * 4 + piece]) = o;
               }
             };
             auto pair_end = [&](int n_a, int n_b) {
@@ -581,7 +584,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 __syncwarp();
                 if (lane == 0 && !(p.ablate & 1)) {
                   tma_store_2d(&tm_c, out_buf + buf_a * OUT_BUF_BYTES, n_a, row_base); tma_store_commit();
-                  if (n_b < p.N) { tma_store_2d(&tm_c, out_buf + buf_b * OUT_BUF_BYTES, n_b, row_base); tma_store_commit(); }
+                  if (row_base + OUT_BOX_ROWS < p.M) tma_store_2d(&tm_c, out_buf + buf_b * OUT_BUF_BYTES, n_a, row_base + OUT_BOX_ROWS);
+                  tma_store_commit();          // always two groups per pair (the second may be empty): pair_begin counts groups
                 }
                 obuf = (buf_b + 1 == OUT_BUFS) ? 0 : buf_b + 1;
               }
