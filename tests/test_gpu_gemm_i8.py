@@ -219,3 +219,24 @@ def test_bad_arguments_are_rejected_before_launch():
     with pytest.raises(RuntimeError):
         g.gemm_i8(A.cpu(), B.cpu(), s.cpu(), s.cpu())        # no CPU path
     assert g.device_status()[0] == 0
+
+
+def test_host_pipeline_equals_whole_batch_call():
+    """Chunked upload / compute / download over three streams gives the bytes of one whole-batch call."""
+    g = need_lib()
+    from gigaslop_b200.hostpipe import QkvRotaryHostPipeline
+    gen = torch.Generator().manual_seed(21)
+    M, K, N, seqlen = 2500, 512, 1536, 333
+    x = (torch.randn(M, K, generator=gen) * 3).half().pin_memory()
+    W = rand_i8(gen, N, K).cuda()
+    sw = rand_scales(gen, N).cuda()
+    sn, cs = (t.cuda() for t in oracle.rope_tables(seqlen, 32, 64))
+    q, s = g.quantize_tensor(x.cuda())
+    whole = g.gemm_i8_rotary(q, W, s, sw, sn, cs, 8, 64, 64, seqlen, row_offset=7).cpu()
+    out = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    pipe = QkvRotaryHostPipeline(M, K, N, "cuda", chunk_rows=1024, depth=2)
+    for _ in range(2):                       # the second pass reuses every slot
+        out.zero_()
+        pipe.run(x, out, W, sw, sn, cs, 8, 64, 64, seqlen, row_offset=7)
+        pipe.finish()
+        assert_bitexact(out, whole, "host pipeline vs whole batch")
