@@ -40,16 +40,26 @@ __device__ __forceinline__ float warp_max(float m) {
   return m;
 }
 
-__device__ __forceinline__ uint32_t q_i8(float x, float qs) {
-  int q = __float2int_rn(__fmul_rn(x, qs));      // round half to even
-  q = max(-127, min(127, q));
-  return static_cast<uint32_t>(q) & 0xffu;
+// Two int32 -> two saturated int8 in the low half of the result, the low half of `upper` above them:
+// result = upper[15:0] << 16 | sat8(hi) << 8 | sat8(lo).
+__device__ __forceinline__ uint32_t pack_sat_s8(int hi, int lo, uint32_t upper) {
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(upper));
+  return d;
+}
+// q = clamp(rne(x * qs), -127, 127) for four values, packed little-endian.  |x| <= amax and qs = fl(fl(1/amax)*127)
+// bound |x*qs| by 127.0001, so the rounded value never leaves [-127, 127]; the pack saturates all the same.
+__device__ __forceinline__ uint32_t pack4_i8(float x0, float x1, float x2, float x3, float qs) {
+  const float2 q2 = make_float2(qs, qs);
+  const float2 a = __fmul2_rn(make_float2(x0, x1), q2), b = __fmul2_rn(make_float2(x2, x3), q2);
+  const uint32_t hi = pack_sat_s8(__float2int_rn(b.y), __float2int_rn(b.x), 0u);     // round half to even
+  return pack_sat_s8(__float2int_rn(a.y), __float2int_rn(a.x), hi);
 }
 
 __device__ __forceinline__ uint2 pack_i8(const float (&v)[8], float qs) {
   uint2 o;
-  o.x = q_i8(v[0], qs) | (q_i8(v[1], qs) << 8) | (q_i8(v[2], qs) << 16) | (q_i8(v[3], qs) << 24);
-  o.y = q_i8(v[4], qs) | (q_i8(v[5], qs) << 8) | (q_i8(v[6], qs) << 16) | (q_i8(v[7], qs) << 24);
+  o.x = pack4_i8(v[0], v[1], v[2], v[3], qs);
+  o.y = pack4_i8(v[4], v[5], v[6], v[7], qs);
   return o;
 }
 
@@ -88,7 +98,22 @@ ptq_kernel(const Tin* __restrict__ x, long long ldx, uint8_t* __restrict__ q, lo
 
   float vals[NV > 0 ? NV : 1][8];
   float amax = 0.f;
-  if constexpr (NV > 0) {
+  constexpr bool HALF_CACHED = NV > 0 && sizeof(Tin) == 2;
+  uint4 raw[HALF_CACHED ? NV : 1];       // fp16 rows are held as loaded: 8 halves per 16-byte vector
+  if constexpr (HALF_CACHED) {
+    // row maximum with packed half2 max / abs (exact: it is a maximum of the very same fp16 values)
+    __half2 m2 = __float2half2_rn(0.f);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      raw[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (v < nvec) raw[i] = __ldg(reinterpret_cast<const uint4*>(xr + v * 8));
+      const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m2 = __hmax2(m2, __habs2(h[k]));
+    }
+    amax = fmaxf(__low2float(m2), __high2float(m2));
+  } else if constexpr (NV > 0) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
@@ -129,7 +154,21 @@ ptq_kernel(const Tin* __restrict__ x, long long ldx, uint8_t* __restrict__ q, lo
     else o = pack_e4m3<1>(vv, f);
     *reinterpret_cast<uint2*>(qr + v * 8) = o;
   };
-  if constexpr (NV > 0) {
+  if constexpr (HALF_CACHED) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f2 = __half22float2(h[k]);
+          vals[0][2 * k] = f2.x; vals[0][2 * k + 1] = f2.y;
+        }
+        emit(v, vals[0]);
+      }
+    }
+  } else if constexpr (NV > 0) {
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
