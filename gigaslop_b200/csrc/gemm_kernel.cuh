@@ -512,6 +512,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           // scale byte = clamp(e - 8, 0, 254) (value 2^(byte-127)), elements = e4m3_rn_satfinite(v * 2^(127-byte)).
           // A thread holds whole 32-column blocks of its row, so the block maximum needs no exchange.
           const float2 sa2 = pk2(sa, sa);
+          const float2 sah2 = pk2(0.5f * sa, 0.5f * sa);      // the gate is dequantised straight to gate / 2 (exact halving)
           auto emit = [&](const uint32_t (&g)[32], const uint32_t (&u)[32], int c) {
             const int n = n0 + wout0 + c;
             if (n + 32 <= p.N) {
@@ -519,10 +520,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               float amax = 0.f;
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
-                const float2 gv = dequant2<KIND>(g[j], g[j + 1], sa2, scp(c + j));
+                const float2 hv = dequant2<KIND>(g[j], g[j + 1], sah2, scp(c + j));          // gate / 2
                 const float2 uv = dequant2<KIND>(u[j], u[j + 1], sa2, scp(BN / 2 + c + j));
-                o[j] = __fdividef(gv.x, 1.0f + __expf(-gv.x)) * uv.x;
-                o[j + 1] = __fdividef(gv.y, 1.0f + __expf(-gv.y)) * uv.y;
+                const float2 ov = fmul2(silu_from_half2(hv), uv);
+                o[j] = ov.x; o[j + 1] = ov.y;
                 amax = fmaxf(amax, fmaxf(fabsf(o[j]), fabsf(o[j + 1])));
               }
               int eb = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 8;
@@ -555,6 +556,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           emit(gb, ub, 32);
         } else {
           const float2 sa2 = pk2(sa, sa);
+          const float2 sah2 = pk2(0.5f * sa, 0.5f * sa);
           // The body exists twice: the product path (swizzled staging + TMA store) and a diagnostic path
           // that stores straight from registers; the choice is made once per tile.
           auto run_tile = [&](auto direct_tag) {
@@ -685,11 +687,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                   uint32_t o[4];
 #pragma unroll
                   for (int i = 0; i < 4; ++i) {
-                    const float2 gv = dequant2<KIND>(g[j + 2 * i], g[j + 2 * i + 1], sa2, sg[i]);
+                    // silu(gate) = h + h * tanh(h), h = gate / 2: the gate is dequantised straight to h (exact halving)
+                    const float2 hv = dequant2<KIND>(g[j + 2 * i], g[j + 2 * i + 1], sah2, sg[i]);
                     const float2 up = dequant2<KIND>(u[j + 2 * i], u[j + 2 * i + 1], sa2, su[i]);
-                    // silu(gate) = gate / (1 + exp(-gate)); exp and the division use the fast hardware approximations
-                    const float2 sl = pk2(__fdividef(gv.x, 1.0f + __expf(-gv.x)), __fdividef(gv.y, 1.0f + __expf(-gv.y)));
-                    o[i] = pack_half2_from(fmul2(sl, up));
+                    o[i] = pack_half2_from(fmul2(silu_from_half2(hv), up));
                   }
                   put(which, n, j >> 3, make_uint4(o[0], o[1], o[2], o[3]));
                 }

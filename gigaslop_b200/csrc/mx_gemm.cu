@@ -189,9 +189,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t w[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-              w[j] = pack_half2(__fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(u[2 * j]),
-                                __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(u[2 * j + 1]));
+              // silu(gate) * up with silu(g) = h + h * tanh(h), h = g / 2
+              const float2 hv = __fmul2_rn(make_float2(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1])), make_float2(0.5f, 0.5f));
+              const float2 uv = make_float2(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1]));
+              w[j] = pack_half2_from(__fmul2_rn(silu_from_half2(hv), uv));
             }
             emit_box(n, w);
           }

@@ -277,6 +277,16 @@ __device__ __forceinline__ uint32_t pack_half2_from(float2 v) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Hardware tanh (one special-function instruction, relative error about 2^-11).
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y; asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y;
+}
+// silu(g) = g * sigmoid(g) = h + h * tanh(h) with h = g / 2: one special-function instruction per value
+// instead of the two (exp and reciprocal) of g / (1 + exp(-g)).  Takes h, returns silu(2h), for a pair.
+__device__ __forceinline__ float2 silu_from_half2(float2 h) {
+  return __ffma2_rn(h, make_float2(tanh_approx(h.x), tanh_approx(h.y)), h);
+}
+
 // ---- misc -----------------------------------------------------------------------
 __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
