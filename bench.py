@@ -26,8 +26,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the QKV+rotary GEMM at the bench's full size,
-# from the ncu capture summarised in profiles/gemm_i8_rotary_config2.md (35.5 MB + 148.1 MB)
-GEMM_DRAM_TRAFFIC = 183.6e6
+# from the ncu capture summarised in profiles/gemm_i8_rotary_config2.md (40.8 MB + 141.6 MB)
+GEMM_DRAM_TRAFFIC = 182.4e6
 METRIC = "w8a8_qkv_rotary_gemm_tops"
 UNIT = "TOPS"
 
