@@ -28,6 +28,8 @@ sys.path.insert(0, ROOT)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the QKV+rotary GEMM at the bench's full size,
 # from the ncu capture summarised in profiles/gemm_i8_rotary_config2.md (40.8 MB + 141.6 MB)
 GEMM_DRAM_TRAFFIC = 182.4e6
+WORKLOAD = ("config2: per-token int8 quantise [65536,512] fp16 + W8A8 QKV GEMM N=1536 K=512 "
+            "with fused rotary (8 heads x 64, seqlen 2048), per GPU")
 METRIC = "w8a8_qkv_rotary_gemm_tops"
 UNIT = "TOPS"
 
@@ -131,8 +133,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config2: per-token int8 quantise + W8A8 QKV GEMM + rotary, K=512 N=1536, "
-                               f"CPU sample of {rows} of 65536 tokens per step", "rows_per_step": rows},
+        "config": {"workload": WORKLOAD, "M_per_gpu": 65536, "N": c["N"], "K": c["K"],
+                   "parallelism": "host cores, all threads", "rows_per_step": rows},
         "tokens_per_s": rows / sec,
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": f"{rows} rows x {steps} steps of config2 (quantize_tensor + rotary_ref, torch CPU fp32)"},
@@ -256,8 +258,7 @@ def run_native(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
-        "config": {"workload": "config2: per-token int8 quantise [65536,512] fp16 + W8A8 QKV GEMM N=1536 K=512 "
-                               "with fused rotary (8 heads x 64, seqlen 2048), per GPU",
+        "config": {"workload": WORKLOAD,
                    "M_per_gpu": M, "N": N, "K": K, "parallelism": f"row-sharded x{world}, no collective",
                    "l2": f"{NSETS} rotating buffer sets of 302 MB (> 126 MB L2)"},
         "tokens_per_s": world * M / (ms_step * 1e-3),
