@@ -26,6 +26,7 @@ constexpr int LSTM_ROWS = 128;               // batch rows per CTA (UMMA M)
 constexpr int LSTM_HS = 32;                  // hidden units per CTA
 constexpr int LSTM_NCOL = 4 * LSTM_HS;       // gate columns per CTA (UMMA N)
 constexpr int LSTM_MAX_KB = 4;               // H <= 512
+constexpr int LSTM_PULLS = LSTM_ROWS * LSTM_MAX_KB * 8 / LSTM_THREADS;   // 16-byte pieces of h per thread and step (at most)
 constexpr int LSTM_KB_BYTES = LSTM_ROWS * 128;                 // one 128-byte K block of a 128-row operand tile
 constexpr int LSTM_IH_BYTES = LSTM_ROWS * LSTM_NCOL * 2;       // 32 KiB: four 128 x 32 fp16 boxes
 constexpr int LSTM_SMEM_W = 0;
@@ -140,6 +141,20 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10, budget);
   const int chunks_per_row = p.k_blocks * 8;                 // 16-byte pieces of a (zero-padded) h row
   unsigned int* my_flags = p.flags + grp * p.slices;
+  // the 16-byte pieces of the 128 x H tile of h this thread moves every step: source offset inside an h buffer
+  // (-1: zero padding), destination offset in the swizzled operand tile (-1: nothing to do)
+  int pull_src[LSTM_PULLS], pull_dst[LSTM_PULLS];
+#pragma unroll
+  for (int i = 0; i < LSTM_PULLS; ++i) {
+    const int id = tid + i * LSTM_THREADS;
+    pull_src[i] = pull_dst[i] = -1;
+    if (id < LSTM_ROWS * chunks_per_row) {
+      const int r = id / chunks_per_row, cc = id % chunks_per_row;
+      const int kb = cc >> 3, ck = cc & 7;
+      pull_dst[i] = kb * LSTM_KB_BYTES + r * 128 + ((ck ^ (r & 7)) << 4);
+      if (row0 + r < B && cc * 16 < H) pull_src[i] = (row0 + r) * H + cc * 16;
+    }
+  }
 
   for (int s = 0; s < p.T; ++s) {
     // ---- 1. wait until every slice of this row group has published h_{s-1} -----------------------------
@@ -159,12 +174,18 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     __syncthreads();
     if (*abort_flag || !ok) break;
     // ---- 2. pull the 128 x H tile of h_{s-1} into the swizzled K-major operand layout ------------------
-    for (int id = tid; id < LSTM_ROWS * chunks_per_row; id += LSTM_THREADS) {
-      const int r = id / chunks_per_row, cc = id % chunks_per_row;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (h_prev && row0 + r < B && cc * 16 < H) v = __ldcg(reinterpret_cast<const uint4*>(h_prev + (size_t)(row0 + r) * H + cc * 16));
-      const int kb = cc >> 3, ck = cc & 7;
-      *reinterpret_cast<uint4*>(h_s + kb * LSTM_KB_BYTES + r * 128 + ((ck ^ (r & 7)) << 4)) = v;
+    // All of a thread's loads are issued before the first store, so their L2 latencies overlap (one after the
+    // other they were the longest part of the step).  pull_src / pull_dst were computed once before the loop.
+    {
+      uint4 v[LSTM_PULLS];
+#pragma unroll
+      for (int i = 0; i < LSTM_PULLS; ++i) {
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (h_prev && pull_src[i] >= 0) v[i] = __ldcg(reinterpret_cast<const uint4*>(h_prev + pull_src[i]));
+      }
+#pragma unroll
+      for (int i = 0; i < LSTM_PULLS; ++i)
+        if (pull_dst[i] >= 0) *reinterpret_cast<uint4*>(h_s + pull_dst[i]) = v[i];
     }
     fence_proxy_async_smem();
     __syncthreads();
