@@ -240,35 +240,41 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           c[j0 + i] = __half2float(__float2half_rn(cn));        // the cell state is carried in fp16
         }
       }
+      uint32_t w8[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i] * 448.f, hv[4 * i + 1] * 448.f), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i + 2] * 448.f, hv[4 * i + 3] * 448.f), __NV_SATFINITE, __NV_E4M3);
+        w8[i] = lo | (hi << 16);
+      }
+      const size_t off = (size_t)row * H + hid0 + half * 16;
+      // the piece the other slices wait for goes out first
+      if (row_ok) *reinterpret_cast<uint4*>(p.hbuf + (size_t)(s & 1) * B * H + off) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+      tc_fence_before();
+      __syncthreads();
+      // ---- 5. publish: one release store after the CTA barrier covers every thread's piece (the release is
+      //         cumulative over what the barrier ordered before it); then prefetch the ih tile two steps ahead
+      if (tid == 0) {
+        st_release_gpu(my_flags + slc, (unsigned int)(s + 1));
+        if (s + 2 < p.T) issue_ih(s + 2);
+      }
+      // ---- 6. the layer's outputs, off the other slices' critical path -------------------------------------
       if (row_ok) {
-        uint32_t w8[4], w16[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i] * 448.f, hv[4 * i + 1] * 448.f), __NV_SATFINITE, __NV_E4M3);
-          const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i + 2] * 448.f, hv[4 * i + 3] * 448.f), __NV_SATFINITE, __NV_E4M3);
-          w8[i] = lo | (hi << 16);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) w16[i] = pack_half2(hv[2 * i], hv[2 * i + 1]);
-        const size_t off = (size_t)row * H + hid0 + half * 16;
-        *reinterpret_cast<uint4*>(p.hbuf + (size_t)(s & 1) * B * H + off) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
         const size_t toff = (size_t)step_t(s) * B * H + off;
         if (p.h8_out) *reinterpret_cast<uint4*>(p.h8_out + toff) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
         if (p.h_out) {
+          uint32_t w16[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w16[i] = pack_half2(hv[2 * i], hv[2 * i + 1]);
           *reinterpret_cast<uint4*>(p.h_out + toff) = make_uint4(w16[0], w16[1], w16[2], w16[3]);
           *reinterpret_cast<uint4*>(p.h_out + toff + 8) = make_uint4(w16[4], w16[5], w16[6], w16[7]);
         }
       }
-      __threadfence();                 // this thread's piece of h_s is visible device-wide before the counter moves
+    } else {
+      tc_fence_before();
+      __syncthreads();
     }
-    tc_fence_before();
-    __syncthreads();
     if (!ok || *abort_flag) break;
-    // ---- 5. publish, and prefetch the ih tile two steps ahead into the buffer just consumed --------------
-    if (tid == 0) {
-      st_release_gpu(my_flags + slc, (unsigned int)(s + 1));
-      if (s + 2 < p.T) issue_ih(s + 2);
-    }
   }
 
   if (p.c_last && row_ok) {
