@@ -107,6 +107,16 @@ def compile_fp8_down_proj(*, C=None, R=None, n_split=1, **_):
     return launcher
 
 
+def compile_fp8_factored_gemm(*, C=None, R=None, N=None, **_):
+    """launcher(ih, x_fp8, scale_x, dn_rc, scale_dn, up_nr, bias, stream, M) --
+    fly/rdna_fp8_factored_gemm.py:86-435 (argument order of fly/bench_factored_gemm.py:46-50); ``dn`` ``[R, C]``
+    and ``up`` ``[N, R]`` K-major instead of the RDNA pre-shuffles."""
+    def launcher(ih, x, scale_x, dn_rc, scale_dn, up_nr, bias, stream, m):
+        with _Stream(stream):
+            ops.fp8_factored_gemm(x[:m], scale_x[:m], dn_rc, scale_dn, up_nr, bias, out=ih[:m])
+    return launcher
+
+
 def compile_fp8_factored_lstm(*, B=None, H=None, K_hh=None, R=None, **_):
     """launcher(h_fp8, c, hh_down, up_hh_nk, bias_hh, x_down, up_ih_nk, bias_ih, stream, B) --
     fly/rdna_fp8_factored_lstm.py:88-351."""

@@ -135,6 +135,26 @@ int32_t gsb200_gemm_f16_f16(const void* A, int64_t lda, const void* B, int64_t l
                      S(stream));
 }
 
+int32_t gsb200_fac_gemm_fp8_f16(const uint8_t* x, int64_t ldx, const float* scale_x, const uint8_t* dn_rc, int64_t lddn,
+                                const float* scale_dn, const void* up_nr, int64_t ldup, const float* bias, void* ih,
+                                int64_t ldih, int64_t M, int32_t C, int32_t R, int32_t N, gsb200_stream_t stream) {
+  if (M == 0) return GSB200_OK;
+  if (!x || !scale_x || !dn_rc || !scale_dn || !up_nr || !bias || !ih) return GSB200_ERR_BAD_ARG;
+  if (R <= 0 || R % 8 != 0 || N < R || ldih < N) return GSB200_ERR_BAD_ARG;
+  if (R > 256) return GSB200_ERR_UNSUPPORTED;          // the second GEMM keeps a row block's x_down (2R bytes per row) resident
+  // 1. x_down[M,R] = f16((x . dn^T) * sx[m] * s_dn), written into the first R columns of each output row
+  int32_t rc = launch_gemm(base_args(KIND_F8, EPI_DEQUANT, x, ldx, dn_rc, nullptr, lddn, ih, ldih, scale_x, scale_dn,
+                                     nullptr, M, R, C, GSB200_FLAG_SCALAR_SCALE_B),
+                           S(stream));
+  if (rc != GSB200_OK) return rc;
+  // 2. ih[M,N] = f16(x_down . up^T + bias), reading x_down from where step 1 left it: the activation-stationary
+  //    schedule has a CTA read a row block's x_down completely before it writes that row block's output, and no
+  //    other CTA touches those rows
+  return launch_gemm(base_args(KIND_F16, EPI_BIAS, ih, 2 * ldih, up_nr, nullptr, 2 * ldup, ih, ldih, nullptr, bias,
+                               nullptr, M, N, 2 * R, 0),
+                     S(stream));
+}
+
 int32_t gsb200_factored_lstm_step(uint8_t* h_fp8_out, float* c_inout, const void* hh_down, const void* up_hh,
                                   const float* bias_hh, const void* x_down, const void* up_ih, const float* bias_ih,
                                   int64_t B, int32_t H, int32_t K_hh, int32_t R, gsb200_stream_t stream) {

@@ -54,7 +54,7 @@ static cudaError_t set_attr() {
   cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  constexpr int RES = (EPI == EPI_ROTARY) ? SCHED_ARES : SCHED_WRES;
+  constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
   return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               GEMM_SMEM_BYTES);
 }
@@ -77,7 +77,8 @@ int32_t ensure_device() {
   cudaError_t errs[] = {
       set_attr<KIND_I8, EPI_I32>(),     set_attr<KIND_I8, EPI_DEQUANT>(), set_attr<KIND_I8, EPI_ROTARY>(),
       set_attr<KIND_I8, EPI_SILU>(),    set_attr<KIND_F8, EPI_DEQUANT>(), set_attr<KIND_F8, EPI_ROTARY>(),
-      set_attr<KIND_F8, EPI_SILU>(),    set_attr<KIND_F8, EPI_SILU_MX>(), set_attr<KIND_F16, EPI_DEQUANT>()};
+      set_attr<KIND_F8, EPI_SILU>(),    set_attr<KIND_F8, EPI_SILU_MX>(), set_attr<KIND_F16, EPI_DEQUANT>(),
+      set_attr<KIND_F16, EPI_BIAS>()};
   for (cudaError_t er : errs)
     if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
   if (!encode_fn()) {
@@ -100,8 +101,10 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 template <int KIND, int EPI>
 static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1,
                                const CUtensorMap& tc, const GemmParams& p, int grid, bool resident, cudaStream_t st) {
-  // resident-operand schedule: rotary keeps A (activation-stationary), the others keep W (weight-stationary)
-  constexpr int RES = (EPI == EPI_ROTARY) ? SCHED_ARES : SCHED_WRES;
+  // resident-operand schedule: rotary and the bias epilogue keep A (activation-stationary: one CTA reads a row
+  // block's A completely before it writes any of that row block's output, which is what lets the low-rank
+  // projection keep its intermediate inside the output buffer), the others keep W (weight-stationary)
+  constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
   if (resident) gemm_tcgen05_kernel<KIND, EPI, RES><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
   else gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
   return cudaGetLastError();
@@ -119,7 +122,8 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     if (a.N % 4 != 0 || a.ldc % 4 != 0) return GSB200_ERR_BAD_ARG;
   } else {
     if (a.N % 8 != 0 || a.ldc % 8 != 0) return GSB200_ERR_BAD_ARG;
-    if (a.epi != EPI_DEQUANT && (!a.scale_a || !a.scale_b0)) return GSB200_ERR_BAD_ARG;   // plain dequant: null = 1.0
+    if (a.epi == EPI_BIAS && !a.scale_b0) return GSB200_ERR_BAD_ARG;                       // the bias vector
+    if (a.epi != EPI_DEQUANT && a.epi != EPI_BIAS && (!a.scale_a || !a.scale_b0)) return GSB200_ERR_BAD_ARG;   // plain dequant: null = 1.0
     const bool scalar_b = (a.flags & GSB200_FLAG_SCALAR_SCALE_B) != 0;
     if (scalar_b && (a.epi != EPI_DEQUANT || !a.scale_b0)) return GSB200_ERR_BAD_ARG;
     if (a.scale_b0 && !scalar_b && (reinterpret_cast<uintptr_t>(a.scale_b0) & 15)) return GSB200_ERR_BAD_ARG;
@@ -181,13 +185,15 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   int grid;
   p.m_major = 0;
   p.n_groups = 0;
-  if (resident && a.epi != EPI_ROTARY) {
+  const bool a_stationary = a.epi == EPI_ROTARY || a.epi == EPI_BIAS;
+  if (a.epi == EPI_BIAS && !resident) return GSB200_ERR_UNSUPPORTED;     // only built for K <= 512 bytes of A per row
+  if (resident && !a_stationary) {
     int groups = sm_count() / p.n_blocks;
     if (groups < 1) groups = 1;
     if (groups > p.m_blocks) groups = p.m_blocks;
     p.n_groups = groups;
     grid = groups * p.n_blocks;
-  } else if (a.epi == EPI_ROTARY) {
+  } else if (a_stationary) {
     p.m_major = 1;
     grid = p.m_blocks < sm_count() ? p.m_blocks : sm_count();
   } else {
@@ -211,8 +217,9 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
       default: return GSB200_ERR_BAD_ARG;
     }
   } else if (a.kind == KIND_F16) {
-    if (a.epi != EPI_DEQUANT) return GSB200_ERR_BAD_ARG;
-    e = launch_inst<KIND_F16, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st);
+    if (a.epi == EPI_DEQUANT) e = launch_inst<KIND_F16, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st);
+    else if (a.epi == EPI_BIAS) e = launch_inst<KIND_F16, EPI_BIAS>(ta, tb0, tb1, tc, p, grid, resident, st);
+    else return GSB200_ERR_BAD_ARG;
   } else {
     return GSB200_ERR_BAD_ARG;
   }

@@ -7,6 +7,7 @@
 //   EPI_ROTARY   dequant, then rotate-half on the Q|K columns  (QKV projection)
 //   EPI_SILU     f16( silu(gate) * up ), gate|up in one UMMA   (SwiGLU dual GEMM)
 //   EPI_SILU_MX  the same product emitted as MXFP8: E4M3 elements + one E8M0 scale per 32 output columns
+//   EPI_BIAS     f16( acc * sA[m] + b[n] )                    second GEMM of the low-rank input projection
 //
 // Three schedules share the epilogue (tiles are 128 rows x 256 accumulator columns):
 //
@@ -39,7 +40,7 @@
 
 namespace gsb {
 
-enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3, EPI_SILU_MX = 4 };
+enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3, EPI_SILU_MX = 4, EPI_BIAS = 5 };
 enum : int { KIND_I8 = 0, KIND_F8 = 1, KIND_F16 = 2 };   // F16: fp16 operands (K counted in bytes = 2 per element), f32 accumulate
 enum : int { SCHED_STREAM = 0, SCHED_WRES = 1, SCHED_ARES = 2 };
 
@@ -140,6 +141,20 @@ __device__ __forceinline__ uint4 dequant_piece(const uint32_t* v, float2 sa2, fl
   o.y = pack_half2_from(dequant2<KIND>(v[2], v[3], sa2, make_float2(s_lo.z, s_lo.w)));
   o.z = pack_half2_from(dequant2<KIND>(v[4], v[5], sa2, make_float2(s_hi.x, s_hi.y)));
   o.w = pack_half2_from(dequant2<KIND>(v[6], v[7], sa2, make_float2(s_hi.z, s_hi.w)));
+  return o;
+}
+
+// 8 consecutive columns of the bias epilogue: f16( acc * sA + b[n] ), b in s_lo / s_hi.
+template <int KIND>
+__device__ __forceinline__ uint4 bias_piece(const uint32_t* v, float2 sa2, float4 s_lo, float4 s_hi) {
+  auto one = [&](uint32_t a0, uint32_t a1, float2 b2) {
+    return pack_half2_from(__ffma2_rn(pk2(acc_to_float<KIND>(a0), acc_to_float<KIND>(a1)), sa2, b2));
+  };
+  uint4 o;
+  o.x = one(v[0], v[1], make_float2(s_lo.x, s_lo.y));
+  o.y = one(v[2], v[3], make_float2(s_lo.z, s_lo.w));
+  o.z = one(v[4], v[5], make_float2(s_hi.x, s_hi.y));
+  o.w = one(v[6], v[7], make_float2(s_hi.z, s_hi.w));
   return o;
 }
 
@@ -593,12 +608,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               }
             };
 
-            if constexpr (EPI == EPI_DEQUANT) {
+            if constexpr (EPI == EPI_DEQUANT || EPI == EPI_BIAS) {
               // chunks of 32 columns = one box; two chunks leave as a pair
               auto emit = [&](const uint32_t (&v)[32], int c, int which) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 8)
-                  put(which, n0 + wout0 + c, j >> 3, dequant_piece<KIND>(&v[j], sa2, scq(c + j), scq(c + j + 4)));
+                for (int j = 0; j < 32; j += 8) {
+                  if constexpr (EPI == EPI_BIAS)
+                    put(which, n0 + wout0 + c, j >> 3, bias_piece<KIND>(&v[j], sa2, scq(c + j), scq(c + j + 4)));
+                  else
+                    put(which, n0 + wout0 + c, j >> 3, dequant_piece<KIND>(&v[j], sa2, scq(c + j), scq(c + j + 4)));
+                }
               };
               uint32_t va[32], vb[32];
               tmem_ld_32x32b_x32(t_row, va);

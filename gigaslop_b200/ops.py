@@ -202,6 +202,27 @@ def fp8_down_proj(x_fp8, scale_x, dn_fp8_rc, scale_dn, out=None):
     return gemm_fp8(x_fp8, dn_fp8_rc, scale_x, scale_dn, out=out, flags=_lib.FLAG_SCALAR_SCALE_B)
 
 
+def fp8_factored_gemm(x_fp8, scale_x, dn_fp8_rc, scale_dn, up_f16_nr, bias, out=None):
+    """Hoisted low-rank input projection ``ih = f16(f16((x . dn^T) * sx * s_dn) . up^T + bias)`` in one call
+    (compile_fp8_factored_gemm, fly/rdna_fp8_factored_gemm.py:86-435).  ``dn`` ``[R, C]`` E4M3 and ``up``
+    ``[N, R]`` fp16, both K-major; the intermediate lives inside ``out`` between the two launches."""
+    _need_cuda(x_fp8, scale_x, dn_fp8_rc, scale_dn, up_f16_nr, bias)
+    _rowmajor(x_fp8, "x"); _rowmajor(dn_fp8_rc, "dn"); _rowmajor(up_f16_nr, "up")
+    if x_fp8.dtype != torch.float8_e4m3fn or dn_fp8_rc.dtype != torch.float8_e4m3fn or up_f16_nr.dtype != torch.float16:
+        raise TypeError("x and dn must be float8_e4m3fn, up float16")
+    M, C = x_fp8.shape
+    R, C2 = dn_fp8_rc.shape
+    N, R2 = up_f16_nr.shape
+    if C2 != C or R2 != R or bias.numel() != N or scale_x.numel() != M:
+        raise ValueError("shape mismatch")
+    ih = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=x_fp8.device)
+    check(lib().gsb200_fac_gemm_fp8_f16(x_fp8.data_ptr(), x_fp8.stride(0), scale_x.data_ptr(), dn_fp8_rc.data_ptr(),
+                                        dn_fp8_rc.stride(0), scale_dn.data_ptr(), up_f16_nr.data_ptr(),
+                                        up_f16_nr.stride(0), bias.data_ptr(), ih.data_ptr(), ih.stride(0), M, C, R, N,
+                                        _stream()), "fp8_factored_gemm")
+    return ih
+
+
 def factored_lstm_step(h_fp8_out, c_inout, hh_down, up_hh, bias_hh, x_down, up_ih, bias_ih):
     """One step of the low-rank hard-gate LSTM cell; argument order of fp8_factored_lstm_wrapper
     (fly/export_fp8_factored_lstm.py:158-182).  ``up_hh`` ``[4H, K_hh]`` and ``up_ih`` ``[4H, R]`` fp16 K-major."""

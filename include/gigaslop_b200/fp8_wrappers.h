@@ -64,6 +64,15 @@
 #ifndef F16_DOWN_PROJ_R
 #define F16_DOWN_PROJ_R 128
 #endif
+#ifndef FP8_FAC_GEMM_C
+#define FP8_FAC_GEMM_C 1024        /* fly/export_configs/rdna_fp8_factored_gemm.toml */
+#endif
+#ifndef FP8_FAC_GEMM_R
+#define FP8_FAC_GEMM_R 128
+#endif
+#ifndef FP8_FAC_GEMM_N
+#define FP8_FAC_GEMM_N 4096
+#endif
 #ifndef FP8_FACTORED_LSTM_H
 #define FP8_FACTORED_LSTM_H 1024   /* fly/export_configs/rdna_fp8_factored_lstm.toml */
 #endif
@@ -92,6 +101,7 @@ GSB200_FP8_MODULE_(fp8_dual_mxfp8)
 GSB200_FP8_MODULE_(fp8_down_proj)
 GSB200_FP8_MODULE_(f16_down_proj)
 GSB200_FP8_MODULE_(fp8_factored_lstm)
+GSB200_FP8_MODULE_(fp8_fac_gemm)
 
 /* fly/export_fp8_dual_gemm_silu.py:311-329 */
 static inline int fp8_ptq_wrapper(const fp8_ptq_Module_t* m, void* d_out_fp8, void* d_out_scale, const void* d_inp,
@@ -164,6 +174,18 @@ static inline int f16_down_proj_wrapper(const f16_down_proj_Module_t* m, void* d
   (void)m;
   return gsb200_gemm_f16_f16(d_x, F16_DOWN_PROJ_C, d_dn_rc, F16_DOWN_PROJ_C, d_x_down, F16_DOWN_PROJ_R, 0, 0, M,
                              F16_DOWN_PROJ_R, F16_DOWN_PROJ_C, 0, (gsb200_stream_t)stream);
+}
+
+/* fly/export_fp8_factored_gemm.py:178-203: ih_f16[M,N] = f16((x_fp8 . dn_fp8) * sx[m] * s_dn) . up_f16 + bias; any M.
+ * dn is taken K-major [R,C] and up K-major [N,R] instead of the RDNA pre-shuffles. */
+static inline int fp8_fac_gemm_wrapper(const fp8_fac_gemm_Module_t* m, void* d_ih_out, const void* d_x,
+                                       const void* d_scale_x, const void* d_dn_rc, const void* d_scale_dn,
+                                       const void* d_up_nr, const void* d_bias, int32_t M, cudaStream_t stream) {
+  (void)m;
+  return gsb200_fac_gemm_fp8_f16((const uint8_t*)d_x, FP8_FAC_GEMM_C, (const float*)d_scale_x, (const uint8_t*)d_dn_rc,
+                                 FP8_FAC_GEMM_C, (const float*)d_scale_dn, d_up_nr, FP8_FAC_GEMM_R, (const float*)d_bias,
+                                 d_ih_out, FP8_FAC_GEMM_N, M, FP8_FAC_GEMM_C, FP8_FAC_GEMM_R, FP8_FAC_GEMM_N,
+                                 (gsb200_stream_t)stream);
 }
 
 /* fly/export_fp8_factored_lstm.py:158-182 */

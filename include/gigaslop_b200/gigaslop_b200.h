@@ -129,6 +129,17 @@ int32_t gsb200_gemm_f16_f16(const void* A, int64_t lda, const void* B, int64_t l
                             const float* scale_a, const float* scale_b, int64_t M, int32_t N, int32_t K,
                             int32_t flags, gsb200_stream_t stream);
 
+/* Hoisted low-rank input projection of the reference's LSTM in one call and without scratch
+ * (fp8_fac_gemm_wrapper, fly/export_fp8_factored_gemm.py:178-203; kernel fly/rdna_fp8_factored_gemm.py:86-435):
+ *     ih_f16[M,N] = f16( f16((x_fp8 . dn_fp8^T) * sx[m] * s_dn) . up_f16^T + bias[n] )
+ * x [M,C] E4M3 with per-token scales sx[M]; dn [R,C] E4M3 K-major with ONE scale s_dn; up [N,R] fp16 K-major;
+ * bias [N] fp32; any M.  The fp16 intermediate x_down[M,R] lives in the first R columns of each output row between
+ * the two launches the call makes (N >= R), so the caller provides no workspace.  C % 16 == 0, R % 8 == 0,
+ * R <= 256, N % 8 == 0, ldih % 8 == 0, ldup % 8 == 0. */
+int32_t gsb200_fac_gemm_fp8_f16(const uint8_t* x, int64_t ldx, const float* scale_x, const uint8_t* dn_rc, int64_t lddn,
+                                const float* scale_dn, const void* up_nr, int64_t ldup, const float* bias, void* ih,
+                                int64_t ldih, int64_t M, int32_t C, int32_t R, int32_t N, gsb200_stream_t stream);
+
 /* One step of the reference's low-rank LSTM cell (compile_fp8_factored_lstm, fly/rdna_fp8_factored_lstm.py:88-351;
  * fp8_factored_lstm_wrapper, fly/export_fp8_factored_lstm.py:158-182 -- same argument order):
  *   gates[B,4H] = hh_down[B,K_hh] . up_hh[4H,K_hh]^T + x_down[B,R] . up_ih[4H,R]^T + bias_hh + bias_ih   (f16 operands)

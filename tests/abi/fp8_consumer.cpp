@@ -34,5 +34,34 @@ int main() {
   for (size_t i = 0; i < c.size(); ++i) bad += std::fabs(__half2float(c[i]) - (float)K) > 0.5f;
   std::printf("fp8_gemm_wrapper rc=%d mismatches=%d\n", rc, bad);
   fp8_gemm_Module_Unload(&mod);
-  return (rc == 0 && bad == 0) ? 0 : 1;
+  if (rc != 0 || bad != 0) return 1;
+
+  // fp8_fac_gemm_wrapper (fly/export_fp8_factored_gemm.py:178-203), known answer: x = 1, dn = 1 (scale 1/8),
+  // sx = 1/8 -> x_down = C/64 = 16; up = 1/4, bias = 3 -> ih = 16 * R / 4 + 3 = 515.
+  {
+    const int Mf = 300, C = FP8_FAC_GEMM_C, R = FP8_FAC_GEMM_R, Nf = FP8_FAC_GEMM_N;
+    fp8_fac_gemm_Module_t fm;
+    if (fp8_fac_gemm_Module_Load(&fm, "unused.hsaco") != 0) { std::printf("module load failed\n"); return 2; }
+    std::vector<uint8_t> x((size_t)Mf * C, 0x38), dn((size_t)R * C, 0x38);
+    std::vector<float> sx(Mf, 0.125f), sdn(1, 0.125f), bias(Nf, 3.0f);
+    std::vector<__half> up((size_t)Nf * R, __float2half(0.25f)), ih((size_t)Mf * Nf);
+    void *d_x, *d_dn, *d_sx, *d_sdn, *d_up, *d_bias, *d_ih;
+    cudaMalloc(&d_x, x.size()); cudaMalloc(&d_dn, dn.size()); cudaMalloc(&d_sx, Mf * 4); cudaMalloc(&d_sdn, 4);
+    cudaMalloc(&d_up, up.size() * 2); cudaMalloc(&d_bias, Nf * 4); cudaMalloc(&d_ih, ih.size() * 2);
+    cudaMemcpy(d_x, x.data(), x.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_dn, dn.data(), dn.size(), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_sx, sx.data(), Mf * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_sdn, sdn.data(), 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_up, up.data(), up.size() * 2, cudaMemcpyHostToDevice);
+    cudaMemcpy(d_bias, bias.data(), Nf * 4, cudaMemcpyHostToDevice);
+    const int rc2 = fp8_fac_gemm_wrapper(&fm, d_ih, d_x, d_sx, d_dn, d_sdn, d_up, d_bias, Mf, st);
+    cudaStreamSynchronize(st);
+    cudaMemcpy(ih.data(), d_ih, ih.size() * 2, cudaMemcpyDeviceToHost);
+    int bad2 = 0;
+    for (size_t i = 0; i < ih.size(); ++i) bad2 += std::fabs(__half2float(ih[i]) - 515.0f) > 0.5f;
+    std::printf("fp8_fac_gemm_wrapper rc=%d mismatches=%d\n", rc2, bad2);
+    fp8_fac_gemm_Module_Unload(&fm);
+    if (rc2 != 0 || bad2 != 0) return 1;
+  }
+  return 0;
 }

@@ -80,3 +80,28 @@ def test_factored_gemm_chain_matches_reference_golden():
     ih = g.gemm_f16(x_down, up.half().cuda()).float().cpu() + bias
     ref = T(gd["ih"])
     assert float((ih - ref).abs().max() / ref.abs().max()) < 0.08
+
+
+@pytest.mark.parametrize("M", [256, 1000, 1])
+def test_fused_factored_gemm_entry_point(M):
+    """gsb200_fac_gemm_fp8_f16 (one call, no scratch: the fp16 intermediate lives inside the output) against the
+    reference's fp32 chain (fly/bench_factored_gemm.py:54-55, rel < 0.08) and, tightly, against the same two
+    rounding points done on the CPU."""
+    g = need_lib()
+    gen = torch.Generator().manual_seed(100 + M)
+    C, R, N = 1024, 128, 4096
+    x = torch.randn(M, C, generator=gen) * 0.1
+    dn = torch.randn(R, C, generator=gen) * 0.1
+    up = (torch.randn(N, R, generator=gen) * 0.1).half()
+    bias = torch.randn(N, generator=gen) * 0.05
+    x8, sx = oracle.fp8_quantize_per_token(x)
+    dn8, sdn = oracle.fp8_quantize_scalar(dn)
+    ih = g.fp8_factored_gemm(x8.cuda(), sx.cuda(), dn8.cuda(), sdn.cuda(), up.cuda(), bias.cuda()).float().cpu()
+    ref = oracle.factored_gemm_ref(x, dn, up.float(), bias)
+    assert float((ih - ref).abs().max() / ref.abs().max()) < 0.08
+    x_down = oracle.down_proj_ref(x8, sx, dn8, sdn).half()
+    model = (x_down.double() @ up.double().t()).float() + bias
+    assert_close(ih, model.half().float(), atol=float(model.abs().max()) * 2 ** -9, rtol=1e-2, what="fused factored GEMM")
+    # the two-call form gives the same bytes
+    two = g.gemm_f16(g.fp8_down_proj(x8.cuda(), sx.cuda(), dn8.cuda(), sdn.cuda()), up.cuda()).float().cpu()
+    assert float(((two + bias).half().float() - ih).abs().max()) <= float(model.abs().max()) * 2 ** -9
