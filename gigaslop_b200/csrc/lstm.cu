@@ -286,6 +286,235 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, LSTM_NCOL); }
 }
 
+// ---- cluster form: the slices of a row group exchange h through distributed shared memory ---------------------
+// Same decomposition and arithmetic as lstm_recurrent_kernel, but the H/32 CTAs of a row group form ONE thread-block
+// cluster.  The h operand tile is kept unswizzled as [16-byte K chunk][row][16 bytes], in which the 128 x 32 piece a
+// CTA produces is one contiguous 4 KiB block: the CTA stages it in its own shared memory and sends it to every CTA of
+// the cluster with one bulk copy each (cp.async.bulk shared::cta -> shared::cluster), whose bytes complete the
+// destination's mbarrier.  No global scratch, no flag polling, no L2 round trips on the step's critical path, and no
+// cooperative launch (row groups do not depend on one another).
+// Operand tile and staging block are double-buffered: h_t goes to buffer t & 1 while the MMAs of step t read buffer
+// (t + 1) & 1; a CTA can only reach the copies of step t + 2 after every CTA has finished the MMAs of step t + 1.
+// Built for H <= 384 (W 48 KiB + 2 x 48 KiB h + 2 x 32 KiB ih); larger H uses the kernel above.
+constexpr int LSTMC_MAX_KB = 3;
+constexpr int LSTMC_SMEM_W = 0;
+constexpr int LSTMC_SMEM_H = LSTMC_SMEM_W + LSTMC_MAX_KB * LSTM_KB_BYTES;
+constexpr int LSTMC_HBUF = LSTMC_MAX_KB * LSTM_KB_BYTES;
+constexpr int LSTMC_SMEM_IH = LSTMC_SMEM_H + 2 * LSTMC_HBUF;
+constexpr int LSTMC_PIECE = LSTM_ROWS * LSTM_HS;                    // 4 KiB: one CTA's piece of h (two 16-byte K chunks x 128 rows)
+constexpr int LSTMC_CHUNK = LSTM_ROWS * 16;                         // 2 KiB: one 16-byte K chunk of all 128 rows
+constexpr int LSTMC_SMEM_STG = LSTMC_SMEM_IH + 2 * LSTM_IH_BYTES;   // [2] staging of this CTA's piece
+constexpr int LSTMC_SMEM_SC = LSTMC_SMEM_STG + 2 * LSTMC_PIECE;
+constexpr int LSTMC_SMEM_BAR = LSTMC_SMEM_SC + 1024;
+constexpr int LSTMC_SMEM_USED = LSTMC_SMEM_BAR + 128;
+constexpr int LSTMC_SMEM_BYTES = LSTMC_SMEM_USED + 1024;
+static_assert(LSTMC_SMEM_BYTES <= 227 * 1024 && LSTMC_SMEM_BYTES > 116 * 1024, "one CTA per SM");
+
+__global__ void __launch_bounds__(LSTM_THREADS, 1)
+lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_ih,
+                    const LstmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // every CTA of the cluster must place its tiles at the same shared-memory offsets: the window offset of the
+  // dynamic allocation is the same for all CTAs of a kernel, so the aligned base is too
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* w_s = smem + LSTMC_SMEM_W;
+  uint8_t* h_s = smem + LSTMC_SMEM_H;
+  uint8_t* ih_s = smem + LSTMC_SMEM_IH;
+  float* sc_s = reinterpret_cast<float*>(smem + LSTMC_SMEM_SC);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + LSTMC_SMEM_BAR);
+  uint64_t* w_full = bars;               // W slice landed
+  uint64_t* ih_full = bars + 1;          // [2] ih tile of a step landed
+  uint64_t* mma_done = bars + 3;         // accumulator of this step complete
+  uint64_t* h_ready = bars + 4;          // [2] every slice's piece of h has landed in this CTA's buffer (bytes counted)
+  uint8_t* stg_s = smem + LSTMC_SMEM_STG;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = blockIdx.x / p.slices;        // row group = cluster
+  const int slc = blockIdx.x % p.slices;        // hidden slice = rank inside the cluster
+  const int row0 = grp * LSTM_ROWS;
+  const int hid0 = slc * LSTM_HS;
+  const int H = p.H, B = p.B;
+
+  if (tid == 0) {
+    mbar_init(w_full, 1); mbar_init(&ih_full[0], 1); mbar_init(&ih_full[1], 1); mbar_init(mma_done, 1);
+    mbar_init(&h_ready[0], 1); mbar_init(&h_ready[1], 1);
+    // arm the first use of each buffer: h_0 arrives in buffer 0 (if there is a step 1), h_1 in buffer 1
+    if (p.T > 1) mbar_arrive_expect_tx(&h_ready[0], p.slices * LSTMC_PIECE);
+    if (p.T > 2) mbar_arrive_expect_tx(&h_ready[1], p.slices * LSTMC_PIECE);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_w); prefetch_tmap(&tm_ih);
+  }
+  if (warp == 0) { tmem_alloc(tmem_slot, LSTM_NCOL); tmem_relinquish(); }
+  if (tid < LSTM_NCOL) {
+    const int n = (tid >> 5) * H + hid0 + (tid & 31);
+    sc_s[tid] = __ldg(p.s_hh + n) * (1.0f / 448.0f);
+    sc_s[LSTM_NCOL + tid] = p.bias ? __ldg(p.bias + n) : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  cluster_sync_all();                    // every CTA's barriers exist before anyone sends to them
+  const uint32_t tmem_base = *tmem_slot;
+  const long long budget = spin_budget();
+  const bool rank_ok = cluster_ctarank() == (uint32_t)slc;
+
+  auto step_t = [&](int s) { return p.reverse ? p.T - 1 - s : s; };
+  auto issue_ih = [&](int s) {
+    uint8_t* dst = ih_s + (s & 1) * LSTM_IH_BYTES;
+    mbar_arrive_expect_tx(&ih_full[s & 1], LSTM_IH_BYTES);
+    const int r = step_t(s) * B + row0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) tma_load_2d(dst + g * (LSTM_ROWS * LSTM_HS * 2), &tm_ih, &ih_full[s & 1], g * H + hid0, r);
+  };
+  if (tid == 0) {
+    mbar_arrive_expect_tx(w_full, p.k_blocks * LSTM_KB_BYTES);
+    for (int kb = 0; kb < p.k_blocks; ++kb)
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        tma_load_2d(w_s + kb * LSTM_KB_BYTES + g * (LSTM_HS * 128), &tm_w, w_full, kb * 128, g * H + hid0);
+    issue_ih(0);
+    if (p.T > 1) issue_ih(1);
+  }
+
+  const int q = warp & 3, half = warp >> 2;
+  const int r_loc = q * 32 + lane;
+  const int row = row0 + r_loc;
+  const bool row_ok = row < B;
+  float c[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    c[j] = (p.c0 && row_ok) ? __half2float(p.c0[(long long)row * H + hid0 + half * 16 + j]) : 0.f;
+  const int my_col = hid0 + half * 16;   // this thread's 16 hidden units = K chunk `half` of the CTA's piece
+
+  bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10, budget) && rank_ok;
+  if (!rank_ok && tid == 0) { *abort_flag = 1; atomicOr(&g_status[0], ST_TIMEOUT_LSTM); g_status[1] = 0x50; }
+
+  // ---- step 0 reads h_0 (or zeros) from buffer 1, staged by this CTA's own threads -------------------------
+  {
+    const int chunks_per_row = H >> 4;
+    for (int id = tid; id < LSTM_ROWS * chunks_per_row; id += LSTM_THREADS) {
+      const int r = id / chunks_per_row, cc = id % chunks_per_row;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (p.h0 && row0 + r < B) v = __ldcg(reinterpret_cast<const uint4*>(p.h0 + (size_t)(row0 + r) * H + cc * 16));
+      *reinterpret_cast<uint4*>(h_s + LSTMC_HBUF + cc * LSTMC_CHUNK + r * 16) = v;
+    }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+
+  for (int s = 0; s < p.T; ++s) {
+    if (*abort_flag || !ok) break;
+    const int rb = (s + 1) & 1;                       // buffer that holds h_{s-1}
+    // ---- 1. the tile of h_{s-1} is complete once every slice has arrived; then the MMAs ---------------------
+    if (tid == 0) {
+      if (s > 0) {
+        ok = mbar_wait_cluster(&h_ready[rb], ((s - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x40, budget);
+        // arm this buffer's next use: h_{s+1} arrives in it if there is a step s + 2
+        if (ok && s + 2 < p.T) mbar_arrive_expect_tx(&h_ready[rb], p.slices * LSTMC_PIECE);
+      }
+      if (ok) {
+        tc_fence_after();
+        constexpr uint32_t idesc = umma_idesc(1, 0, 0, LSTM_ROWS, LSTM_NCOL);
+        const uint64_t a_desc = umma_smem_desc_kchunks(smem_u32(h_s + rb * LSTMC_HBUF), LSTMC_CHUNK);
+        const int ksteps = H >> 5;                    // 32 bytes of K per MMA
+        for (int ks = 0; ks < ksteps; ++ks) {
+          const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(w_s + (ks >> 2) * LSTM_KB_BYTES));
+          umma_f8(tmem_base, a_desc + (uint64_t)ks * (2 * LSTMC_CHUNK >> 4), b_desc + 2 * (ks & 3), idesc, ks != 0);
+        }
+        umma_commit(mma_done);
+      } else {
+        *abort_flag = 1;
+      }
+    }
+    // ---- 2. gate math on this thread's row ---------------------------------------------------------------------
+    ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20, budget) &&
+         mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30, budget);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      uint32_t acc[4][16];
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * LSTM_HS + half * 16, acc[g]);
+      tmem_ld_wait();
+      const uint8_t* ihb = ih_s + (s & 1) * LSTM_IH_BYTES;
+      float hv[16];
+#pragma unroll
+      for (int j0 = 0; j0 < 16; j0 += 8) {
+        float pre[4][8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int piece = half * 2 + (j0 >> 3);
+          const uint4 raw = *reinterpret_cast<const uint4*>(ihb + g * (LSTM_ROWS * LSTM_HS * 2) + r_loc * 64 +
+                                                            ((piece ^ ((r_loc >> 1) & 3)) << 4));
+          const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h2[i]);
+            const int col = g * LSTM_HS + half * 16 + j0 + 2 * i;
+            pre[g][2 * i] = fmaf(__uint_as_float(acc[g][j0 + 2 * i]), sc_s[col], f.x + sc_s[LSTM_NCOL + col]);
+            pre[g][2 * i + 1] = fmaf(__uint_as_float(acc[g][j0 + 2 * i + 1]), sc_s[col + 1], f.y + sc_s[LSTM_NCOL + col + 1]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float ig = sigmoid_f(pre[0][i]), fg = sigmoid_f(pre[1][i]), gg = tanh_f(pre[2][i]), og = sigmoid_f(pre[3][i]);
+          const float cn = fmaf(fg, c[j0 + i], ig * gg);
+          hv[j0 + i] = og * tanh_f(cn);
+          c[j0 + i] = __half2float(__float2half_rn(cn));
+        }
+      }
+      uint32_t w8[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i] * 448.f, hv[4 * i + 1] * 448.f), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i + 2] * 448.f, hv[4 * i + 3] * 448.f), __NV_SATFINITE, __NV_E4M3);
+        w8[i] = lo | (hi << 16);
+      }
+      // ---- 3. stage this CTA's piece of h_s (K chunk `half`, 16 bytes per row) ...
+      uint8_t* stg = stg_s + (s & 1) * LSTMC_PIECE;
+      *reinterpret_cast<uint4*>(stg + half * LSTMC_CHUNK + r_loc * 16) =
+          row_ok ? make_uint4(w8[0], w8[1], w8[2], w8[3]) : make_uint4(0, 0, 0, 0);
+      fence_proxy_async_smem();                       // generic-proxy staging stores before the bulk copies read them
+      tc_fence_before();
+      __syncthreads();
+      // ---- 4. ... and send it into buffer s & 1 of every CTA of the row group, one bulk copy each --------------
+      if (s + 1 < p.T && tid < p.slices) {
+        const uint32_t dst = mapa_shared(smem_u32(h_s + (s & 1) * LSTMC_HBUF + slc * LSTMC_PIECE), (uint32_t)tid);
+        bulk_copy_to_cluster(dst, stg, LSTMC_PIECE, mapa_shared(smem_u32(&h_ready[s & 1]), (uint32_t)tid));
+      }
+      if (tid == 0 && s + 2 < p.T) issue_ih(s + 2);
+      // ---- 5. the layer's outputs ------------------------------------------------------------------------------------
+      if (row_ok) {
+        const size_t toff = (size_t)step_t(s) * B * H + (size_t)row * H + my_col;
+        if (p.h8_out) *reinterpret_cast<uint4*>(p.h8_out + toff) = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+        if (p.h_out) {
+          uint32_t w16[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w16[i] = pack_half2(hv[2 * i], hv[2 * i + 1]);
+          *reinterpret_cast<uint4*>(p.h_out + toff) = make_uint4(w16[0], w16[1], w16[2], w16[3]);
+          *reinterpret_cast<uint4*>(p.h_out + toff + 8) = make_uint4(w16[4], w16[5], w16[6], w16[7]);
+        }
+      }
+    } else {
+      tc_fence_before();
+      __syncthreads();
+    }
+  }
+
+  if (p.c_last && row_ok) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) p.c_last[(long long)row * H + my_col + j] = __float2half_rn(c[j]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, LSTM_NCOL); }
+  cluster_sync_all();                    // nobody leaves while another CTA of the cluster may still store into it
+}
+
 // ---- host -------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFnL)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -365,6 +594,41 @@ int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return GSB200_ERR_BAD_ARG;
+  }
+  // Cluster form first (h exchanged through distributed shared memory): H <= 384, the slices of a row group in one
+  // cluster of H / 32 CTAs (more than 8 needs the non-portable cluster size).  GSB200_LSTM_NO_CLUSTER=1 in the
+  // environment, or a device that cannot host such a cluster, selects the cooperative kernel with global scratch.
+  static int no_cluster = -1;
+  if (no_cluster < 0) {
+    const char* ev = getenv("GSB200_LSTM_NO_CLUSTER");
+    no_cluster = (ev && ev[0] == '1') ? 1 : 0;
+  }
+  if (!no_cluster && p.k_blocks <= LSTMC_MAX_KB && slices <= 16) {
+    static int cluster_state[64];          // 0 unknown, 1 attributes set, -1 unavailable
+    if (dev >= 0 && dev < 64 && cluster_state[dev] == 0) {
+      cudaError_t ce = cudaFuncSetAttribute(lstm_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LSTMC_SMEM_BYTES);
+      if (ce == cudaSuccess && slices > 8)
+        ce = cudaFuncSetAttribute(lstm_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      cluster_state[dev] = ce == cudaSuccess ? 1 : -1;
+      if (ce != cudaSuccess) cudaGetLastError();
+    }
+    if (dev >= 0 && dev < 64 && cluster_state[dev] == 1) {
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LSTM_THREADS);
+      cfg.dynamicSmemBytes = LSTMC_SMEM_BYTES; cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = slices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      int max_clusters = 0;
+      cudaError_t ce = cudaOccupancyMaxActiveClusters(&max_clusters, lstm_cluster_kernel, &cfg);
+      if (ce == cudaSuccess && max_clusters >= 1) {
+        ce = cudaLaunchKernelEx(&cfg, lstm_cluster_kernel, tw, tih, p);
+        if (ce == cudaSuccess) return GSB200_OK;
+      }
+      cudaGetLastError();                  // fall through to the cooperative kernel
+      cluster_state[dev] = -1;
+    }
   }
   void* args[3] = {&tw, &tih, &p};
   e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(lstm_recurrent_kernel), dim3(grid), dim3(LSTM_THREADS), args,

@@ -103,6 +103,60 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// ---- thread-block clusters: distributed shared memory ------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint4 v) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(cluster_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Arrive on an mbarrier of another CTA of the cluster; release at cluster scope, so what this thread wrote (and
+// what a CTA barrier ordered before it) is visible to whoever acquires the barrier's completion.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitSuspendNs)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a barrier that threads of other CTAs of the cluster arrive at (same contract as mbar_wait).
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned int fail_code, unsigned int where, long long budget) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  long long t0 = clock64();
+  int spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > budget) {
+        *abort_flag = 1;
+        atomicOr(&g_status[0], fail_code);
+        g_status[1] = where;
+        __threadfence();
+        return false;
+      }
+    }
+  }
+}
+// Hardware barrier over every thread of the cluster (each CTA's shared memory stays valid until all have arrived).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ---- TMA --------------------------------------------------------------------
 // Untiled bulk copy global -> shared that reports its bytes to an mbarrier.  Both addresses 16-byte aligned,
 // size a multiple of 16 bytes.
@@ -180,6 +234,26 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)1 << 46;                            // [46,48) descriptor version (Blackwell)
   d |= (uint64_t)2 << 61;                            // [61,64) layout: SWIZZLE_128B
   return d;
+}
+
+// Descriptor for an unswizzled K-major operand kept as [16-byte K chunk][row][16 bytes]: the 8 x 16-byte core
+// matrices of one K chunk follow each other every 128 bytes (stride byte offset), the next K chunk starts
+// `chunk_bytes` further on (leading byte offset).  One 32-byte K step of an 8-bit MMA spans two chunks, so stepping
+// along K adds 2 * chunk_bytes >> 4 to the start-address field.
+__device__ __forceinline__ uint64_t umma_smem_desc_kchunks(uint32_t smem_addr, uint32_t chunk_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((chunk_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(128 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;                                          // layout bits [61,64) = 0: no swizzle
+}
+// Bulk copy from this CTA's shared memory into the shared memory of a CTA of the cluster; the bytes are reported
+// to an mbarrier of the destination CTA (both destination addresses are cluster addresses from mapa_shared).
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster_addr, const void* src, uint32_t bytes,
+                                                     uint32_t mbar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster_addr), "r"(smem_u32(src)), "r"(bytes), "r"(mbar_cluster_addr) : "memory");
 }
 
 // Instruction descriptor, dense, non-block-scaled kinds.

@@ -80,3 +80,38 @@ def test_lstm_rejects_unsupported_shapes():
     W = torch.zeros(4 * 48, 48, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
     with pytest.raises(RuntimeError):
         g.lstm_layer(ih, W, torch.ones(4 * 48, device="cuda"), 4, 8)        # H % 32 != 0
+
+
+def test_cluster_and_cooperative_kernels_agree(tmp_path):
+    """The recurrence has two kernels: the cluster form (h exchanged through distributed shared memory, H <= 384) and
+    the cooperative form with global scratch (any H <= 512, and the fallback).  Same arithmetic, so the same bytes:
+    the cooperative form is forced in a child process through GSB200_LSTM_NO_CLUSTER=1."""
+    import os
+    import subprocess
+    import sys
+    g = need_lib()
+    T, B, H = 30, 300, 384
+    gen = torch.Generator().manual_seed(77)
+    L = make_layer(gen, H, 64)
+    ih = (torch.randn(T * B, 4 * H, generator=gen) * 0.5).half()
+    h0 = ((torch.rand(B, H, generator=gen) * 2 - 1) * 448).to(torch.float8_e4m3fn)
+    inp = tmp_path / "in.pt"
+    out = tmp_path / "out.pt"
+    torch.save(dict(ih=ih, W=L["W_hh"], s=L["s_hh"], b=L["b"], h0=h0, T=T, B=B), inp)
+    code = (
+        "import sys, torch; sys.path.insert(0, %r); import gigaslop_b200 as g\n"
+        "d = torch.load(%r)\n"
+        "h16, h8, c = g.lstm_layer(d['ih'].cuda(), d['W'].cuda(), d['s'].cuda(), d['T'], d['B'], bias=d['b'].cuda(),\n"
+        "                          h0=d['h0'].cuda(), want_c=True)\n"
+        "torch.save(dict(h16=h16.cpu(), h8=h8.cpu().view(torch.uint8), c=c.cpu()), %r)\n"
+    ) % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), str(inp), str(out))
+    env = dict(os.environ, GSB200_LSTM_NO_CLUSTER="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = torch.load(out)
+    h16, h8, c = g.lstm_layer(ih.cuda(), L["W_hh"].cuda(), L["s_hh"].cuda(), T, B, bias=L["b"].cuda(), h0=h0.cuda(),
+                              want_c=True)
+    assert torch.equal(h16.cpu(), ref["h16"])
+    assert torch.equal(h8.cpu().view(torch.uint8), ref["h8"])
+    assert torch.equal(c.cpu(), ref["c"])
+    assert g.device_status()[0] == 0
