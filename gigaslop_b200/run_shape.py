@@ -14,6 +14,8 @@ three buffer sets so that no launch finds its inputs in L2.  Ops (shapes of the 
     mx_gemm / mx_dual_silu       block-scaled (kind::mxf8f6f4) GEMMs            (config 4)
     ih_proj                      hoisted LSTM input projection [M,384]x[1536,384] (config 5; M = T*B)
     lstm_layer                   persistent recurrence, B=512 H=384, T = M / 512  (config 5)
+    lstm_stack                   the 5-layer stack of config 5 (hoisted projection + recurrence per layer,
+                                 alternating direction), T = M / 512
     fac_gemm                     low-rank input projection C=1024 R=128 N=4096
 """
 import argparse
@@ -21,7 +23,7 @@ import argparse
 import torch
 
 from . import ops
-from .lstm import lstm_layer, lstm_scratch
+from .lstm import lstm_layer, lstm_scratch, lstm_stack
 
 DEV = "cuda"
 
@@ -102,6 +104,19 @@ def build(op, M, K):
         scr = lstm_scratch(B, H, DEV)
         return (lambda i: lstm_layer(ih, W, s, T, B, bias=b, scratch=scr)), 2.0 * T * B * 4 * H * H, \
             T * B * 4 * H * 2 + T * B * H * 3
+    if op == "lstm_stack":
+        B, H, NL = 512, 384, 5
+        T = max(1, M // B)
+        layers = []
+        for _ in range(NL):
+            layers.append(dict(W_ih=_f8(g, 4 * H, H, amp=44.8), s_ih=torch.full((4 * H,), 1 / 448.0, device=DEV),
+                               b=(0.05 * torch.randn(4 * H, generator=g)).to(DEV),
+                               W_hh=_f8(g, 4 * H, H, amp=44.8), s_hh=torch.full((4 * H,), 1 / 448.0, device=DEV)))
+        x8 = _f8(g, T * B, H)
+        sx = torch.full((T * B,), 1 / 448.0, device=DEV)
+        scr = lstm_scratch(B, H, DEV)
+        return (lambda i: lstm_stack(x8, sx, layers, T, B, scratch=scr)), NL * 2 * 2.0 * T * B * 4 * H * H, \
+            NL * (T * B * H + 2 * T * B * 4 * H * 2 + T * B * H * 3)
     if op == "fac_gemm":
         C, R, N = 1024, 128, 4096
         x = [_f8(g, M, C, amp=100.0) for _ in range(sets)]
