@@ -33,6 +33,8 @@ SIGNATURES = {
     "gsb200_gemm_fp8_rotary_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i32, _i32,
                                           _i32, _i32, _i32, _i32, _i64, _i32, _p]),
     "gsb200_gemm_f16_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _p]),
+    "gsb200_module_cuda_init": (None, [_p]),
+    "gsb200_module_cuda_load_to_device": (None, [_p]),
     "gsb200_fac_gemm_fp8_f16": (_i32, [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i32, _i32, _i32, _p]),
     "gsb200_factored_lstm_step": (_i32, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_mx_tiled_scale_bytes": (_i64, [_i64, _i32]),

@@ -247,6 +247,10 @@ void module_load_to_device(void** args) {
   extern "C" void _mlir_##P##_cuda_init(void** a) { module_init(a); }                   \
   extern "C" void _mlir_##P##_cuda_load_to_device(void** a) { module_load_to_device(a); }
 
+// generic pair for headers written by gigaslop_b200.export_headers (they alias their prefix's hook names to these)
+extern "C" void gsb200_module_cuda_init(void** a) { module_init(a); }
+extern "C" void gsb200_module_cuda_load_to_device(void** a) { module_load_to_device(a); }
+
 GSB200_MODULE_HOOKS(gemm_i8_std)
 GSB200_MODULE_HOOKS(gemm_i8_rotary_N1536_K512_H8D64R64S1024)
 GSB200_MODULE_HOOKS(gemm_i8_rotary_N1536_K512_H8D64R64S2048)

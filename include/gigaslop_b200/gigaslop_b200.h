@@ -48,7 +48,14 @@ typedef struct CUstream_st* gsb200_stream_t; /* == cudaStream_t */
 /* Library / device management.  No reference counterpart: the generated
  * `<prefix>_Kernel_Module_Load` (cute/main.cpp:95-96) maps onto gsb200_init. */
 const char* gsb200_version(void);
-int32_t gsb200_init(void);                       /* validate the current device, set kernel attributes */
+int32_t gsb200_init(void);
+
+/* Module hooks behind `<prefix>_Kernel_Module_Load` of the exported-kernel headers (cute/main.cpp:14-15 declares them
+ * per prefix as `_mlir_<prefix>_cuda_init` / `_mlir_<prefix>_cuda_load_to_device`; a generated header aliases those
+ * names to this pair).  Arguments as the reference's: init(&lib_handle_ptr, &cudaError_t);
+ * load_to_device(&lib_handle_ptr, &device, &cudaError_t).  They validate the device and set kernel attributes. */
+void gsb200_module_cuda_init(void** args);
+void gsb200_module_cuda_load_to_device(void** args);                       /* validate the current device, set kernel attributes */
 int32_t gsb200_device_status(uint32_t out[4]);   /* read-and-clear the device status word (0 = healthy) */
 int32_t gsb200_set_spin_budget(uint32_t clocks); /* bound (SM clocks) for device-side waits; 0 restores the default */
 /* Launches one warp that waits on a barrier nothing signals; with a small spin budget the wait gives up and
