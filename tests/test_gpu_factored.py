@@ -105,3 +105,21 @@ def test_fused_factored_gemm_entry_point(M):
     # the two-call form gives the same bytes
     two = g.gemm_f16(g.fp8_down_proj(x8.cuda(), sx.cuda(), dn8.cuda(), sdn.cuda()), up.cuda()).float().cpu()
     assert float(((two + bias).half().float() - ih).abs().max()) <= float(model.abs().max()) * 2 ** -9
+
+
+@pytest.mark.parametrize("M,C,R,N", [(500, 512, 64, 1000), (130, 256, 256, 264), (3000, 1024, 128, 1536)])
+def test_fused_factored_gemm_other_shapes(M, C, R, N):
+    """Other ranks and widths (N not a multiple of the tile, R = 256 = the largest resident x_down, R = 64)."""
+    g = need_lib()
+    gen = torch.Generator().manual_seed(M + C + R + N)
+    x = torch.randn(M, C, generator=gen) * 0.1
+    dn = torch.randn(R, C, generator=gen) * 0.1
+    up = (torch.randn(N, R, generator=gen) * 0.1).half()
+    bias = torch.randn(N, generator=gen) * 0.05
+    x8, sx = oracle.fp8_quantize_per_token(x)
+    dn8, sdn = oracle.fp8_quantize_scalar(dn)
+    ih = g.fp8_factored_gemm(x8.cuda(), sx.cuda(), dn8.cuda(), sdn.cuda(), up.cuda(), bias.cuda()).float().cpu()
+    x_down = oracle.down_proj_ref(x8, sx, dn8, sdn).half()
+    model = (x_down.double() @ up.double().t()).float() + bias
+    assert_close(ih, model.half().float(), atol=float(model.abs().max()) * 2 ** -9, rtol=1e-2, what="fused factored GEMM")
+    assert g.device_status()[0] == 0

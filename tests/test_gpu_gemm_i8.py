@@ -240,3 +240,20 @@ def test_host_pipeline_equals_whole_batch_call():
         pipe.run(x, out, W, sw, sn, cs, 8, 64, 64, seqlen, row_offset=7)
         pipe.finish()
         assert_bitexact(out, whole, "host pipeline vs whole batch")
+
+
+@pytest.mark.parametrize("nhead,K,M,seqlen", [(6, 512, 700, 128), (1, 256, 300, 50), (3, 384, 1030, 2048), (12, 512, 260, 333)])
+def test_rotary_other_head_counts(nhead, K, M, seqlen):
+    """N = 3 * nhead * 64 that is not a multiple of the 256-column tile (tail tiles, rotated / V boundary inside a
+    tile), K below four K blocks, sequence lengths that wrap inside a row block: bit for bit against the CPU model."""
+    g = need_lib()
+    head_dim = rotary_dim = 64
+    N = 3 * nhead * head_dim
+    gen = torch.Generator().manual_seed(nhead * 1000 + K + M)
+    A, sa = oracle.quantize_tensor(torch.randn(M, K, generator=gen))
+    B, sb = rand_i8(gen, N, K), rand_scales(gen, N)
+    sn, cs = oracle.rope_tables(seqlen, rotary_dim // 2, head_dim)
+    c = g.gemm_i8_rotary(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(), nhead, head_dim, rotary_dim, seqlen)
+    exact = oracle.rotary_exact(A, B, sa, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)
+    assert f16_equal_up_to_signed_zero(c, exact) == 0
+    assert g.device_status()[0] == 0
