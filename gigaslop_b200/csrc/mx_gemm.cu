@@ -12,9 +12,13 @@
 // tcgen05.cp.32x128b.warpx4 by the MMA thread, in order with the MMAs that read it.  The instruction
 // descriptor's scale ids select the byte (the 32-block inside the stage) for each K = 32 MMA.
 //
-// Tiles are 128 rows x 128 accumulator columns; two accumulator stages (256 TMEM columns) overlap the
-// epilogue with the next tile; the scale factors use 12 further columns.  The dual form issues two N = 64
-// MMAs per K step (gate -> columns 0..63, up -> 64..127) so each keeps its own scale tile.
+// Tiles are 128 rows x 128 accumulator columns (dual: gate -> columns 0..63, up -> 64..127); two accumulator
+// stages (256 TMEM columns) overlap the epilogue with the next tile; the scale factors sit in further columns.
+// One kernel, two forms:
+//   streaming (any K)          both operands and all scale tiles pass through a 5-stage ring, tiles are dealt
+//                              round-robin; the dual form issues two N = 64 MMAs per K step so that gate and up keep
+//                              their own scale tiles.
+//   weight-stationary (K<=512) see the comment above the MXW_ constants.
 #include "capi_internal.h"
 #include "ptx.cuh"
 
@@ -35,13 +39,20 @@ constexpr int MX_SMEM_BYTES = MX_SMEM_BAR + 256 + 1024;
 constexpr int MX_TMEM_COLS = 512;                    // power of two >= 256 + 12
 constexpr int MX_SF_COL = 256;                       // SFA at +0, SFB0 at +4, SFB1 at +8
 static_assert(MX_SMEM_BYTES > 116 * 1024 && MX_SMEM_BYTES <= 227 * 1024, "one CTA per SM");
-// Weight-stationary form (K <= 512): the CTA's 128 rows of W (dual: 64 gate + 64 up) and their scale tiles stay in
-// shared memory / TMEM for the whole kernel, only A tiles + their scale tiles stream.  An N = 128 MMA runs 64 clocks,
-// so the one issuing thread has 256 clocks per 128-byte K block; its barrier wait, scale copy and commit cost more
-// than that, and the tensor core's short queue cannot hide the difference.  This form therefore keeps the
-// per-K-block work minimal: one ring stage carries TWO K blocks (one wait and one commit per 8 MMAs), the W scales
-// are copied to TMEM once, and the dual form turns its gate and up rows into ONE N = 128 operand (the 64 + 64 rows
-// are adjacent in shared memory; their scale tile is assembled from the two tiles' row groups once per CTA).
+// Weight-stationary form (K <= 512): CTA (group g, slice n) keeps the 128 rows of W of column slice n (dual: 64 gate
+// + 64 up) in shared memory and their scale tiles in TMEM for the whole launch and walks row blocks g, g + groups,
+// ...; only A tiles and their scale tiles stream.  What it is built around (all measured on B200):
+//   * an N = 128 MMA runs 64 clocks but costs the thread that issues it ~55, and a barrier wait, a scale copy and a
+//     commit cost 60-90 each: one issuing thread leaves the tensor core idle more than half the time.  Two threads
+//     can issue concurrently (the tensor core takes their MMAs in turn), so warp 1 issues the even tiles of the CTA
+//     into accumulator stage 0 and warp 2 the odd tiles into stage 1;
+//   * a producer thread that waits for a free stage and then issues its loads completes one round per ~570 clocks
+//     plus ~170 per 16 KiB box, however many stages are in flight (22 bytes per clock with one box per stage, 37
+//     with two); a second producer thread doubles that.  So one ring stage carries TWO K blocks, and warps 0 and 3
+//     fill the stages alternately;
+//   * the gate and up rows of the dual form are adjacent in shared memory and are multiplied as ONE N = 128
+//     operand; the scale tile of that operand is assembled once per CTA from the row groups of the two tiles.
+// The streaming form spends 104 us (plain) / 276 us (dual) on M = 65536, N = 2048, K = 512; this one 76 / 131 us.
 constexpr int MXW_MAX_KB = 4;
 constexpr int MXW_KPS = 2;                                           // K blocks per ring stage
 constexpr int MXW_W_BYTES = MXW_MAX_KB * MX_B_BYTES;                 // 64 KiB
@@ -66,7 +77,6 @@ struct MxParams {
   int m_blocks, n_blocks, k_blocks;
   int n_groups;                      // weight-stationary: row-block groups (grid = n_groups * n_blocks)
   const uint8_t* sfa; const uint8_t* sfb0; const uint8_t* sfb1;    // tiled scale factors
-  __half* C; long long ldc;          // output (the weight-stationary form stores from registers)
 };
 
 // Shared-memory descriptor of one scale tile for tcgen05.cp: 32 rows of 16 bytes, unswizzled K-major, 8-row
@@ -492,7 +502,6 @@ int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t
   p.n_blocks = (N + out_cols - 1) / out_cols;
   p.k_blocks = K / MX_BK;
   p.sfa = sfa; p.sfb0 = sfb0; p.sfb1 = sfb1;
-  p.C = static_cast<__half*>(C); p.ldc = ldc;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (wst) {                                                        // weight-stationary form
     int groups = sm_count() / p.n_blocks;

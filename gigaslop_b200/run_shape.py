@@ -11,7 +11,8 @@ three buffer sets so that no launch finds its inputs in L2.  Ops (shapes of the 
     dual_silu_i8 / dual_silu_fp8 SwiGLU dual GEMM N=2048 K=512                  (config 3)
     down_i8 / down_fp8           down-projection N=512 K=2048                   (config 3)
     dual_silu_mxfp8              FP8 SwiGLU emitting MXFP8                      (config 4)
-    mx_gemm / mx_dual_silu       block-scaled (kind::mxf8f6f4) GEMMs            (config 4)
+    mx_gemm / mx_dual_silu       block-scaled (kind::mxf8f6f4) GEMMs N=2048 K=512 (config 4)
+    mx_down                      block-scaled down-projection N=512 K=2048      (config 4)
     ih_proj                      hoisted LSTM input projection [M,384]x[1536,384] (config 5; M = T*B)
     lstm_layer                   persistent recurrence, B=512 H=384, T = M / 512  (config 5)
     lstm_stack                   the 5-layer stack of config 5 (hoisted projection + recurrence per layer,
@@ -82,15 +83,15 @@ def build(op, M, K):
         outs = [torch.empty(M, N, dtype=torch.float16, device=DEV) for _ in range(sets)]
         fn = ops.dual_gemm_i8_silu if kind8 is _i8 else ops.dual_gemm_fp8_silu
         return (lambda i: fn(A[i], Wg, Wu, sa, sg, su, out=outs[i])), 4.0 * M * N * K, M * K + 2 * N * K + M * N * 2
-    if op in ("mx_gemm", "mx_dual_silu"):
-        N, K = 2048, 512
+    if op in ("mx_gemm", "mx_dual_silu", "mx_down"):
+        N, K = (512, 2048) if op == "mx_down" else (2048, 512)
         A = [_f8(g, M, K) for _ in range(sets)]
         sfa = ops.mx_scales_to_tiled(torch.randint(120, 128, (M, K // 32), generator=g, dtype=torch.uint8).to(DEV), K)
         Wg, Wu = _f8(g, N, K), _f8(g, N, K)
         sfg = ops.mx_scales_to_tiled(torch.randint(120, 128, (N, K // 32), generator=g, dtype=torch.uint8).to(DEV), K)
         sfu = ops.mx_scales_to_tiled(torch.randint(120, 128, (N, K // 32), generator=g, dtype=torch.uint8).to(DEV), K)
         outs = [torch.empty(M, N, dtype=torch.float16, device=DEV) for _ in range(sets)]
-        if op == "mx_gemm":
+        if op != "mx_dual_silu":
             return (lambda i: ops.gemm_mxfp8(A[i], sfa, Wg, sfg, out=outs[i])), 2.0 * M * N * K, M * K + N * K + M * N * 2
         return (lambda i: ops.dual_gemm_mxfp8_silu(A[i], sfa, Wg, Wu, sfg, sfu, out=outs[i])), 4.0 * M * N * K, \
             M * K + 2 * N * K + M * N * 2
