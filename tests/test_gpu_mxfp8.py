@@ -78,7 +78,8 @@ def mx_operand(gen, rows, K, spread=True):
 # K <= 512 runs the weight-stationary kernel (256-column slices: N % 256 of 0, 128 and other remainders, 3 and 4
 # K blocks, ragged M, more row blocks than one group walks), K = 2048 the streaming one
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (128, 128, 512), (300, 512, 512), (1000, 512, 2048), (64, 96, 256),
-                                   (300, 384, 512), (257, 2048, 512), (200, 640, 384), (20000, 256, 512)])
+                                   (300, 384, 512), (257, 2048, 512), (200, 640, 384), (20000, 256, 512),
+                                   (20000, 256, 640), (40000, 128, 1024)])   # streaming form, several tiles per CTA: both pipelines
 def test_block_scaled_gemm(M, N, K):
     g = need_lib()
     gen = torch.Generator().manual_seed(M + N + K)
@@ -92,7 +93,7 @@ def test_block_scaled_gemm(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 64, 128), (256, 2048, 512), (1000, 192, 512), (300, 320, 512), (129, 2048, 256),
-                                   (20000, 128, 384), (700, 256, 1024)])
+                                   (20000, 128, 384), (700, 256, 1024), (20000, 128, 640)])
 def test_block_scaled_dual_silu(M, N, K):
     g = need_lib()
     gen = torch.Generator().manual_seed(3 * M + N + K)
