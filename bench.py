@@ -222,15 +222,17 @@ def run_native(args):
 
     def e2e_step():
         pipe.run(x_host, out_host, w, s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
-                 cfg["seqlen"], row_offset=row_offset)
+                 cfg["seqlen"], row_offset=row_offset, join=False)
 
     for _ in range(2):
         e2e_step()
+    pipe.join()
     barrier()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
+    for _ in range(e2e_steps):      # consecutive steps are pipelined: a step's upload overlaps the download tail of the one before
         e2e_step()
+    pipe.join()                      # the current stream (and e1) waits for the last download
     e1.record()
     barrier()
     te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -270,7 +272,7 @@ def run_native(args):
                      "kernel": "gemm_tcgen05_kernel<i8, rotary>", "bytes_per_launch": gemm_bytes},
         "e2e": {"value": world * ops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
                 "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2, "ms_per_step": e2e_ms,
-                "api": "gigaslop_b200.hostpipe.QkvRotaryHostPipeline.run (pinned host buffers, 8192-row chunks on 3 streams)"},
+                "api": "gigaslop_b200.hostpipe.QkvRotaryHostPipeline.run(join=False) + join() (pinned host buffers, 8192-row chunks on 3 streams, consecutive steps pipelined)"},
         "gpu_launches": 2 * args.steps,
         "clocks": sampler.summary(),
     }

@@ -9,6 +9,11 @@ two copy directions instead of their sum.
 
 Results are identical to one whole-batch call: the quantiser and the GEMM are
 row-wise, and each chunk's first row goes to the rotary kernel as ``row_offset``.
+
+Back-to-back batches: ``run(..., join=False)`` leaves the three streams running, so
+the upload and the kernels of the next batch overlap the download tail of this one
+(the device-side slots are handed on through events across calls); ``join()`` makes
+the current stream wait for everything queued so far, ``finish()`` the host.
 """
 import torch
 
@@ -38,9 +43,14 @@ class QkvRotaryHostPipeline:
         self.done = [torch.cuda.Event() for _ in range(depth)]    # chunk computed
         self.free_x = [torch.cuda.Event() for _ in range(depth)]  # x slot consumed by the quantiser
         self.free_o = [torch.cuda.Event() for _ in range(depth)]  # o slot downloaded
+        self.issued = 0                                           # chunks queued since construction (slot = issued % depth)
 
-    def run(self, x_host, out_host, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0):
-        """Enqueue one pass over all rows; returns after the work is queued.  ``finish()`` waits for it."""
+    def run(self, x_host, out_host, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0, join=True):
+        """Enqueue one pass over all rows; returns after the work is queued.  ``finish()`` waits for it.
+
+        ``join=True`` makes the current stream wait for the pass; with ``join=False`` the caller calls ``join()``
+        (or ``finish()``) after the last of a series of passes, and may not touch ``out_host`` before that.
+        """
         if not (x_host.is_pinned() and out_host.is_pinned()):
             raise ValueError("host buffers must be pinned (page-locked) for asynchronous copies")
         if tuple(x_host.shape) != (self.M, self.K) or tuple(out_host.shape) != (self.M, self.N):
@@ -50,17 +60,19 @@ class QkvRotaryHostPipeline:
             st.wait_stream(cur)
         n_chunks = (self.M + self.chunk - 1) // self.chunk
         for i in range(n_chunks):
-            b = i % self.depth
+            b = self.issued % self.depth
+            reuse = self.issued >= self.depth                 # the slot has been used before, in this pass or an earlier one
+            self.issued += 1
             r0 = i * self.chunk
             rows = min(self.chunk, self.M - r0)
             with torch.cuda.stream(self.h2d):
-                if i >= self.depth:
+                if reuse:
                     self.h2d.wait_event(self.free_x[b])
                 self.x[b][:rows].copy_(x_host[r0:r0 + rows], non_blocking=True)
                 self.up[b].record(self.h2d)
             with torch.cuda.stream(self.cmp):
                 self.cmp.wait_event(self.up[b])
-                if i >= self.depth:
+                if reuse:
                     self.cmp.wait_event(self.free_o[b])
                 ops.quantize_tensor(self.x[b][:rows], out=self.q[b][:rows], out_scale=self.s[b][:rows])
                 self.free_x[b].record(self.cmp)
@@ -71,9 +83,17 @@ class QkvRotaryHostPipeline:
                 self.d2h.wait_event(self.done[b])
                 out_host[r0:r0 + rows].copy_(self.o[b][:rows], non_blocking=True)
                 self.free_o[b].record(self.d2h)
+        if join:
+            self.join()
+
+    def join(self):
+        """The current stream waits for every pass queued so far (no host synchronisation)."""
+        cur = torch.cuda.current_stream(self.dev)
         cur.wait_stream(self.d2h)
         cur.wait_stream(self.cmp)
         cur.wait_stream(self.h2d)
 
     def finish(self):
+        """The host waits for every pass queued so far."""
+        self.join()
         torch.cuda.current_stream(self.dev).synchronize()

@@ -240,6 +240,15 @@ def test_host_pipeline_equals_whole_batch_call():
         pipe.run(x, out, W, sw, sn, cs, 8, 64, 64, seqlen, row_offset=7)
         pipe.finish()
         assert_bitexact(out, whole, "host pipeline vs whole batch")
+    # back-to-back passes without a join in between (the next pass starts under the download of this one), into two
+    # result buffers; 2500 rows are three chunks, so the slots rotate across the passes
+    out2 = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    out.zero_(); out2.zero_()
+    for o in (out, out2, out):
+        pipe.run(x, o, W, sw, sn, cs, 8, 64, 64, seqlen, row_offset=7, join=False)
+    pipe.finish()
+    assert_bitexact(out, whole, "pipelined passes, first buffer")
+    assert_bitexact(out2, whole, "pipelined passes, second buffer")
 
 
 @pytest.mark.parametrize("nhead,K,M,seqlen", [(6, 512, 700, 128), (1, 256, 300, 50), (3, 384, 1030, 2048), (12, 512, 260, 333)])
