@@ -26,7 +26,7 @@ class QkvRotaryHostPipeline:
     ``x_host`` and ``out_host`` must be pinned.  Weights, scales and tables stay on the device.
     """
 
-    def __init__(self, M, K, N, device, chunk_rows=8192, depth=3):
+    def __init__(self, M, K, N, device, chunk_rows=8192, depth=4):
         self.M, self.K, self.N = M, K, N
         self.dev = torch.device(device)
         self.chunk = min(chunk_rows, M)
