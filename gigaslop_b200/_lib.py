@@ -21,6 +21,7 @@ SIGNATURES = {
     "gsb200_init": (_i32, []),
     "gsb200_device_status": (_i32, [C.POINTER(C.c_uint32)]),
     "gsb200_set_spin_budget": (_i32, [C.c_uint32]),
+    "gsb200_set_sm_limit": (_i32, [_i32]),
     "gsb200_selftest_wait_timeout": (_i32, [_p]),
     "gsb200_ptq_int8": (_i32, [_p, _i32, _i64, _p, _i64, _p, _i64, _i32, _p]),
     "gsb200_ptq_fp8": (_i32, [_p, _i32, _i64, _p, _i64, _p, _i64, _i32, _i32, _p]),

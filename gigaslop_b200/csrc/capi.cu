@@ -19,6 +19,12 @@ int32_t gsb200_device_status(uint32_t out[4]) {
 
 int32_t gsb200_set_spin_budget(uint32_t clocks) { return set_spin_budget(clocks); }
 
+int32_t gsb200_set_sm_limit(int32_t sms) {
+  if (sms < 0) return GSB200_ERR_BAD_ARG;
+  set_sm_limit(sms);
+  return GSB200_OK;
+}
+
 int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream) { return selftest_wait_timeout(S(stream)); }
 
 int32_t gsb200_ptq_int8(const void* x, int32_t x_dtype, int64_t ldx, int8_t* q, int64_t ldq, float* scale, int64_t M,

@@ -55,7 +55,8 @@ int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t
                        const uint8_t* B1, long long ldb, const uint8_t* sfb0, const uint8_t* sfb1, void* C,
                        long long ldc, long long M, int N, int K, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
-int sm_count();                   // SMs of the current device (cached)
+int sm_count();                   // SMs of the current device (cached), capped by set_sm_limit
+void set_sm_limit(int sms);       // cap for the grids of the persistent kernels (0 = none)
 int32_t read_clear_status(uint32_t out[4]);
 int32_t set_spin_budget(uint32_t clocks);
 int32_t selftest_wait_timeout(cudaStream_t st);

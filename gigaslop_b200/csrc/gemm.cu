@@ -90,10 +90,14 @@ int32_t ensure_device() {
   return GSB200_OK;
 }
 
+static int g_sm_limit = 0;           // 0: no limit
+void set_sm_limit(int sms) { g_sm_limit = sms; }
+
 int sm_count() {
   int dev = 0;
   cudaGetDevice(&dev);
-  return (dev >= 0 && dev < kMaxDevices && g_dev_sms[dev] > 0) ? g_dev_sms[dev] : 148;
+  const int n = (dev >= 0 && dev < kMaxDevices && g_dev_sms[dev] > 0) ? g_dev_sms[dev] : 148;
+  return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -1,0 +1,71 @@
+"""Two-stream front end of the quantise + QKV-rotary path for a stream of device-resident batches.
+
+``quantize_tensor`` and ``gemm_i8_rotary`` of ONE batch depend on each other, those of consecutive batches do
+not.  Issued on one stream they run strictly one after the other, and every kernel boundary costs the tail of
+one kernel (SMs that have run out of work) plus the ramp of the next.  This helper puts the quantiser on a
+second stream: the quantiser of batch i+1 becomes eligible together with the GEMM of batch i and runs under
+the GEMM's ramp and tail (the GEMM stream has the higher priority, so its CTAs are placed first; a GEMM CTA
+fills an SM's register file, so the quantiser's blocks take whatever SMs are not, or no longer, occupied).
+
+Results are those of the two calls made directly: the kernels and their arguments are the same.
+"""
+import torch
+
+from . import ops
+
+
+class QkvRotaryStreamPipeline:
+    """``submit(x, out, ...)`` per batch, ``join()`` after the last; int8 activations and scales live in ``depth`` slots.
+
+    ``x`` is ``[M, K]`` fp16 on the device, ``out`` ``[M, N]`` fp16 on the device; neither may be reused before the
+    batch has finished (``join()``, or ``depth`` later submits for ``x``).
+    """
+
+    def __init__(self, M, K, N, device, depth=3):
+        if depth < 3:
+            raise ValueError("depth must be at least 3 (a slot is rewritten two batches after its GEMM was queued)")
+        self.M, self.K, self.N = M, K, N
+        self.dev = torch.device(device)
+        self.depth = depth
+        self.sq = torch.cuda.Stream(self.dev, priority=0)       # quantiser
+        self.sg = torch.cuda.Stream(self.dev, priority=-1)      # GEMM: placed first when both are pending
+        self.q = [torch.empty(M, K, dtype=torch.int8, device=self.dev) for _ in range(depth)]
+        self.s = [torch.empty(M, dtype=torch.float32, device=self.dev) for _ in range(depth)]
+        self.qdone = [torch.cuda.Event() for _ in range(depth)]
+        self.gdone = [torch.cuda.Event() for _ in range(depth)]
+        self.n = 0
+
+    def submit(self, x, out, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0, events=None):
+        """Queue one batch.  ``events``: optional pair of CUDA events recorded around the GEMM on its stream."""
+        if tuple(x.shape) != (self.M, self.K) or tuple(out.shape) != (self.M, self.N):
+            raise ValueError("tensor shapes do not match the pipeline")
+        cur = torch.cuda.current_stream(self.dev)
+        self.sq.wait_stream(cur)
+        self.sg.wait_stream(cur)
+        n, b = self.n, self.n % self.depth
+        with torch.cuda.stream(self.sq):
+            if n >= 2:          # eligible together with the GEMM of the batch before; also frees slot b (GEMM n - depth)
+                self.sq.wait_event(self.gdone[(n - 2) % self.depth])
+            ops.quantize_tensor(x, out=self.q[b], out_scale=self.s[b])
+            self.qdone[b].record(self.sq)
+        with torch.cuda.stream(self.sg):
+            self.sg.wait_event(self.qdone[b])
+            if events is not None:
+                events[0].record(self.sg)
+            ops.gemm_i8_rotary(self.q[b], w, self.s[b], s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen,
+                               row_offset=row_offset, out=out)
+            if events is not None:
+                events[1].record(self.sg)
+            self.gdone[b].record(self.sg)
+        self.n += 1
+
+    def join(self):
+        """The current stream waits for every batch queued so far (no host synchronisation)."""
+        cur = torch.cuda.current_stream(self.dev)
+        cur.wait_stream(self.sg)
+        cur.wait_stream(self.sq)
+
+    def finish(self):
+        """The host waits for every batch queued so far."""
+        self.join()
+        torch.cuda.current_stream(self.dev).synchronize()

@@ -58,6 +58,10 @@ void gsb200_module_cuda_init(void** args);
 void gsb200_module_cuda_load_to_device(void** args);                       /* validate the current device, set kernel attributes */
 int32_t gsb200_device_status(uint32_t out[4]);   /* read-and-clear the device status word (0 = healthy) */
 int32_t gsb200_set_spin_budget(uint32_t clocks); /* bound (SM clocks) for device-side waits; 0 restores the default */
+/* The persistent GEMM kernels launch at most `sms` CTAs (one per SM) from now on; 0 restores "all SMs".  A caller that
+ * runs another kernel beside a GEMM on a second stream (the quantiser of the next batch, say) leaves it a few SMs
+ * this way: a GEMM CTA fills an SM's register file, so nothing else runs on the SMs it occupies. */
+int32_t gsb200_set_sm_limit(int32_t sms);
 /* Launches one warp that waits on a barrier nothing signals; with a small spin budget the wait gives up and
  * sets bit 2 of the status word.  Exercises the give-up path without hanging the device. */
 int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream);

@@ -266,3 +266,27 @@ def test_rotary_other_head_counts(nhead, K, M, seqlen):
     exact = oracle.rotary_exact(A, B, sa, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)
     assert f16_equal_up_to_signed_zero(c, exact) == 0
     assert g.device_status()[0] == 0
+
+
+def test_stream_pipeline_equals_direct_calls():
+    """Quantiser and GEMM of consecutive batches on two streams give the bytes of the two calls made one after the other."""
+    g = need_lib()
+    from gigaslop_b200.devpipe import QkvRotaryStreamPipeline
+    gen = torch.Generator().manual_seed(33)
+    M, K, N, seqlen = 3000, 512, 1536, 777
+    W = rand_i8(gen, N, K).cuda()
+    sw = rand_scales(gen, N).cuda()
+    sn, cs = (t.cuda() for t in oracle.rope_tables(seqlen, 32, 64))
+    xs = [(torch.randn(M, K, generator=gen) * (1 + i)).half().cuda() for i in range(7)]
+    want = []
+    for x in xs:
+        q, s = g.quantize_tensor(x)
+        want.append(g.gemm_i8_rotary(q, W, s, sw, sn, cs, 8, 64, 64, seqlen, row_offset=5).cpu())
+    pipe = QkvRotaryStreamPipeline(M, K, N, "cuda")
+    outs = [torch.empty(M, N, dtype=torch.float16, device="cuda") for _ in xs]
+    for x, o in zip(xs, outs):                 # seven batches through three slots
+        pipe.submit(x, o, W, sw, sn, cs, 8, 64, 64, seqlen, row_offset=5)
+    pipe.finish()
+    for i, (o, w_) in enumerate(zip(outs, want)):
+        assert_bitexact(o.cpu(), w_, f"stream pipeline, batch {i}")
+    assert g.device_status()[0] == 0
