@@ -29,6 +29,8 @@ SIGNATURES = {
     "gsb200_gemm_i8_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_gemm_i8_rotary_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i32, _i32,
                                          _i32, _i32, _i32, _i32, _i64, _i32, _p]),
+    "gsb200_ptq_gemm_i8_rotary_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i32, _i32,
+                                             _i32, _i32, _i32, _i32, _i64, _i32, _p]),
     "gsb200_dual_gemm_i8_silu_f16": (_i32, [_p, _i64, _p, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_gemm_fp8_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_gemm_fp8_rotary_f16": (_i32, [_p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _i64, _i32, _i32,

@@ -86,6 +86,19 @@ int32_t gsb200_gemm_i8_rotary_f16(const int8_t* A, int64_t lda, const int8_t* B,
                        rotary_dim, seqlen, row_offset, flags, stream);
 }
 
+int32_t gsb200_ptq_gemm_i8_rotary_f16(const void* x_f16, int64_t ldx, const int8_t* B, int64_t ldb, void* C, int64_t ldc,
+                                      float* scale_a_out, const float* scale_b, const float* sin_tab,
+                                      const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,
+                                      int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
+                                      int32_t flags, gsb200_stream_t stream) {
+  if (!x_f16) return GSB200_ERR_BAD_ARG;
+  GemmArgs a = base_args(KIND_I8, EPI_ROTARY, nullptr, 0, B, nullptr, ldb, C, ldc, nullptr, scale_b, nullptr, M, N, K, flags);
+  a.sin_tab = sin_tab; a.cos_tab = cos_tab;
+  a.nhead = nhead; a.head_dim = head_dim; a.rotary_dim = rotary_dim; a.seqlen = seqlen; a.row_offset = row_offset;
+  a.x_f16 = static_cast<const __half*>(x_f16); a.ldx = ldx; a.scale_a_out = scale_a_out;
+  return launch_gemm(a, S(stream));
+}
+
 int32_t gsb200_dual_gemm_i8_silu_f16(const int8_t* A, int64_t lda, const int8_t* B_gate, const int8_t* B_up,
                                      int64_t ldb, void* C, int64_t ldc, const float* scale_a,
                                      const float* scale_b_gate, const float* scale_b_up, int64_t M, int32_t N,

@@ -33,6 +33,8 @@ struct GemmArgs {
   long long M; int N; int K;
   int nhead, head_dim, rotary_dim, seqlen; long long row_offset;
   int flags;
+  // fused activation quantiser (KIND_I8 + EPI_ROTARY, K <= 512): fp16 activations instead of A / scale_a
+  const __half* x_f16; long long ldx; float* scale_a_out;
 };
 int32_t launch_gemm(const GemmArgs& a, cudaStream_t st);
 struct LstmLayerArgs {

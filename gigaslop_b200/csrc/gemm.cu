@@ -81,6 +81,11 @@ int32_t ensure_device() {
       set_attr<KIND_F16, EPI_BIAS>()};
   for (cudaError_t er : errs)
     if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
+  {
+    cudaError_t er = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND_I8, EPI_ROTARY, SCHED_ARES, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
+    if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
+  }
   if (!encode_fn()) {
     fprintf(stderr, "gigaslop_b200: cuTensorMapEncodeTiled not available from the driver\n");
     return GSB200_ERR_DEVICE;
@@ -117,9 +122,17 @@ static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, co
 int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   if (a.M == 0) return GSB200_OK;
   if (a.M < 0 || a.M > 0x7fffff00ll || a.N <= 0 || a.K <= 0) return GSB200_ERR_BAD_ARG;
-  if (!a.A || !a.B0 || !a.C) return GSB200_ERR_BAD_ARG;
-  if (!aligned16(a.A) || !aligned16(a.B0) || !aligned16(a.C)) return GSB200_ERR_BAD_ARG;
-  if (a.K % 16 != 0 || a.lda < a.K || a.ldb < a.K || a.lda % 16 != 0 || a.ldb % 16 != 0) return GSB200_ERR_BAD_ARG;
+  const bool fused = a.x_f16 != nullptr;          // the int8 A operand is made on chip from fp16 activations
+  if (fused) {
+    if (a.kind != KIND_I8 || a.epi != EPI_ROTARY || a.A || a.scale_a) return GSB200_ERR_BAD_ARG;
+    if (!aligned16(a.x_f16) || a.ldx < a.K || a.ldx % 8 != 0) return GSB200_ERR_BAD_ARG;
+    if (a.K > RES_MAX_KBLOCKS * BK || a.K % BK != 0 || (a.flags & GSB200_FLAG_STREAMING)) return GSB200_ERR_UNSUPPORTED;
+  } else {
+    if (!a.A || !aligned16(a.A) || a.lda < a.K || a.lda % 16 != 0) return GSB200_ERR_BAD_ARG;
+  }
+  if (!a.B0 || !a.C) return GSB200_ERR_BAD_ARG;
+  if (!aligned16(a.B0) || !aligned16(a.C)) return GSB200_ERR_BAD_ARG;
+  if (a.K % 16 != 0 || a.ldb < a.K || a.ldb % 16 != 0) return GSB200_ERR_BAD_ARG;
   if (a.ldc < a.N) return GSB200_ERR_BAD_ARG;
   const bool dual = a.epi == EPI_SILU || a.epi == EPI_SILU_MX;
   if (a.epi == EPI_I32) {
@@ -127,7 +140,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   } else {
     if (a.N % 8 != 0 || a.ldc % 8 != 0) return GSB200_ERR_BAD_ARG;
     if (a.epi == EPI_BIAS && !a.scale_b0) return GSB200_ERR_BAD_ARG;                       // the bias vector
-    if (a.epi != EPI_DEQUANT && a.epi != EPI_BIAS && (!a.scale_a || !a.scale_b0)) return GSB200_ERR_BAD_ARG;   // plain dequant: null = 1.0
+    if (a.epi != EPI_DEQUANT && a.epi != EPI_BIAS && ((!a.scale_a && !fused) || !a.scale_b0)) return GSB200_ERR_BAD_ARG;   // plain dequant: null = 1.0
     const bool scalar_b = (a.flags & GSB200_FLAG_SCALAR_SCALE_B) != 0;
     if (scalar_b && (a.epi != EPI_DEQUANT || !a.scale_b0)) return GSB200_ERR_BAD_ARG;
     if (a.scale_b0 && !scalar_b && (reinterpret_cast<uintptr_t>(a.scale_b0) & 15)) return GSB200_ERR_BAD_ARG;
@@ -167,12 +180,13 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.row_offset = (int)(a.row_offset % p.seqlen);
   p.direct_store = (a.flags & GSB200_FLAG_DIRECT_STORE) ? 1 : 0;
   p.ablate = (a.flags >> 8) & 7;
+  p.x_f16 = a.x_f16; p.ldx = a.ldx; p.scale_a_out = a.scale_a_out;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
 
   CUtensorMap ta, tb0, tb1, tc;
   const CUtensorMapDataType u8 = CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  bool ok = make_map_2d(&ta, u8, 1, a.A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
+  bool ok = fused || make_map_2d(&ta, u8, 1, a.A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)a.lda, BK, BM);
   ok = ok && make_map_2d(&tb0, u8, 1, a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
   ok = ok && make_map_2d(&tb1, u8, 1, dual ? a.B1 : a.B0, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.ldb, BK, BN / 2);
   if (a.epi != EPI_I32 && a.epi != EPI_SILU_MX)
@@ -180,6 +194,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
                            (uint64_t)a.ldc, OUT_BOX_COLS, OUT_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B);
   else
     tc = ta;
+  if (fused) ta = tb0;                            // never used by the fused kernel
   if (!ok) return GSB200_ERR_BAD_ARG;
 
   // One operand stays resident in shared memory whenever K <= 512 (its 4 K-pieces fit): the W slice for the
@@ -208,7 +223,14 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     switch (a.epi) {
       case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       case EPI_DEQUANT: e = launch_inst<KIND_I8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_ROTARY:
+        if (fused) {
+          gemm_tcgen05_kernel<KIND_I8, EPI_ROTARY, SCHED_ARES, true><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
+          e = cudaGetLastError();
+        } else {
+          e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st);
+        }
+        break;
       case EPI_SILU: e = launch_inst<KIND_I8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;
     }

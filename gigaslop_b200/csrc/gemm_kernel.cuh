@@ -84,7 +84,11 @@ struct SmemMap {
   static constexpr int SCALE_BUFS = SCHED == SCHED_WRES ? 1 : 6;
   static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
   static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
-  static constexpr int BAR_OFF = SCALE_OFF + SCALE_BUFS * SCALE_BUF_BYTES;
+  // fused activation quantiser (activation-stationary only): the token scales of up to four row blocks in flight
+  static constexpr int SA_OFF = SCALE_OFF + SCALE_BUFS * SCALE_BUF_BYTES;
+  static constexpr int SA_BUFS = 4;
+  static constexpr int SA_BYTES = SCHED == SCHED_ARES ? SA_BUFS * BM * 4 : 0;
+  static constexpr int BAR_OFF = SA_OFF + SA_BYTES;
   static constexpr int USED = BAR_OFF + 256;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
@@ -112,6 +116,9 @@ struct GemmParams {
   int seqlen;                  // runtime sequence length: angle row = (row + row_offset) % seqlen
   int rot_cols;                // 2 * nhead * head_dim: columns below this are rotated (head_dim = 64, rotary_dim = 64)
   int row_offset;              // global row index of this shard's row 0
+  const __half* x_f16;         // fused activation quantiser: fp16 activations [M, K] (the int8 A operand is then made on chip)
+  long long ldx;               //   row stride of x_f16 in elements
+  float* scale_a_out;          //   optional: the token scales [M], as quantize_tensor would return them
   int direct_store;            // 1: plain st.global from registers instead of smem + TMA store
   int ablate;                  // timing ablations (results are then wrong): 1 = skip the output stores, 2 = skip the epilogue body
 };
@@ -195,7 +202,7 @@ struct TileWalk {
   }
 };
 
-template <int KIND, int EPI, int SCHED>
+template <int KIND, int EPI, int SCHED, bool FUSEQ = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_c,
@@ -221,7 +228,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* acc_empty = acc_full + ACC_STAGES;             // [ACC_STAGES]
   uint64_t* res_full = acc_empty + ACC_STAGES;             // [RES_MAX_KBLOCKS] resident piece landed (WRES uses [0] only)
   uint64_t* res_empty = res_full + RES_MAX_KBLOCKS;        // [RES_MAX_KBLOCKS] ARES: A piece no longer needed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_empty + RES_MAX_KBLOCKS);
+  uint64_t* sa_ready = res_empty + RES_MAX_KBLOCKS;        // [SA_BUFS] FUSEQ: token scales of a row block written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sa_ready + Map::SA_BUFS);
+  float* sa_s = reinterpret_cast<float*>(smem + Map::SA_OFF);
+  static_assert(!FUSEQ || (SCHED == SCHED_ARES && KIND == KIND_I8), "the fused quantiser feeds the resident int8 A block");
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -232,7 +242,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
-    for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], 1); mbar_init(&res_empty[s], 1); }
+    // FUSEQ: the two quantiser warps both report a finished A block
+    for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], FUSEQ ? 2 : 1); mbar_init(&res_empty[s], 1); }
+    for (int s = 0; s < Map::SA_BUFS; ++s) mbar_init(&sa_ready[s], 2);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1);
@@ -300,11 +312,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, pm * BM);
           if (++rot == p.n_blocks) rot = 0;
         } else if constexpr (ARES) {
-          if (n_blk == 0 && m_blk + (int)gridDim.x < p.m_blocks)
+          if (!FUSEQ && n_blk == 0 && m_blk + (int)gridDim.x < p.m_blocks)
             for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, (m_blk + (int)gridDim.x) * BM);
         }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if constexpr (ARES) {
+          if constexpr (ARES && !FUSEQ) {
             if (n_blk == 0) {                 // new row block: refill this K piece of A once its last reader retired
               if (!mbar_wait(&res_empty[kb], rph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x300 | kb, budget)) { ok = false; break; }
               mbar_arrive_expect_tx(&res_full[kb], A_STAGE_BYTES);
@@ -385,6 +397,91 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (ok) umma_commit(&acc_full[as]);     // accumulator complete
       }
     }
+  } else if constexpr (FUSEQ) {
+    // ------------------------------ activation quantiser (warps 2 and 3) ------------------------------
+    // Per-token absmax quantisation of this CTA's next row block, fp16 -> int8, written straight into the resident
+    // A block in the layout the MMAs read (rows of 128 bytes per K piece, 128-byte swizzle), with the arithmetic
+    // of ptq_kernel: qs = fl(fl(1 / amax) * 127), q = rne(x * qs), scale = fl(1 / qs).  One row per warp and
+    // round: lane l holds the 16 elements 16 l .. 16 l + 15 (K <= 512), i.e. chunk l % 8 of K piece l / 8.
+    // The block can only be rewritten once the MMAs of the previous row block have retired, and the next MMAs wait
+    // for it; the epilogue, which is what bounds this kernel, still has the last two tiles to drain meanwhile.
+    const int wq = warp - 2;
+    const int kvec = p.K >> 4;                          // lanes that hold data
+    int rbi = 0;
+    bool ok = true;
+    for (int m_blk = blockIdx.x; ok && m_blk < p.m_blocks; m_blk += gridDim.x, ++rbi) {
+      // the rows of the row block after this one go to L2 now (128-byte lines; 2 KiB per lane of this warp's half)
+      {
+        const long long nm = (long long)(m_blk + (int)gridDim.x) * BM;
+        if (m_blk + (int)gridDim.x < p.m_blocks) {
+          for (int r = wq * 64 + (lane >> 3); r < wq * 64 + 64; r += 4) {
+            const long long row = nm + r;
+            if (row < p.M && (lane & 7) * 64 < p.K)
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x_f16 + row * p.ldx + (lane & 7) * 64));
+          }
+        }
+      }
+      if (rbi > 0) {
+        for (int kb = 0; kb < p.k_blocks; ++kb)
+          if (!mbar_wait(&res_empty[kb], (uint32_t)(rbi - 1) & 1u, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x400 | kb, budget)) { ok = false; break; }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      float* sa_dst = sa_s + (rbi & (Map::SA_BUFS - 1)) * BM;
+      const long long row0 = (long long)m_blk * BM;
+      const uint32_t dst_lane = (uint32_t)((lane >> 3) * A_STAGE_BYTES);      // K piece of this lane
+      // rows wq, wq + 2, ... of the block, four per round so that their loads are in flight together
+      for (int r0 = wq; r0 < BM; r0 += 8) {
+        uint4 raw[4][2];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const long long row = row0 + r0 + 2 * j;
+          raw[j][0] = raw[j][1] = make_uint4(0u, 0u, 0u, 0u);
+          if (row < p.M && lane < kvec) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x_f16 + row * p.ldx + lane * 16);
+            raw[j][0] = __ldg(src); raw[j][1] = __ldg(src + 1);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = r0 + 2 * j;
+          const long long row = row0 + r;
+          __half2 m2 = __float2half2_rn(0.f);
+          const __half2* h = reinterpret_cast<const __half2*>(&raw[j][0]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) m2 = __hmax2(m2, __habs2(h[k]));
+          float amax = fmaxf(__low2float(m2), __high2float(m2));
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+          amax = fmaxf(amax, 1e-8f);
+          const float qs = __fmul_rn(__frcp_rn(amax), 127.0f);
+          const float2 q2 = make_float2(qs, qs);
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f0 = __half22float2(h[2 * k]), f1 = __half22float2(h[2 * k + 1]);
+            const float2 a2 = __fmul2_rn(f0, q2), b2 = __fmul2_rn(f1, q2);
+            uint32_t hi, lo;
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(__float2int_rn(b2.y)), "r"(__float2int_rn(b2.x)), "r"(0u));
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(lo) : "r"(__float2int_rn(a2.y)), "r"(__float2int_rn(a2.x)), "r"(hi));
+            w[k] = lo;
+          }
+          if (lane < kvec)
+            *reinterpret_cast<uint4*>(res_base + dst_lane + r * 128 + (((lane & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          if (lane == 0) {
+            const float sc = row < p.M ? __frcp_rn(qs) : 0.f;
+            sa_dst[r] = sc;
+            if (p.scale_a_out && row < p.M) p.scale_a_out[row] = sc;
+          }
+        }
+      }
+      fence_proxy_async_smem();                        // the stores above before the MMAs' reads of the block
+      __syncwarp();
+      if (lane == 0) {
+        for (int kb = 0; kb < p.k_blocks; ++kb) mbar_arrive(&res_full[kb]);
+        mbar_arrive(&sa_ready[rbi & (Map::SA_BUFS - 1)]);
+      }
+    }
   }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
@@ -406,6 +503,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // per-row state, fetched once per row block and kept in registers across its column blocks; the token
     // scale and the channel scales of the NEXT tile are fetched while the current tile is processed
     float sa = 0.f, sa_next = 0.f;
+    int fq_rbi = 0;                        // FUSEQ: row blocks this warp has started
     float2 sn2[16], cs2[16];               // sin / cos row of this thread's token as fp32 pairs
     int cur_m_blk = -1;
     int trig_m_blk = -1;                   // row block whose sin / cos rows are in sn2 / cs2
@@ -435,10 +533,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const bool row_ok = row < p.M;
 
       // ---- per-tile prologue: everything that comes from global memory, before the accumulator wait ----
+      bool new_row_block = false;            // FUSEQ: the token scale is picked up after the accumulator wait
       if constexpr (EPI != EPI_I32) {
         if (m_blk != cur_m_blk) {
           cur_m_blk = m_blk;
-          sa = sa_next;
+          if constexpr (FUSEQ) new_row_block = true; else sa = sa_next;
         }
         if constexpr (EPI == EPI_ROTARY) {
           // The angle rows cost 16 scattered 16-byte loads per thread.  Once this warp's columns lie past the
@@ -463,14 +562,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           // The rotated columns use sin and cos premultiplied by the token scale: folded in once per row block,
           // at the first tile in which this warp rotates (rows fetched ahead have arrived by then).
-          if (trig_m_blk == m_blk && !trig_scaled && n0 + wout0 < p.rot_cols) {
+          if (!FUSEQ && trig_m_blk == m_blk && !trig_scaled && n0 + wout0 < p.rot_cols) {
             trig_scaled = true;
             const float2 s2 = pk2(sa, sa);
 #pragma unroll
             for (int j = 0; j < 16; ++j) { sn2[j] = fmul2(sn2[j], s2); cs2[j] = fmul2(cs2[j], s2); }
           }
         }
-        if (tw.valid(p) && tw.m != m_blk) {
+        if (!FUSEQ && tw.valid(p) && tw.m != m_blk) {
           const int r = tw.m * BM + q * 32 + lane;
           sa_next = (r < p.M) ? (p.scale_a ? ldg_f_here(p.scale_a + r) : 1.f) : 0.f;
         }
@@ -482,6 +581,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!agreed) break;
       asm volatile("" : "+r"(agreed));   // opaque from here on: the scale address below must stay dependent on the wait
       tc_fence_after();
+      if constexpr (FUSEQ && EPI != EPI_I32) {
+        // token scales made on chip: written by the quantiser warps before the A block these MMAs read
+        if (new_row_block) {
+          const bool have = mbar_wait(&sa_ready[fq_rbi & (Map::SA_BUFS - 1)], (uint32_t)(fq_rbi / Map::SA_BUFS) & 1u, abort_flag,
+                                      ST_TIMEOUT_EPILOGUE, (2u << 16) | 0x500, budget);
+          if (!__all_sync(0xffffffffu, have)) break;
+          sa = sa_s[(fq_rbi & (Map::SA_BUFS - 1)) * BM + q * 32 + lane];
+          ++fq_rbi;
+        }
+        if constexpr (EPI == EPI_ROTARY) {
+          if (trig_m_blk == m_blk && !trig_scaled && n0 + wout0 < p.rot_cols) {
+            trig_scaled = true;
+            const float2 s2 = pk2(sa, sa);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { sn2[j] = fmul2(sn2[j], s2); cs2[j] = fmul2(cs2[j], s2); }
+          }
+        }
+      }
       // The tile's channel scales landed with its first K block, before the MMAs that have now completed.
       // They are read with loads the compiler may move across the staging stores below (plain loads would
       // be kept in order with every store to shared memory); the address depends on the outcome of the

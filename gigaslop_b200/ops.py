@@ -126,6 +126,32 @@ def gemm_i8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, ro
                    nhead, head_dim, rotary_dim, seqlen, row_offset, out, flags, _I8)
 
 
+def quantize_gemm_i8_rotary(x, B, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
+                            row_offset=0, out=None, out_scale=None, flags=0):
+    """``gemm_i8_rotary(*quantize_tensor(x), ...)`` in one launch: fp16 ``x`` [M, K] in, the int8 operand is made on
+    chip.  Same bytes as the two calls.  ``out_scale`` (optional, [M] fp32) receives the token scales."""
+    _need_cuda(x, B, scale_b, sin_buf, cos_buf)
+    if x.dtype != torch.float16 or B.dtype != torch.int8 or x.dim() != 2 or B.dim() != 2 or x.shape[1] != B.shape[1]:
+        raise ValueError("x must be fp16 [M, K] and B int8 [N, K]")
+    if x.stride(1) != 1 or B.stride(1) != 1:
+        raise ValueError("rows must be contiguous")
+    if sin_buf.dtype != torch.float32 or not sin_buf.is_contiguous() or not cos_buf.is_contiguous():
+        raise ValueError("sin/cos must be contiguous float32 [seqlen, rotary_dim/2]")
+    if sin_buf.shape[0] < seqlen or sin_buf.shape[1] != rotary_dim // 2:
+        raise ValueError("sin/cos table smaller than seqlen")
+    M, K = x.shape
+    N = B.shape[0]
+    C = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=x.device)
+    if out_scale is not None and (out_scale.dtype != torch.float32 or out_scale.numel() < M or not out_scale.is_cuda):
+        raise ValueError("out_scale must be a CUDA float32 tensor of at least M elements")
+    check(lib().gsb200_ptq_gemm_i8_rotary_f16(
+        x.data_ptr(), x.stride(0), B.data_ptr(), B.stride(0), C.data_ptr(), C.stride(0),
+        out_scale.data_ptr() if out_scale is not None else None, scale_b.data_ptr(), sin_buf.data_ptr(),
+        cos_buf.data_ptr(), M, N, K, nhead, head_dim, rotary_dim, seqlen, row_offset, flags, _stream()),
+        "quantize_gemm_i8_rotary")
+    return C
+
+
 def gemm_fp8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
                     row_offset=0, out=None, flags=0):
     """FP8 QKV GEMM + rotary (fly/rdna_fp8_gemm_rotary.py compile_fp8_gemm_rotary)."""

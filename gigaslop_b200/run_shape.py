@@ -8,6 +8,7 @@ three buffer sets so that no launch finds its inputs in L2.  Ops (shapes of the 
     ptq_int8 / ptq_fp8           per-token quantiser, [M, 512] fp16           (--K for another width)
     gemm_i8 / gemm_fp8           dequant GEMM N=512 K=512                       (config 1)
     rotary_i8 / rotary_fp8       QKV GEMM + rotary N=1536 K=512                 (config 2)
+    ptq_rotary_i8                per-token quantiser fused into the QKV GEMM + rotary, fp16 in (config 2)
     dual_silu_i8 / dual_silu_fp8 SwiGLU dual GEMM N=2048 K=512                  (config 3)
     down_i8 / down_fp8           down-projection N=512 K=2048                   (config 3)
     dual_silu_mxfp8              FP8 SwiGLU emitting MXFP8                      (config 4)
@@ -52,6 +53,15 @@ def build(op, M, K):
         if op == "ptq_int8":
             return (lambda i: ops.quantize_tensor(xs[i], out=q, out_scale=s)), None, M * K * 3 + M * 4
         return (lambda i: ops.fp8_quantize_per_token(xs[i], torch_formulation=False, out=q, out_scale=s)), None, M * K * 3 + M * 4
+    if op == "ptq_rotary_i8":
+        N, K = 1536, 512
+        xs = [torch.randn(M, K, generator=g).half().to(DEV) for _ in range(sets)]
+        W = _i8(g, N, K)
+        sb = _scales(g, N)
+        sin, cos = (t.to(DEV) for t in (torch.randn(2048, 32, generator=g), torch.randn(2048, 32, generator=g)))
+        outs = [torch.empty(M, N, dtype=torch.float16, device=DEV) for _ in range(sets)]
+        return (lambda i: ops.quantize_gemm_i8_rotary(xs[i], W, sb, sin, cos, 8, 64, 64, 2048, out=outs[i])), \
+            2.0 * M * N * K, M * K * 2 + N * K + M * N * 2 + 4 * N
     kind8 = _i8 if op.endswith("i8") else _f8
     if op in ("gemm_i8", "gemm_fp8", "down_i8", "down_fp8", "rotary_i8", "rotary_fp8", "ih_proj"):
         N, K = {"gemm": (512, 512), "down": (512, 2048), "rotary": (1536, 512), "ih": (1536, 384)}[op.split("_")[0]]

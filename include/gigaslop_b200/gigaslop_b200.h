@@ -103,6 +103,22 @@ int32_t gsb200_gemm_i8_rotary_f16(const int8_t* A, int64_t lda, const int8_t* B,
                                   int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
                                   int32_t flags, gsb200_stream_t stream);
 
+/* Per-token int8 quantisation of fp16 activations FUSED into the QKV + rotary GEMM: x_f16 [M, K] goes in, the int8
+ * operand is made on chip (two warps of each CTA write it into the shared-memory block the MMAs read, with the
+ * arithmetic of gsb200_ptq_int8), and never travels to memory.  The result is bit-identical to gsb200_ptq_int8
+ * followed by gsb200_gemm_i8_rotary_f16 (quantize_tensor, cute/ampere_gemm_i8_quant_rmem.py:1029-1033, then
+ * `cute_dsl_gemm_i8_rotary_*_wrapper`, cute/export_gemm_i8_rotary.py:69-82).  scale_a_out: optional [M] fp32, receives
+ * the token scales.  K must be a multiple of 128 and at most 512, ldx a multiple of 8.  A new entry point beside
+ * the drop-in ones: the reference has no fused form.  It saves the int8 round trip through memory but, as built, not
+ * time: the two quantiser warps share their schedulers with the epilogue warps that bound the GEMM, and the MMAs of a
+ * row block wait for them (config 2: 201 us against 97 us for the two calls, 92 us for the two calls on two streams).
+ * Use it where the int8 copy of the activations must not exist; otherwise the two calls. */
+int32_t gsb200_ptq_gemm_i8_rotary_f16(const void* x_f16, int64_t ldx, const int8_t* B, int64_t ldb, void* C, int64_t ldc,
+                                      float* scale_a_out, const float* scale_b, const float* sin_tab,
+                                      const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,
+                                      int32_t head_dim, int32_t rotary_dim, int32_t seqlen, int64_t row_offset,
+                                      int32_t flags, gsb200_stream_t stream);
+
 /* C_f16 = silu(A.Bg^T * sA*sBg) * (A.Bu^T * sA*sBu).  TensorOpDualGemmI8Silu
  * (cute/ampere_dual_gemm_i8_silu.py:36-438; export at cute/export_dual_gemm_i8_silu.py:53-63). */
 int32_t gsb200_dual_gemm_i8_silu_f16(const int8_t* A, int64_t lda, const int8_t* B_gate, const int8_t* B_up,

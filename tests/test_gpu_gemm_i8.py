@@ -290,3 +290,25 @@ def test_stream_pipeline_equals_direct_calls():
     for i, (o, w_) in enumerate(zip(outs, want)):
         assert_bitexact(o.cpu(), w_, f"stream pipeline, batch {i}")
     assert g.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("M,K,nhead,seqlen", [(300, 512, 8, 2048), (128, 128, 8, 64), (1000, 256, 3, 333), (2500, 384, 6, 100),
+                                              (40000, 512, 8, 2048)])
+def test_fused_quantise_rotary_equals_two_calls(M, K, nhead, seqlen):
+    """fp16 activations quantised on chip inside the QKV + rotary GEMM: the bytes of quantize_tensor + gemm_i8_rotary
+    (ragged M, 1 to 4 K pieces, several row blocks per CTA, N that is not a multiple of the tile) and the same scales."""
+    g = need_lib()
+    N = 3 * nhead * 64
+    gen = torch.Generator().manual_seed(M + K + nhead)
+    x = (torch.randn(M, K, generator=gen) * torch.logspace(-2, 2, M)[:, None]).half().cuda()
+    x[M // 2] = 0                                            # an all-zero token: amax clamps to 1e-8
+    W = rand_i8(gen, N, K).cuda()
+    sw = rand_scales(gen, N).cuda()
+    sn, cs = (t.cuda() for t in oracle.rope_tables(seqlen, 32, 64))
+    q, s = g.quantize_tensor(x)
+    want = g.gemm_i8_rotary(q, W, s, sw, sn, cs, nhead, 64, 64, seqlen, row_offset=3)
+    s_out = torch.full((M,), -1.0, device="cuda")
+    got = g.quantize_gemm_i8_rotary(x, W, sw, sn, cs, nhead, 64, 64, seqlen, row_offset=3, out_scale=s_out)
+    assert g.device_status()[0] == 0
+    assert_bitexact(s_out.cpu(), s.cpu(), "token scales of the fused kernel")
+    assert_bitexact(got.cpu(), want.cpu(), "fused quantise + rotary GEMM vs two calls")
