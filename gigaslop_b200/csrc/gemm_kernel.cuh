@@ -442,20 +442,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             raw[j][0] = __ldg(src); raw[j][1] = __ldg(src + 1);
           }
         }
+        // the four rows go through every stage together, so that their shuffle and reciprocal chains overlap
+        float amax[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int r = r0 + 2 * j;
-          const long long row = row0 + r;
           __half2 m2 = __float2half2_rn(0.f);
           const __half2* h = reinterpret_cast<const __half2*>(&raw[j][0]);
 #pragma unroll
           for (int k = 0; k < 8; ++k) m2 = __hmax2(m2, __habs2(h[k]));
-          float amax = fmaxf(__low2float(m2), __high2float(m2));
+          amax[j] = fmaxf(__low2float(m2), __high2float(m2));
+        }
 #pragma unroll
-          for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-          amax = fmaxf(amax, 1e-8f);
-          const float qs = __fmul_rn(__frcp_rn(amax), 127.0f);
-          const float2 q2 = make_float2(qs, qs);
+        for (int d = 16; d > 0; d >>= 1) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) amax[j] = fmaxf(amax[j], __shfl_xor_sync(0xffffffffu, amax[j], d));
+        }
+        float qs[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) qs[j] = __fmul_rn(__frcp_rn(fmaxf(amax[j], 1e-8f)), 127.0f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = r0 + 2 * j;
+          const __half2* h = reinterpret_cast<const __half2*>(&raw[j][0]);
+          const float2 q2 = make_float2(qs[j], qs[j]);
           uint32_t w[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -468,11 +477,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
           if (lane < kvec)
             *reinterpret_cast<uint4*>(res_base + dst_lane + r * 128 + (((lane & 7) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          if (lane == 0) {
-            const float sc = row < p.M ? __frcp_rn(qs) : 0.f;
-            sa_dst[r] = sc;
-            if (p.scale_a_out && row < p.M) p.scale_a_out[row] = sc;
-          }
+        }
+        if (lane < 4) {                                  // lane j reports row j of the round
+          const int r = r0 + 2 * lane;
+          const long long row = row0 + r;
+          const float myqs = lane == 0 ? qs[0] : lane == 1 ? qs[1] : lane == 2 ? qs[2] : qs[3];
+          const float sc = row < p.M ? __frcp_rn(myqs) : 0.f;
+          sa_dst[r] = sc;
+          if (p.scale_a_out && row < p.M) p.scale_a_out[row] = sc;
         }
       }
       fence_proxy_async_smem();                        // the stores above before the MMAs' reads of the block

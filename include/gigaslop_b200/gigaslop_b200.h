@@ -111,7 +111,7 @@ int32_t gsb200_gemm_i8_rotary_f16(const int8_t* A, int64_t lda, const int8_t* B,
  * the token scales.  K must be a multiple of 128 and at most 512, ldx a multiple of 8.  A new entry point beside
  * the drop-in ones: the reference has no fused form.  It saves the int8 round trip through memory but, as built, not
  * time: the two quantiser warps share their schedulers with the epilogue warps that bound the GEMM, and the MMAs of a
- * row block wait for them (config 2: 201 us against 97 us for the two calls, 92 us for the two calls on two streams).
+ * row block wait for them (config 2: 184 us against 97 us for the two calls, 92 us for the two calls on two streams).
  * Use it where the int8 copy of the activations must not exist; otherwise the two calls. */
 int32_t gsb200_ptq_gemm_i8_rotary_f16(const void* x_f16, int64_t ldx, const int8_t* B, int64_t ldb, void* C, int64_t ldc,
                                       float* scale_a_out, const float* scale_b, const float* sin_tab,
