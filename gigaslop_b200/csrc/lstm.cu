@@ -22,6 +22,8 @@
 namespace gsb {
 
 constexpr int LSTM_THREADS = 256;            // 8 warps: all load / do gate math; warp 0 lane 0 also issues TMA + MMA
+constexpr int LSTMC_MMA_TID = 128;           // cluster kernel: the thread (lane 0 of warp 4) that issues the MMAs
+constexpr int LSTMC_IH_TID = 0;              // cluster kernel: the thread that issues the TMA loads of the ih tiles (on a thread of warp 7 the step is 12 % slower)
 constexpr int LSTM_ROWS = 128;               // batch rows per CTA (UMMA M)
 constexpr int LSTM_HS = 32;                  // hidden units per CTA
 constexpr int LSTM_NCOL = 4 * LSTM_HS;       // gate columns per CTA (UMMA N)
@@ -405,30 +407,28 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   fence_proxy_async_smem();
   __syncthreads();
 
+  // The MMAs of step s + 1 are issued inside step s by one thread of warp 4, as soon as that warp has put out its
+  // output stores (they take ~1700 clocks to get into the store queue: 768 partial-line writes per CTA and step; the
+  // tile of h_s is complete ~1300 clocks after the CTA barrier, so the wait for it hides behind them).  Warp 0 has
+  // the bulk copies and the next TMA loads to issue; everything of the next step waits for these MMAs.
+  // Descriptors are built once; a K step adds a constant to the start-address field.
+  const uint64_t a_base[2] = {umma_smem_desc_kchunks(smem_u32(h_s), LSTMC_CHUNK),
+                              umma_smem_desc_kchunks(smem_u32(h_s + LSTMC_HBUF), LSTMC_CHUNK)};
+  const uint64_t b_base = umma_smem_desc_sw128(smem_u32(w_s));
+  auto issue_mmas = [&](int buf) {                    // one thread: gates += (tile of h in buffer `buf`) . W^T
+    constexpr uint32_t idesc = umma_idesc(1, 0, 0, LSTM_ROWS, LSTM_NCOL);
+    const uint64_t a_desc = buf ? a_base[1] : a_base[0];
+    const int ksteps = H >> 5;                        // 32 bytes of K per MMA
+    tc_fence_after();
+    for (int ks = 0; ks < ksteps; ++ks)
+      umma_f8(tmem_base, a_desc + (uint64_t)(ks * (2 * LSTMC_CHUNK >> 4)),
+              b_base + (uint64_t)((ks >> 2) * (LSTM_KB_BYTES >> 4) + 2 * (ks & 3)), idesc, ks != 0);
+    umma_commit(mma_done);
+  };
+  if (tid == LSTMC_MMA_TID && ok && p.T > 0) issue_mmas(1);       // step 0 reads buffer 1
+
   for (int s = 0; s < p.T; ++s) {
     if (*abort_flag || !ok) break;
-    const int rb = (s + 1) & 1;                       // buffer that holds h_{s-1}
-    // ---- 1. the tile of h_{s-1} is complete once every slice has arrived; then the MMAs ---------------------
-    if (tid == 0) {
-      if (s > 0) {
-        ok = mbar_wait_cluster(&h_ready[rb], ((s - 1) >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x40, budget);
-        // arm this buffer's next use: h_{s+1} arrives in it if there is a step s + 2
-        if (ok && s + 2 < p.T) mbar_arrive_expect_tx(&h_ready[rb], p.slices * LSTMC_PIECE);
-      }
-      if (ok) {
-        tc_fence_after();
-        constexpr uint32_t idesc = umma_idesc(1, 0, 0, LSTM_ROWS, LSTM_NCOL);
-        const uint64_t a_desc = umma_smem_desc_kchunks(smem_u32(h_s + rb * LSTMC_HBUF), LSTMC_CHUNK);
-        const int ksteps = H >> 5;                    // 32 bytes of K per MMA
-        for (int ks = 0; ks < ksteps; ++ks) {
-          const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(w_s + (ks >> 2) * LSTM_KB_BYTES));
-          umma_f8(tmem_base, a_desc + (uint64_t)ks * (2 * LSTMC_CHUNK >> 4), b_desc + 2 * (ks & 3), idesc, ks != 0);
-        }
-        umma_commit(mma_done);
-      } else {
-        *abort_flag = 1;
-      }
-    }
     // ---- 2. gate math on this thread's row ---------------------------------------------------------------------
     ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20, budget) &&
          mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30, budget);
@@ -486,7 +486,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t dst = mapa_shared(smem_u32(h_s + (s & 1) * LSTMC_HBUF + slc * LSTMC_PIECE), (uint32_t)tid);
         bulk_copy_to_cluster(dst, stg, LSTMC_PIECE, mapa_shared(smem_u32(&h_ready[s & 1]), (uint32_t)tid));
       }
-      if (tid == 0 && s + 2 < p.T) issue_ih(s + 2);
+      if (tid == LSTMC_IH_TID && s + 2 < p.T) issue_ih(s + 2);
       // ---- 5. the layer's outputs ------------------------------------------------------------------------------------
       if (row_ok) {
         const size_t toff = (size_t)step_t(s) * B * H + (size_t)row * H + my_col;
@@ -497,6 +497,17 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           for (int i = 0; i < 8; ++i) w16[i] = pack_half2(hv[2 * i], hv[2 * i + 1]);
           *reinterpret_cast<uint4*>(p.h_out + toff) = make_uint4(w16[0], w16[1], w16[2], w16[3]);
           *reinterpret_cast<uint4*>(p.h_out + toff + 8) = make_uint4(w16[4], w16[5], w16[6], w16[7]);
+        }
+      }
+      // ---- 6. the next step's MMAs: the tile of h_s (buffer s & 1) is complete once every slice has arrived ---------
+      if (tid == LSTMC_MMA_TID && s + 1 < p.T) {
+        const bool got = mbar_wait_cluster(&h_ready[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x40, budget);
+        if (got) {
+          // arm this buffer's next use: h_{s+2} arrives in it if there is a step s + 3
+          if (s + 3 < p.T) mbar_arrive_expect_tx(&h_ready[s & 1], p.slices * LSTMC_PIECE);
+          issue_mmas(s & 1);
+        } else {
+          *abort_flag = 1;
         }
       }
     } else {
