@@ -312,3 +312,27 @@ def test_fused_quantise_rotary_equals_two_calls(M, K, nhead, seqlen):
     assert g.device_status()[0] == 0
     assert_bitexact(s_out.cpu(), s.cpu(), "token scales of the fused kernel")
     assert_bitexact(got.cpu(), want.cpu(), "fused quantise + rotary GEMM vs two calls")
+
+
+def test_sm_limit_changes_the_grid_not_the_result():
+    """gsb200_set_sm_limit caps the persistent grids (here to 40 and 1 CTA): same bytes as with all SMs."""
+    g = need_lib()
+    from gigaslop_b200 import _lib
+    L = _lib.lib()
+    gen = torch.Generator().manual_seed(77)
+    M, K, N, seqlen = 5000, 512, 1536, 300
+    A, sa = oracle.quantize_tensor(torch.randn(M, K, generator=gen))
+    W, sw = rand_i8(gen, N, K), rand_scales(gen, N)
+    sn, cs = oracle.rope_tables(seqlen, 32, 64)
+    args = (A.cuda(), W.cuda(), sa.cuda(), sw.cuda())
+    want_r = g.gemm_i8_rotary(*args, sn.cuda(), cs.cuda(), 8, 64, 64, seqlen).cpu()
+    want_d = g.gemm_i8(*args).cpu()
+    try:
+        for limit in (40, 1):
+            assert L.gsb200_set_sm_limit(limit) == 0
+            assert_bitexact(g.gemm_i8_rotary(*args, sn.cuda(), cs.cuda(), 8, 64, 64, seqlen).cpu(), want_r, f"rotary, {limit} SMs")
+            assert_bitexact(g.gemm_i8(*args).cpu(), want_d, f"dequant, {limit} SMs")
+        assert L.gsb200_set_sm_limit(-1) != 0
+    finally:
+        assert L.gsb200_set_sm_limit(0) == 0
+    assert g.device_status()[0] == 0
