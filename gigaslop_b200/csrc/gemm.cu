@@ -215,6 +215,16 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   } else if (a_stationary) {
     p.m_major = 1;
     grid = p.m_blocks < sm_count() ? p.m_blocks : sm_count();
+    // the row blocks of the last, incomplete round are shared by as many CTAs as there are to go round
+    const int rem = p.m_blocks % grid;
+    p.ares_split = 1;
+    // (not for the bias epilogue: the low-rank projection reads its A from inside the output rows it writes, which
+    // only works while one CTA owns a row block)
+    if (resident && !fused && a.epi == EPI_ROTARY && rem > 0 && !(a.flags & GSB200_FLAG_OWN_ROW_BLOCKS)) {
+      int S = grid / rem;
+      if (S > p.n_blocks) S = p.n_blocks;
+      if (S > 1) p.ares_split = S;
+    }
   } else {
     grid = (int)(tiles < sm_count() ? tiles : sm_count());
   }

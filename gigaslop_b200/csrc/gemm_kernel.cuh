@@ -103,6 +103,7 @@ struct GemmParams {
   int m_blocks, n_blocks, k_blocks;
   int n_groups;                // WRES: number of row-block groups (grid = n_groups * n_blocks)
   int m_major;                 // STREAM: a CTA walks all column blocks of a row block before the next (ARES always does)
+  int ares_split;              // ARES: CTAs that share each row block of the last, incomplete round (1 = no sharing)
   void* C;                     // output base (direct-store path and int32 output)
   uint8_t* out_scale;          // EPI_SILU_MX: E8M0 scales [M, N/32]
   long long ld_scale;          //              row stride of out_scale in bytes
@@ -179,12 +180,35 @@ template <int SCHED>
 struct TileWalk {
   int m, n;
   int dm, dn;      // STREAM with the column block fastest: what one step of `grid` tiles adds
+  int n_lo, n_hi;  // row-block-major walks: this CTA's column blocks of row block m are [n_lo, n_hi)
+  int visit;       // row-block-major walks: how many row blocks this CTA has left behind
+  // Row blocks cta, cta + grid, ... while whole rounds last.  The row blocks left over (fewer than CTAs) would
+  // keep some SMs busy for a whole row block while the others idle: with the activation-stationary schedule each of
+  // them is shared by p.ares_split CTAs, which take consecutive column blocks of it (each loads the A block).
+  __device__ __forceinline__ void set_visit(const GemmParams& p) {
+    const int grid = (int)gridDim.x, full = p.m_blocks / grid, rem = p.m_blocks - full * grid;
+    m = p.m_blocks;                                   // nothing left unless one of the cases below applies
+    n_lo = 0; n_hi = p.n_blocks;
+    if (visit < full) {
+      m = (int)blockIdx.x + visit * grid;
+    } else if (visit == full && rem > 0) {
+      const int S = (SCHED == SCHED_ARES && p.ares_split > 1) ? p.ares_split : 1;
+      const int per = (p.n_blocks + S - 1) / S;
+      const int c = (int)blockIdx.x;
+      if (c < rem * S && (c % S) * per < p.n_blocks) {
+        m = full * grid + c / S;
+        n_lo = (c % S) * per;
+        n_hi = n_lo + per < p.n_blocks ? n_lo + per : p.n_blocks;
+      }
+    }
+    n = n_lo;
+  }
   __device__ __forceinline__ void start(const GemmParams& p) {
-    dm = dn = 0;
+    dm = dn = 0; n_lo = 0; n_hi = p.n_blocks; visit = 0;
     if constexpr (SCHED == SCHED_WRES) {
       n = blockIdx.x % p.n_blocks; m = blockIdx.x / p.n_blocks;
     } else {
-      if (SCHED == SCHED_ARES || p.m_major) { n = 0; m = blockIdx.x; }
+      if (SCHED == SCHED_ARES || p.m_major) set_visit(p);
       else {
         m = blockIdx.x / p.n_blocks; n = blockIdx.x % p.n_blocks;
         dm = gridDim.x / p.n_blocks; dn = gridDim.x % p.n_blocks;
@@ -192,13 +216,22 @@ struct TileWalk {
     }
   }
   __device__ __forceinline__ bool valid(const GemmParams& p) const { return m < p.m_blocks; }
+  __device__ __forceinline__ bool first() const { return n == n_lo; }       // first / last tile of this CTA's stay on row block m
+  __device__ __forceinline__ bool last() const { return n == n_hi - 1; }
   __device__ __forceinline__ void next(const GemmParams& p) {
     if constexpr (SCHED == SCHED_WRES) {
       m += p.n_groups;
     } else {
-      if (SCHED == SCHED_ARES || p.m_major) { if (++n == p.n_blocks) { n = 0; m += gridDim.x; } }
+      if (SCHED == SCHED_ARES || p.m_major) { if (++n == n_hi) { ++visit; set_visit(p); } }
       else { m += dm; n += dn; if (n >= p.n_blocks) { n -= p.n_blocks; ++m; } }
     }
+  }
+  // row block of this CTA's next stay, or -1
+  __device__ __forceinline__ int next_row_block(const GemmParams& p) const {
+    TileWalk nx = *this;
+    nx.n = nx.n_hi - 1;
+    nx.next(p);
+    return nx.valid(p) ? nx.m : -1;
   }
 };
 
@@ -302,7 +335,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int m0 = m_blk * BM;
         const int n0 = n_blk * OUT_COLS_PER_TILE;
         const int n1 = DUAL ? n0 : n0 + BN / 2;
-        if (ARES && n_blk == 0 && it != 0) rph ^= 1;
+        const bool rb_first = tw.first();      // first tile of this CTA's stay on the row block
+        if (ARES && rb_first && it != 0) rph ^= 1;
         // A comes from HBM with a latency the small ring cannot cover: ask for it in L2 well ahead.
         //   WRES: the row block two tiles on (one CTA of the group asks, the others find it in L2)
         //   ARES: this CTA's next row block, at the start of the current one
@@ -312,12 +346,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, pm * BM);
           if (++rot == p.n_blocks) rot = 0;
         } else if constexpr (ARES) {
-          if (!FUSEQ && n_blk == 0 && m_blk + (int)gridDim.x < p.m_blocks)
-            for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, (m_blk + (int)gridDim.x) * BM);
+          if (!FUSEQ && rb_first) {
+            const int nm = tw.next_row_block(p);
+            if (nm >= 0)
+              for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, nm * BM);
+          }
         }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if constexpr (ARES && !FUSEQ) {
-            if (n_blk == 0) {                 // new row block: refill this K piece of A once its last reader retired
+            if (rb_first) {                   // new row block: refill this K piece of A once its last reader retired
               if (!mbar_wait(&res_empty[kb], rph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x300 | kb, budget)) { ok = false; break; }
               mbar_arrive_expect_tx(&res_full[kb], A_STAGE_BYTES);
               tma_load_2d(res_base + kb * A_STAGE_BYTES, &tm_a, &res_full[kb], kb * BK, m0);
@@ -369,10 +406,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as, budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
-        if (ARES && n_blk == 0 && it != 0) rph ^= 1;
+        const bool rb_first = tw.first(), rb_last = tw.last();
+        if (ARES && rb_first && it != 0) rph ^= 1;
         for (int kb = 0; kb < p.k_blocks && !(p.ablate & 4); ++kb) {
           if constexpr (ARES) {
-            if (n_blk == 0 && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
+            if (rb_first && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
           }
           if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s, budget)) { ok = false; break; }
           tc_fence_after();
@@ -391,7 +429,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             else umma_f8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
           }
           umma_commit(&empty_bar[s]);          // ring stage reusable once these MMAs retire
-          if (ARES && n_blk == p.n_blocks - 1) umma_commit(&res_empty[kb]);   // last reader of this A piece
+          if (ARES && rb_last) umma_commit(&res_empty[kb]);   // last reader of this A piece
           if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
         if (ok) umma_commit(&acc_full[as]);     // accumulator complete

@@ -13,6 +13,8 @@ import torch
 
 from . import ops
 
+FLAG_OWN_ROW_BLOCKS = 8      # GSB200_FLAG_OWN_ROW_BLOCKS
+
 
 class QkvRotaryStreamPipeline:
     """``submit(x, out, ...)`` per batch, ``join()`` after the last; int8 activations and scales live in ``depth`` slots.
@@ -52,8 +54,9 @@ class QkvRotaryStreamPipeline:
             self.sg.wait_event(self.qdone[b])
             if events is not None:
                 events[0].record(self.sg)
+            # no sharing of the last round's row blocks: the next batch's quantiser is what fills those SMs here
             ops.gemm_i8_rotary(self.q[b], w, self.s[b], s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen,
-                               row_offset=row_offset, out=out)
+                               row_offset=row_offset, out=out, flags=FLAG_OWN_ROW_BLOCKS)
             if events is not None:
                 events[1].record(self.sg)
             self.gdone[b].record(self.sg)

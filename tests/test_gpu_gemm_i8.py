@@ -336,3 +336,28 @@ def test_sm_limit_changes_the_grid_not_the_result():
     finally:
         assert L.gsb200_set_sm_limit(0) == 0
     assert g.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("M", [19072, 20000, 25344])
+def test_rotary_shared_leftover_row_blocks(M):
+    """More row blocks than CTAs with an incomplete last round (1, 9 and 50 row blocks left over on 148 SMs): those
+    row blocks are shared by 6, 6 and 2 CTAs.  Same bytes as the walk of a single CTA, which shares nothing (and which
+    the small cases pin against the CPU model), and as 37 CTAs."""
+    g = need_lib()
+    from gigaslop_b200 import _lib
+    L = _lib.lib()
+    gen = torch.Generator().manual_seed(M)
+    K, N, seqlen = 256, 1536, 1000
+    A = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8).cuda()
+    sa = (torch.rand(M, generator=gen) * 0.02).cuda()
+    W, sw = rand_i8(gen, N, K).cuda(), rand_scales(gen, N).cuda()
+    sn, cs = (t.cuda() for t in oracle.rope_tables(seqlen, 32, 64))
+    got = g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, seqlen, row_offset=11).cpu()
+    try:
+        for limit in (1, 37):
+            assert L.gsb200_set_sm_limit(limit) == 0
+            ref = g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, seqlen, row_offset=11).cpu()
+            assert_bitexact(got, ref, f"all SMs vs {limit}")
+    finally:
+        assert L.gsb200_set_sm_limit(0) == 0
+    assert g.device_status()[0] == 0
