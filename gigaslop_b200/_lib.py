@@ -7,12 +7,11 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("GIGASLOP_B200_LIB") or os.path.join(_PKG, "libgigaslop_b200.so")
 
 OK = 0
-ERRORS = {-1: "bad argument", -2: "unsupported shape", -3: "device is not sm_100", -4: "device-side wait timed out"}
+ERRORS = {-1: "bad argument", -2: "unsupported shape", -3: "device is not sm_100"}
 
 F16, F32 = 0, 1
-FLAG_DIRECT_STORE = 1
-FLAG_STREAMING = 2
 FLAG_SCALAR_SCALE_B = 4
+FLAG_OWN_ROW_BLOCKS = 8
 
 _i32, _i64, _p = C.c_int32, C.c_int64, C.c_void_p
 
@@ -47,10 +46,20 @@ SIGNATURES = {
     "gsb200_lstm_scratch_bytes": (_i64, [_i64, _i32]),
     "gsb200_lstm_layer_fp8": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p, _i64, _p]),
     "gsb200_lstm_layer_fp8_static": (_i32, [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i32, _i32, _p]),
+    "gsb200_lstm_stack_workspace_bytes": (_i64, [_i64, _i64, _i32, _i32]),
+    "gsb200_lstm_stack_fp8": (_i32, [_p, _i64, _p, _i32, _p, _i32, _i32, _p, _i64, _i64, _i32, _i32, _p, _i64, _p, _p]),
     "gsb200_ptq_mxfp8": (_i32, [_p, _i32, _i64, _p, _i64, _p, _i64, _i64, _i32, _p]),
     "gsb200_dual_gemm_fp8_silu_mxfp8": (_i32, [_p, _i64, _p, _p, _i64, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "gsb200_dual_gemm_fp8_silu_f16": (_i32, [_p, _i64, _p, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i32, _i32, _i32, _p]),
 }
+
+
+
+class LstmLayer(C.Structure):
+    """``gsb200_lstm_layer_t``: the weights of one layer of the LSTM stack (device pointers)."""
+    _fields_ = [("w_ih", _p), ("ld_w_ih", _i64), ("s_ih", _p), ("w_hh", _p), ("ld_w_hh", _i64), ("s_hh", _p),
+                ("bias", _p)]
+
 
 _lib = None
 

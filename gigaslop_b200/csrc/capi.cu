@@ -233,6 +233,19 @@ int32_t gsb200_lstm_layer_fp8_static(const void* ih, int64_t ld_ih, const uint8_
   return launch_lstm_layer_static(a, S(stream));
 }
 
+int64_t gsb200_lstm_stack_workspace_bytes(int64_t T, int64_t B, int32_t H, int32_t overlap) {
+  return static_cast<int64_t>(lstm_stack_workspace_bytes(T, B, H, overlap));
+}
+
+int32_t gsb200_lstm_stack_fp8(const uint8_t* x, int64_t ldx, const float* sx, int32_t C,
+                              const gsb200_lstm_layer_t* layers, int32_t n_layers, int32_t reverse_first, void* h_out,
+                              int64_t T, int64_t B, int32_t H, int32_t time_blocks, void* workspace,
+                              int64_t workspace_bytes, gsb200_stream_t stream, gsb200_stream_t aux_stream) {
+  return launch_lstm_stack(x, ldx, sx, C, layers, n_layers, reverse_first, static_cast<__half*>(h_out), T, B, H,
+                           time_blocks, workspace, workspace_bytes < 0 ? 0 : static_cast<size_t>(workspace_bytes),
+                           S(stream), S(aux_stream));
+}
+
 }  // extern "C"
 
 // ---- module hooks named by the reference's generated headers -------------------------------------------

@@ -1,5 +1,6 @@
 // Declarations shared by the translation units of libgigaslop_b200.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -35,6 +36,7 @@ struct GemmArgs {
   int flags;
   // fused activation quantiser (KIND_I8 + EPI_ROTARY, K <= 512): fp16 activations instead of A / scale_a
   const __half* x_f16; long long ldx; float* scale_a_out;
+  int sm_cap;                    // > 0: this launch uses at most so many CTAs (beside the process-wide cap)
 };
 int32_t launch_gemm(const GemmArgs& a, cudaStream_t st);
 struct LstmLayerArgs {
@@ -48,6 +50,10 @@ struct LstmLayerArgs {
 size_t lstm_scratch_bytes(long long B, int H);
 int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_bytes, cudaStream_t st);
 int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st);
+size_t lstm_stack_workspace_bytes(long long T, long long B, int H, int overlap);
+int32_t launch_lstm_stack(const uint8_t* x, long long ldx, const float* sx, int C, const gsb200_lstm_layer_t* layers,
+                          int n_layers, int reverse_first, __half* h_out, long long T, long long B, int H,
+                          int time_blocks, void* ws, size_t ws_bytes, cudaStream_t st, cudaStream_t aux);
 int32_t launch_factored_lstm_step(uint8_t* h_out, float* c, const __half* hh_down, const __half* up_hh,
                                   const float* bias_hh, const __half* x_down, const __half* up_ih, const float* bias_ih,
                                   long long B, int H, int K_hh, int R, cudaStream_t st);
@@ -58,7 +64,13 @@ int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t
                        long long ldc, long long M, int N, int K, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached), capped by set_sm_limit
-void set_sm_limit(int sms);       // cap for the grids of the persistent kernels (0 = none)
+int sm_count_physical();          // SMs of the current device, whatever the cap
+void set_sm_limit(int sms);       // process-wide cap for the grids of the persistent GEMM kernels (0 = none)
+// Tiled 2-D tensor map of a row-major [rows, cols] tensor (served from a per-thread table when the same
+// arguments come again); false if the driver refuses it.
+bool tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows, uint64_t cols,
+             uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz);
+unsigned long long tmap_encode_count();   // tensor maps actually encoded since the library was loaded
 int32_t read_clear_status(uint32_t out[4]);
 int32_t set_spin_budget(uint32_t clocks);
 int32_t selftest_wait_timeout(cudaStream_t st);

@@ -5,6 +5,8 @@
 // CTA = 128 batch rows x 32 hidden units (gate columns i|f|g|o x 32 -> UMMA N = 128), one tile per CTA.
 #include <cuda_fp8.h>
 
+#include <atomic>
+
 #include "capi_internal.h"
 #include "ptx.cuh"
 
@@ -38,7 +40,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + FS_SMEM_BAR);
   uint64_t* full = bars; uint64_t* mma_done = bars + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slices = p.H / FS_HS;
@@ -46,7 +48,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
   const int kbs = p.kb_hh + p.kb_ih;
 
   if (tid == 0) {
-    mbar_init(full, 1); mbar_init(mma_done, 1); *abort_flag = 0; fence_mbar_init();
+    mbar_init(full, 1); mbar_init(mma_done, 1); abort_flag.set(0); fence_mbar_init();
     prefetch_tmap(&tm_hh); prefetch_tmap(&tm_xd); prefetch_tmap(&tm_uhh); prefetch_tmap(&tm_uih);
   }
   if (warp == 0) { tmem_alloc(tmem_slot, FS_NCOL); tmem_relinquish(); }
@@ -58,7 +60,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const long long budget = spin_budget();          // bound of every wait below, fetched once
+  const unsigned int budget = spin_budget();          // bound of every wait below, fetched once
 
   if (tid == 0) {
     mbar_arrive_expect_tx(full, kbs * 2 * FS_KB_BYTES);
@@ -101,7 +103,7 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
     const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
     for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * FS_HS + half * 16, acc[g]);
-    tmem_ld_wait();
+    tmem_ld_wait(acc[0], acc[1], acc[2], acc[3]);
     if (row_ok) {
       float hv[16];
 #pragma unroll
@@ -136,18 +138,8 @@ factored_lstm_step_kernel(const __grid_constant__ CUtensorMap tm_hh, const __gri
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, FS_NCOL); }
 }
 
-typedef CUresult (*EncodeTiledFnF)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static bool fs_map(EncodeTiledFnF enc, CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {64, box_rows};
-  cuuint32_t es[2] = {1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+static bool fs_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  return tmap_2d(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, rows, cols, cols, 64, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 int32_t launch_factored_lstm_step(uint8_t* h_out, float* c, const __half* hh_down, const __half* up_hh,
@@ -165,23 +157,20 @@ int32_t launch_factored_lstm_step(uint8_t* h_out, float* c, const __half* hh_dow
   if (rc != GSB200_OK) return rc;
   const long long grid = ((B + FS_ROWS - 1) / FS_ROWS) * (H / FS_HS);
   if (grid > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
-  static bool attr_done[64];
+  static std::atomic<int> attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if (dev < 0 || dev >= 64) return GSB200_ERR_DEVICE;
+  if (!attr_done[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(factored_lstm_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FS_SMEM_BYTES);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(factored step)");
-    attr_done[dev] = true;
+    attr_done[dev].store(1, std::memory_order_release);
   }
-  void* fnp = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fnp, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return GSB200_ERR_DEVICE;
-  EncodeTiledFnF enc = reinterpret_cast<EncodeTiledFnF>(fnp);
+  // the four maps depend only on pointers and shapes: a caller stepping through time with the same buffers gets
+  // them from the per-thread table after the first step
   CUtensorMap t_hh, t_xd, t_uhh, t_uih;
-  if (!fs_map(enc, &t_hh, hh_down, (uint64_t)B, (uint64_t)K_hh, FS_ROWS) || !fs_map(enc, &t_xd, x_down, (uint64_t)B, (uint64_t)R, FS_ROWS) ||
-      !fs_map(enc, &t_uhh, up_hh, (uint64_t)4 * H, (uint64_t)K_hh, FS_HS) || !fs_map(enc, &t_uih, up_ih, (uint64_t)4 * H, (uint64_t)R, FS_HS))
+  if (!fs_map(&t_hh, hh_down, (uint64_t)B, (uint64_t)K_hh, FS_ROWS) || !fs_map(&t_xd, x_down, (uint64_t)B, (uint64_t)R, FS_ROWS) ||
+      !fs_map(&t_uhh, up_hh, (uint64_t)4 * H, (uint64_t)K_hh, FS_HS) || !fs_map(&t_uih, up_ih, (uint64_t)4 * H, (uint64_t)R, FS_HS))
     return GSB200_ERR_BAD_ARG;
   FacStepParams p{};
   p.B = (int)B; p.H = H; p.kb_hh = K_hh / 64; p.kb_ih = R / 64;

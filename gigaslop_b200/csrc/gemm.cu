@@ -2,33 +2,61 @@
 // encoding and launch of the persistent kernel (one CTA per SM).
 #include <cuda.h>
 
+#include <atomic>
+
 #include "capi_internal.h"
+#include "diag.h"
 #include "gemm_kernel.cuh"
 
 namespace gsb {
 
-// ---- driver entry point for tensor-map encoding (no link-time libcuda dependency) -------------
+// ---- tensor maps ---------------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is reached through the runtime's driver-entry-point query (no link-time libcuda
+// dependency); the pointer is looked up once per process.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
+  static std::atomic<EncodeTiledFn> fn{nullptr};
+  EncodeTiledFn f = fn.load(std::memory_order_acquire);
+  if (!f) {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
+        qres == cudaDriverEntryPointSuccess) {
+      f = reinterpret_cast<EncodeTiledFn>(p);
+      fn.store(f, std::memory_order_release);
+    }
   }
-  return fn;
+  return f;
 }
 
-// 2-D row-major tensor [rows, cols] of `esz`-byte elements with a box of box_cols x box_rows and
-// the given swizzle (box_cols * esz must equal the swizzle span).
-static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows,
-                        uint64_t cols, uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows,
-                        CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+// 2-D row-major tensor [rows, cols] of `esz`-byte elements, row stride ld_elems, box of box_cols x box_rows.
+// A tensor map is a pure function of these arguments (it holds the address, not the data), so the last maps a
+// host thread built are kept in a small per-thread table: a caller that launches the same kernels on the same
+// buffers step after step -- the per-timestep LSTM wrapper, a pipeline over a ring of buffers -- encodes nothing
+// in steady state.  Per thread, so no lock and no sharing between the host threads that drive different GPUs.
+struct TmapKey {
+  const void* base; uint64_t rows, cols, ld; uint32_t box_cols, box_rows; int dt, esz, swz;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_cols == o.box_cols &&
+           box_rows == o.box_rows && dt == o.dt && esz == o.esz && swz == o.swz;
+  }
+};
+constexpr int kTmapCacheSlots = 64;
+struct TmapSlot { TmapKey key; CUtensorMap map; bool used; };
+static std::atomic<unsigned long long> g_tmap_encodes{0};      // encodes since load (test / benchmark hook)
+
+bool tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows, uint64_t cols,
+             uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz) {
+  static thread_local TmapSlot cache[kTmapCacheSlots];
+  const TmapKey key{base, rows, cols, ld_elems, box_cols, box_rows, (int)dt, esz, (int)swz};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h = (h ^ (rows * 0x9E3779B97F4A7C15ull) ^ (cols << 17) ^ (ld_elems << 29) ^ ((uint64_t)box_rows << 41) ^
+       ((uint64_t)box_cols << 47) ^ ((uint64_t)dt << 53)) * 0xD6E8FEB86659FD93ull;
+  TmapSlot& slot = cache[(h >> 40) % kTmapCacheSlots];
+  if (slot.used && slot.key == key) { *m = slot.map; return true; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -41,13 +69,23 @@ static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const v
     fprintf(stderr, "gigaslop_b200: cuTensorMapEncodeTiled failed (%d)\n", (int)r);
     return false;
   }
+  g_tmap_encodes.fetch_add(1, std::memory_order_relaxed);
+  slot.key = key; slot.map = *m; slot.used = true;
   return true;
+}
+unsigned long long tmap_encode_count() { return g_tmap_encodes.load(std::memory_order_relaxed); }
+
+static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows,
+                        uint64_t cols, uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows,
+                        CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+  return tmap_2d(m, dt, esz, base, rows, cols, ld_elems, box_cols, box_rows, swz);
 }
 
 // ---- per-device state -------------------------------------------------------------------------
+// Atomics: the contract allows one host thread per GPU, and two of them may meet here.
 constexpr int kMaxDevices = 64;
-static int g_dev_ok[kMaxDevices];       // 0 unknown, 1 ok, -1 unsupported
-static int g_dev_sms[kMaxDevices];
+static std::atomic<int> g_dev_ok[kMaxDevices];       // 0 unknown, 1 ok, -1 unsupported
+static std::atomic<int> g_dev_sms[kMaxDevices];
 
 template <int KIND, int EPI>
 static cudaError_t set_attr() {
@@ -64,14 +102,15 @@ int32_t ensure_device() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_status(e, "cudaGetDevice");
   if (dev < 0 || dev >= kMaxDevices) return GSB200_ERR_DEVICE;
-  if (g_dev_ok[dev] == 1) return GSB200_OK;
-  if (g_dev_ok[dev] == -1) return GSB200_ERR_DEVICE;
+  const int known = g_dev_ok[dev].load(std::memory_order_acquire);
+  if (known == 1) return GSB200_OK;
+  if (known == -1) return GSB200_ERR_DEVICE;
   int major = 0, sms = 0;
   cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (major != 10) {
     fprintf(stderr, "gigaslop_b200: device %d is sm_%d*, this library only carries sm_100a code\n", dev, major * 10);
-    g_dev_ok[dev] = -1;
+    g_dev_ok[dev].store(-1, std::memory_order_release);
     return GSB200_ERR_DEVICE;
   }
   cudaError_t errs[] = {
@@ -90,19 +129,27 @@ int32_t ensure_device() {
     fprintf(stderr, "gigaslop_b200: cuTensorMapEncodeTiled not available from the driver\n");
     return GSB200_ERR_DEVICE;
   }
-  g_dev_sms[dev] = sms;
-  g_dev_ok[dev] = 1;
+  g_dev_sms[dev].store(sms, std::memory_order_relaxed);
+  g_dev_ok[dev].store(1, std::memory_order_release);
   return GSB200_OK;
 }
 
-static int g_sm_limit = 0;           // 0: no limit
-void set_sm_limit(int sms) { g_sm_limit = sms; }
+// Cap for the grids of the persistent GEMM kernels.  One value for the whole process (every device, every
+// host thread); 0 = no cap.
+static std::atomic<int> g_sm_limit{0};
+void set_sm_limit(int sms) { g_sm_limit.store(sms, std::memory_order_relaxed); }
 
-int sm_count() {
+int sm_count_physical() {
   int dev = 0;
   cudaGetDevice(&dev);
-  const int n = (dev >= 0 && dev < kMaxDevices && g_dev_sms[dev] > 0) ? g_dev_sms[dev] : 148;
-  return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
+  const int n = (dev >= 0 && dev < kMaxDevices) ? g_dev_sms[dev].load(std::memory_order_relaxed) : 0;
+  return n > 0 ? n : 148;
+}
+
+int sm_count() {
+  const int n = sm_count_physical();
+  const int lim = g_sm_limit.load(std::memory_order_relaxed);
+  return (lim > 0 && lim < n) ? lim : n;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -122,11 +169,13 @@ static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, co
 int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   if (a.M == 0) return GSB200_OK;
   if (a.M < 0 || a.M > 0x7fffff00ll || a.N <= 0 || a.K <= 0) return GSB200_ERR_BAD_ARG;
+  if (a.flags & ~(GSB200_FLAG_SCALAR_SCALE_B | GSB200_FLAG_OWN_ROW_BLOCKS | GSB200_DIAG_FLAG_MASK)) return GSB200_ERR_BAD_ARG;
+  const bool force_streaming = (a.flags & GSB200_DIAG_FLAG_MASK & GSB200_DIAG_FLAG_STREAMING) != 0;
   const bool fused = a.x_f16 != nullptr;          // the int8 A operand is made on chip from fp16 activations
   if (fused) {
     if (a.kind != KIND_I8 || a.epi != EPI_ROTARY || a.A || a.scale_a) return GSB200_ERR_BAD_ARG;
     if (!aligned16(a.x_f16) || a.ldx < a.K || a.ldx % 8 != 0) return GSB200_ERR_BAD_ARG;
-    if (a.K > RES_MAX_KBLOCKS * BK || a.K % BK != 0 || (a.flags & GSB200_FLAG_STREAMING)) return GSB200_ERR_UNSUPPORTED;
+    if (a.K > RES_MAX_KBLOCKS * BK || a.K % BK != 0 || force_streaming) return GSB200_ERR_UNSUPPORTED;
   } else {
     if (!a.A || !aligned16(a.A) || a.lda < a.K || a.lda % 16 != 0) return GSB200_ERR_BAD_ARG;
   }
@@ -178,8 +227,8 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.seqlen = a.seqlen > 0 ? a.seqlen : 1;
   p.rot_cols = rot_cols;
   p.row_offset = (int)(a.row_offset % p.seqlen);
-  p.direct_store = (a.flags & GSB200_FLAG_DIRECT_STORE) ? 1 : 0;
-  p.ablate = (a.flags >> 8) & 7;
+  p.direct_store = (a.flags & GSB200_DIAG_FLAG_MASK & GSB200_DIAG_FLAG_DIRECT_STORE) ? 1 : 0;
+  p.ablate = ((a.flags & GSB200_DIAG_FLAG_MASK) >> 8) & 7;
   p.x_f16 = a.x_f16; p.ldx = a.ldx; p.scale_a_out = a.scale_a_out;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
@@ -200,21 +249,23 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   // One operand stays resident in shared memory whenever K <= 512 (its 4 K-pieces fit): the W slice for the
   // dequant / SwiGLU epilogues, the A row block for the rotary epilogue (whose per-row sin/cos state is then
   // fetched once per row block).  Larger K streams both operands.
-  const bool resident = p.k_blocks <= RES_MAX_KBLOCKS && !(a.flags & GSB200_FLAG_STREAMING);
+  const bool resident = p.k_blocks <= RES_MAX_KBLOCKS && !force_streaming;
   int grid;
   p.m_major = 0;
   p.n_groups = 0;
   const bool a_stationary = a.epi == EPI_ROTARY || a.epi == EPI_BIAS;
+  int sms = sm_count();
+  if (a.sm_cap > 0 && a.sm_cap < sms) sms = a.sm_cap;
   if (a.epi == EPI_BIAS && !resident) return GSB200_ERR_UNSUPPORTED;     // only built for K <= 512 bytes of A per row
   if (resident && !a_stationary) {
-    int groups = sm_count() / p.n_blocks;
+    int groups = sms / p.n_blocks;
     if (groups < 1) groups = 1;
     if (groups > p.m_blocks) groups = p.m_blocks;
     p.n_groups = groups;
     grid = groups * p.n_blocks;
   } else if (a_stationary) {
     p.m_major = 1;
-    grid = p.m_blocks < sm_count() ? p.m_blocks : sm_count();
+    grid = p.m_blocks < sms ? p.m_blocks : sms;
     // the row blocks of the last, incomplete round are shared by as many CTAs as there are to go round
     const int rem = p.m_blocks % grid;
     p.ares_split = 1;
@@ -226,7 +277,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
       if (S > 1) p.ares_split = S;
     }
   } else {
-    grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    grid = (int)(tiles < sms ? tiles : sms);
   }
   cudaError_t e = cudaErrorInvalidValue;
   if (a.kind == KIND_I8) {
@@ -268,10 +319,11 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
 // normally: the give-up path is exercised without hanging or faulting the device.
 __global__ void selftest_wait_timeout_kernel() {
   __shared__ uint64_t bar;
-  __shared__ int abort_flag;
-  if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag = 0; fence_mbar_init(); }
+  __shared__ int abort_word;
+  const AbortFlag abort_flag{smem_u32(&abort_word)};
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); abort_flag.set(0); fence_mbar_init(); }
   __syncthreads();
-  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, ST_TIMEOUT_EPILOGUE, 0xdead, spin_budget());
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, abort_flag, ST_TIMEOUT_EPILOGUE, 0xdead, spin_budget());
   __syncthreads();
 }
 

@@ -55,6 +55,8 @@ constexpr int FRONT_WARPS = 4;                          // warp 0 producer, warp
 constexpr int GEMM_THREADS = 32 * (FRONT_WARPS + EPI_WARPS);
 constexpr int FRONT_REGS = 56;                          // register budgets after setmaxnreg (per thread)
 constexpr int EPI_REGS = 224;
+constexpr int FRONT_REGS_FUSEQ = 80;                    // with the fused quantiser warps 2-3 hold four rows in flight
+constexpr int EPI_REGS_FUSEQ = 208;
 constexpr int A_STAGE_BYTES = BM * BK;                  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK;                  // 32 KiB
 constexpr int RES_MAX_KBLOCKS = 4;                      // resident operand (W slice or A block): up to K = 512
@@ -120,9 +122,15 @@ struct GemmParams {
   const __half* x_f16;         // fused activation quantiser: fp16 activations [M, K] (the int8 A operand is then made on chip)
   long long ldx;               //   row stride of x_f16 in elements
   float* scale_a_out;          //   optional: the token scales [M], as quantize_tensor would return them
+  // Diagnostics, honoured only by a library built with -DGSB200_DIAG (never by the shipped one):
   int direct_store;            // 1: plain st.global from registers instead of smem + TMA store
-  int ablate;                  // timing ablations (results are then wrong): 1 = skip the output stores, 2 = skip the epilogue body
+  int ablate;                  // timing ablations (results are then wrong): 1 = skip the output stores, 2 = skip the epilogue body, 4 = skip the main loop
 };
+#ifdef GSB200_DIAG
+constexpr bool kDiag = true;
+#else
+constexpr bool kDiag = false;
+#endif
 
 template <int KIND>
 __device__ __forceinline__ float acc_to_float(uint32_t v) {
@@ -265,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sa_ready + Map::SA_BUFS);
   float* sa_s = reinterpret_cast<float*>(smem + Map::SA_OFF);
   static_assert(!FUSEQ || (SCHED == SCHED_ARES && KIND == KIND_I8), "the fused quantiser feeds the resident int8 A block");
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -278,7 +286,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // FUSEQ: the two quantiser warps both report a finished A block
     for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], FUSEQ ? 2 : 1); mbar_init(&res_empty[s], 1); }
     for (int s = 0; s < Map::SA_BUFS; ++s) mbar_init(&sa_ready[s], 2);
-    *abort_flag = 0;
+    abort_flag.set(0);
     fence_mbar_init();
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1);
     if (EPI != EPI_I32) prefetch_tmap(&tm_c);
@@ -295,12 +303,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const long long budget = spin_budget();          // bound of every wait below, fetched once
+  const unsigned int budget = spin_budget();          // bound of every wait below, fetched once
 
   // The register re-split sits inside each role's branch: code placed after the point where the two
   // branches meet would be compiled for the smaller budget.
   if (warp < FRONT_WARPS) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FRONT_REGS));
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FUSEQ ? FRONT_REGS_FUSEQ : FRONT_REGS));
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -330,7 +338,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t rph = 0;                       // ARES: phase of the resident-A barriers, flips per row block
       int rot = 0;                            // WRES: it % n_blocks, which CTA of a group asks for the L2 prefetch
       TileWalk<SCHED> tw; tw.start(p);
-      for (int it = 0; ok && !(p.ablate & 4) && tw.valid(p); ++it, tw.next(p)) {
+      for (int it = 0; ok && !(kDiag && (p.ablate & 4)) && tw.valid(p); ++it, tw.next(p)) {
         const int m_blk = tw.m, n_blk = tw.n;
         const int m0 = m_blk * BM;
         const int n0 = n_blk * OUT_COLS_PER_TILE;
@@ -394,7 +402,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       // s8 x s8 -> s32 | e4m3 x e4m3 -> f32 | f16 x f16 -> f32 (format code 0 means e4m3 resp. f16 in its kind)
       constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, BM, BN) : umma_idesc(1, 0, 0, BM, BN);
       int s = 0; uint32_t ph = 0; bool ok = true;
-      if (WRES && !(p.ablate & 4)) {
+      if (WRES && !(kDiag && (p.ablate & 4))) {
         ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200, budget);
         tc_fence_after();
       }
@@ -408,7 +416,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const uint32_t d_tmem = tmem_base + as * BN;
         const bool rb_first = tw.first(), rb_last = tw.last();
         if (ARES && rb_first && it != 0) rph ^= 1;
-        for (int kb = 0; kb < p.k_blocks && !(p.ablate & 4); ++kb) {
+        for (int kb = 0; kb < p.k_blocks && !(kDiag && (p.ablate & 4)); ++kb) {
           if constexpr (ARES) {
             if (rb_first && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
           }
@@ -534,7 +542,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EPI_REGS));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FUSEQ ? EPI_REGS_FUSEQ : EPI_REGS));
     // ------------------------------ epilogue ----------------------------------
     // Eight free-running warps.  Warp e reads TMEM lane quarter e % 4 (32 rows) and the column half e / 4
     // of every tile, in chunks: the TMEM load of chunk i+1 is in flight during the arithmetic of chunk i,
@@ -666,7 +674,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (lane == 0) mbar_arrive(&acc_empty[as]);
       };
 
-      if (row_base < p.M && !(p.ablate & 2)) {
+      if (row_base < p.M && !(kDiag && (p.ablate & 2))) {
         if constexpr (EPI == EPI_I32) {
           // raw accumulators, direct 16-byte stores
           auto emit = [&](const uint32_t (&v)[32], int c) {
@@ -682,10 +690,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           tmem_ld_32x32b_x32(t_row, va);
 #pragma unroll
           for (int c = 0; c < WACC; c += 64) {
-            tmem_ld_wait();
+            tmem_ld_wait(va);
             tmem_ld_32x32b_x32(t_row + c + 32, vb);
             emit(va, c);
-            tmem_ld_wait();
+            tmem_ld_wait(vb);
             if (c + 64 < WACC) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
             emit(vb, c + 32);
           }
@@ -729,18 +737,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           uint32_t ga[32], ua[32], gb[32], ub[32];
           tmem_ld_32x32b_x32(t_row, ga);
           tmem_ld_32x32b_x32(t_row + BN / 2, ua);
-          tmem_ld_wait();
+          tmem_ld_wait(ga, ua);
           tmem_ld_32x32b_x32(t_row + 32, gb);
           tmem_ld_32x32b_x32(t_row + BN / 2 + 32, ub);
           emit(ga, ua, 0);
-          tmem_ld_wait();
+          tmem_ld_wait(gb, ub);
           release();
           emit(gb, ub, 32);
         } else {
           const float2 sa2 = pk2(sa, sa);
           const float2 sah2 = pk2(0.5f * sa, 0.5f * sa);
-          // The body exists twice: the product path (swizzled staging + TMA store) and a diagnostic path
-          // that stores straight from registers; the choice is made once per tile.
+          // The product path stages the tile in swizzled shared memory and leaves through TMA stores.  A library
+          // built with -DGSB200_DIAG carries the body a second time, storing straight from registers.
           auto run_tile = [&](auto direct_tag) {
             constexpr bool DIRECT = decltype(direct_tag)::value;
             __half* drow0 = reinterpret_cast<__half*>(p.C) + (long long)row * p.ldc;
@@ -766,7 +774,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               if constexpr (!DIRECT) {
                 fence_proxy_async_smem();          // generic-proxy smem writes -> visible to the TMA engine
                 __syncwarp();
-                if (lane == 0 && !(p.ablate & 1)) {
+                if (lane == 0 && !(kDiag && (p.ablate & 1))) {
                   tma_store_2d(&tm_c, out_buf + buf_a * OUT_BUF_BYTES, n_a, row_base); tma_store_commit();
                   if (row_base + OUT_BOX_ROWS < p.M) tma_store_2d(&tm_c, out_buf + buf_b * OUT_BUF_BYTES, n_a, row_base + OUT_BOX_ROWS);
                   tma_store_commit();          // always two groups per pair (the second may be empty): pair_begin counts groups
@@ -792,10 +800,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               for (int c = 0; c < WACC; c += 64) {
                 const int n = n0 + wout0 + c;
                 const bool live = n < p.N;
-                tmem_ld_wait();
+                tmem_ld_wait(va);
                 tmem_ld_32x32b_x32(t_row + c + 32, vb);
                 if (live) { pair_begin(); emit(va, c, 0); }
-                tmem_ld_wait();
+                tmem_ld_wait(vb);
                 if (c + 64 < WACC) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
                 if (live) { emit(vb, c + 32, 1); pair_end(n, n + 32); }
               }
@@ -852,10 +860,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               // instruction cache holds makes the warps stall on instruction fetch
 #pragma unroll 1
               for (int c = 0; c < WACC; c += 64) {
-                tmem_ld_wait();
+                tmem_ld_wait(xa0, xa1);
                 ldh(c, 1, xb0, xb1);
                 emit(xa0, xa1, c, 0);
-                tmem_ld_wait();
+                tmem_ld_wait(xb0, xb1);
                 if (c + 64 < WACC) ldh(c + 64, 0, xa0, xa1); else release();
                 emit(xb0, xb1, c, 1);
               }
@@ -886,16 +894,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               const bool live = n < p.N;
               tmem_ld_32x32b_x32(t_row, ga);
               tmem_ld_32x32b_x32(t_row + BN / 2, ua);
-              tmem_ld_wait();
+              tmem_ld_wait(ga, ua);
               tmem_ld_32x32b_x32(t_row + 32, gb);
               tmem_ld_32x32b_x32(t_row + BN / 2 + 32, ub);
               if (live) { pair_begin(); emit(ga, ua, 0, 0); }
-              tmem_ld_wait();
+              tmem_ld_wait(gb, ub);
               release();
               if (live) { emit(gb, ub, 32, 1); pair_end(n, n + 32); }
             }
           };
-          if (p.direct_store) run_tile(true_tag{}); else run_tile(false_tag{});
+          if constexpr (kDiag) {
+            if (p.direct_store) run_tile(true_tag{}); else run_tile(false_tag{});
+          } else {
+            run_tile(false_tag{});
+          }
         }
       } else {
         release();

@@ -16,6 +16,8 @@
 #include <cooperative_groups.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
+
 #include "capi_internal.h"
 #include "ptx.cuh"
 
@@ -84,7 +86,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   uint64_t* ih_full = bars + 1;          // [2] ih tile of a step landed
   uint64_t* mma_done = bars + 3;         // accumulator of this step complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = blockIdx.x / p.slices;        // row group
@@ -95,7 +97,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
 
   if (tid == 0) {
     mbar_init(w_full, 1); mbar_init(&ih_full[0], 1); mbar_init(&ih_full[1], 1); mbar_init(mma_done, 1);
-    *abort_flag = 0;
+    abort_flag.set(0);
     fence_mbar_init();
     prefetch_tmap(&tm_w); prefetch_tmap(&tm_ih);
   }
@@ -110,7 +112,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const long long budget = spin_budget();          // bound of every wait below, fetched once
+  const unsigned int budget = spin_budget();          // bound of every wait below, fetched once
 
   auto step_t = [&](int s) { return p.reverse ? p.T - 1 - s : s; };
   auto issue_ih = [&](int s) {   // one thread: TMA the four gate boxes of step s into buffer s & 1
@@ -141,22 +143,13 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     c[j] = (p.c0 && row_ok) ? __half2float(p.c0[(long long)row * H + hid0 + half * 16 + j]) : 0.f;
 
   bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10, budget);
-  const int chunks_per_row = p.k_blocks * 8;                 // 16-byte pieces of a (zero-padded) h row
   unsigned int* my_flags = p.flags + grp * p.slices;
-  // the 16-byte pieces of the 128 x H tile of h this thread moves every step: source offset inside an h buffer
-  // (-1: zero padding), destination offset in the swizzled operand tile (-1: nothing to do)
-  int pull_src[LSTM_PULLS], pull_dst[LSTM_PULLS];
-#pragma unroll
-  for (int i = 0; i < LSTM_PULLS; ++i) {
-    const int id = tid + i * LSTM_THREADS;
-    pull_src[i] = pull_dst[i] = -1;
-    if (id < LSTM_ROWS * chunks_per_row) {
-      const int r = id / chunks_per_row, cc = id % chunks_per_row;
-      const int kb = cc >> 3, ck = cc & 7;
-      pull_dst[i] = kb * LSTM_KB_BYTES + r * 128 + ((ck ^ (r & 7)) << 4);
-      if (row0 + r < B && cc * 16 < H) pull_src[i] = (row0 + r) * H + cc * 16;
-    }
-  }
+  // The 16-byte pieces of the 128 x H tile of h this thread moves every step.  Piece i of a thread is row
+  // (tid / 8) + 32 * (i % 4), 16-byte chunk tid % 8 of K block i / 4: eight neighbouring threads read one 128-byte
+  // line, and both offsets are one per-thread base plus constants known at compile time (no per-piece state).
+  const int pull_r = tid >> 3, pull_ck = tid & 7;
+  const int pull_dst0 = pull_r * 128 + ((pull_ck ^ (pull_r & 7)) << 4);         // + kb * LSTM_KB_BYTES + j * 32 * 128
+  const long long pull_src0 = (long long)(row0 + pull_r) * H + pull_ck * 16;     // + kb * 128 + j * 32 * H
 
   for (int s = 0; s < p.T; ++s) {
     // ---- 1. wait until every slice of this row group has published h_{s-1} -----------------------------
@@ -164,9 +157,9 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     if (s > 0 && tid < p.slices) {
       long long t0 = clock64();
       while (ld_acquire_gpu(my_flags + tid) < (unsigned int)s) {
-        if (*abort_flag) break;
+        if (abort_flag.get()) break;
         if (clock64() - t0 > budget) {
-          *abort_flag = 1;
+          abort_flag.set(1);
           atomicOr(&g_status[0], ST_TIMEOUT_LSTM);
           g_status[1] = (unsigned int)s;
           break;
@@ -174,20 +167,24 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       }
     }
     __syncthreads();
-    if (*abort_flag || !ok) break;
+    if (abort_flag.get() || !ok) break;
     // ---- 2. pull the 128 x H tile of h_{s-1} into the swizzled K-major operand layout ------------------
     // All of a thread's loads are issued before the first store, so their L2 latencies overlap (one after the
-    // other they were the longest part of the step).  pull_src / pull_dst were computed once before the loop.
+    // other they were the longest part of the step).
     {
       uint4 v[LSTM_PULLS];
 #pragma unroll
       for (int i = 0; i < LSTM_PULLS; ++i) {
+        const int kb = i >> 2, j = i & 3;
         v[i] = make_uint4(0, 0, 0, 0);
-        if (h_prev && pull_src[i] >= 0) v[i] = __ldcg(reinterpret_cast<const uint4*>(h_prev + pull_src[i]));
+        if (h_prev && kb < p.k_blocks && row0 + pull_r + 32 * j < B && kb * 128 + pull_ck * 16 < H)
+          v[i] = __ldcg(reinterpret_cast<const uint4*>(h_prev + pull_src0 + (long long)j * 32 * H + kb * 128));
       }
 #pragma unroll
-      for (int i = 0; i < LSTM_PULLS; ++i)
-        if (pull_dst[i] >= 0) *reinterpret_cast<uint4*>(h_s + pull_dst[i]) = v[i];
+      for (int i = 0; i < LSTM_PULLS; ++i) {
+        const int kb = i >> 2, j = i & 3;
+        if (kb < p.k_blocks) *reinterpret_cast<uint4*>(h_s + pull_dst0 + kb * LSTM_KB_BYTES + j * (32 * 128)) = v[i];
+      }
     }
     fence_proxy_async_smem();
     __syncthreads();
@@ -213,7 +210,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * LSTM_HS + half * 16, acc[g]);
-      tmem_ld_wait();
+      tmem_ld_wait(acc[0], acc[1], acc[2], acc[3]);
       const uint8_t* ihb = ih_s + (s & 1) * LSTM_IH_BYTES;
       float hv[16];
 #pragma unroll
@@ -276,7 +273,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       tc_fence_before();
       __syncthreads();
     }
-    if (!ok || *abort_flag) break;
+    if (!ok || abort_flag.get()) break;
   }
 
   if (p.c_last && row_ok) {
@@ -330,7 +327,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* h_ready = bars + 4;          // [2] every slice's piece of h has landed in this CTA's buffer (bytes counted)
   uint8_t* stg_s = smem + LSTMC_SMEM_STG;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = blockIdx.x / p.slices;        // row group = cluster
@@ -345,7 +342,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // arm the first use of each buffer: h_0 arrives in buffer 0 (if there is a step 1), h_1 in buffer 1
     if (p.T > 1) mbar_arrive_expect_tx(&h_ready[0], p.slices * LSTMC_PIECE);
     if (p.T > 2) mbar_arrive_expect_tx(&h_ready[1], p.slices * LSTMC_PIECE);
-    *abort_flag = 0;
+    abort_flag.set(0);
     fence_mbar_init();
     prefetch_tmap(&tm_w); prefetch_tmap(&tm_ih);
   }
@@ -360,7 +357,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_after();
   cluster_sync_all();                    // every CTA's barriers exist before anyone sends to them
   const uint32_t tmem_base = *tmem_slot;
-  const long long budget = spin_budget();
+  const unsigned int budget = spin_budget();
   const bool rank_ok = cluster_ctarank() == (uint32_t)slc;
 
   auto step_t = [&](int s) { return p.reverse ? p.T - 1 - s : s; };
@@ -392,7 +389,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int my_col = hid0 + half * 16;   // this thread's 16 hidden units = K chunk `half` of the CTA's piece
 
   bool ok = mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10, budget) && rank_ok;
-  if (!rank_ok && tid == 0) { *abort_flag = 1; atomicOr(&g_status[0], ST_TIMEOUT_LSTM); g_status[1] = 0x50; }
+  if (!rank_ok && tid == 0) { abort_flag.set(1); atomicOr(&g_status[0], ST_TIMEOUT_LSTM); g_status[1] = 0x50; }
 
   // ---- step 0 reads h_0 (or zeros) from buffer 1, staged by this CTA's own threads -------------------------
   {
@@ -428,7 +425,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (tid == LSTMC_MMA_TID && ok && p.T > 0) issue_mmas(1);       // step 0 reads buffer 1
 
   for (int s = 0; s < p.T; ++s) {
-    if (*abort_flag || !ok) break;
+    if (abort_flag.get() || !ok) break;
     // ---- 2. gate math on this thread's row ---------------------------------------------------------------------
     ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20, budget) &&
          mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30, budget);
@@ -439,7 +436,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * LSTM_HS + half * 16, acc[g]);
-      tmem_ld_wait();
+      tmem_ld_wait(acc[0], acc[1], acc[2], acc[3]);
       const uint8_t* ihb = ih_s + (s & 1) * LSTM_IH_BYTES;
       float hv[16];
 #pragma unroll
@@ -507,7 +504,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           if (s + 3 < p.T) mbar_arrive_expect_tx(&h_ready[s & 1], p.slices * LSTMC_PIECE);
           issue_mmas(s & 1);
         } else {
-          *abort_flag = 1;
+          abort_flag.set(1);
         }
       }
     } else {
@@ -527,10 +524,6 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 }
 
 // ---- host -------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFnL)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 size_t lstm_scratch_bytes(long long B, int H) {
   const size_t hbuf = ((size_t)2 * B * H + 255) & ~(size_t)255;
   const size_t flags = (size_t)((B + LSTM_ROWS - 1) / LSTM_ROWS) * (H / LSTM_HS) * sizeof(unsigned int);
@@ -556,15 +549,18 @@ int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_
   const int groups = (int)((a.B + LSTM_ROWS - 1) / LSTM_ROWS);
   const int slices = a.H / LSTM_HS;
   const int grid = groups * slices;
-  if (grid > sm_count()) return GSB200_ERR_UNSUPPORTED;     // every CTA must be resident: they wait on one another
+  // every CTA must be resident (they wait on one another); the grid is never capped, so the physical SM count
+  // is what bounds it, not the cap a caller may have set for the GEMM grids
+  if (grid > sm_count_physical()) return GSB200_ERR_UNSUPPORTED;
 
-  static bool attr_done[64];
+  static std::atomic<int> attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if (dev < 0 || dev >= 64) return GSB200_ERR_DEVICE;
+  if (!attr_done[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(lstm_recurrent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LSTM_SMEM_BYTES);
     if (e != cudaSuccess) return cuda_status(e, "cudaFuncSetAttribute(lstm)");
-    attr_done[dev] = true;
+    attr_done[dev].store(1, std::memory_order_release);
   }
 
   LstmParams p{};
@@ -575,72 +571,61 @@ int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_
   const size_t hbuf_bytes = ((size_t)2 * a.B * a.H + 255) & ~(size_t)255;
   p.hbuf = static_cast<uint8_t*>(scratch);
   p.flags = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(scratch) + hbuf_bytes);
-  cudaError_t e = cudaMemsetAsync(p.flags, 0, (size_t)grid * sizeof(unsigned int), st);
-  if (e != cudaSuccess) return cuda_status(e, "lstm flags memset");
 
-  void* fnp = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fnp, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return GSB200_ERR_DEVICE;
-  EncodeTiledFnL enc = reinterpret_cast<EncodeTiledFnL>(fnp);
+  if (a.ld_w < a.H || a.ld_w % 16 != 0) return GSB200_ERR_BAD_ARG;
   CUtensorMap tw, tih;
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)a.H, (cuuint64_t)4 * a.H};
-    cuuint64_t strides[1] = {(cuuint64_t)a.ld_w};
-    cuuint32_t box[2] = {128, LSTM_HS};
-    cuuint32_t es[2] = {1, 1};
-    if (a.ld_w < a.H || a.ld_w % 16 != 0) return GSB200_ERR_BAD_ARG;
-    if (enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(a.w_hh), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return GSB200_ERR_BAD_ARG;
-  }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)4 * a.H, (cuuint64_t)a.T * a.B};
-    cuuint64_t strides[1] = {(cuuint64_t)a.ld_ih * 2};
-    cuuint32_t box[2] = {LSTM_HS, LSTM_ROWS};
-    cuuint32_t es[2] = {1, 1};
-    if (enc(&tih, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(a.ih), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return GSB200_ERR_BAD_ARG;
-  }
+  if (!tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w_hh, (uint64_t)4 * a.H, (uint64_t)a.H, (uint64_t)a.ld_w, 128,
+               LSTM_HS, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !tmap_2d(&tih, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.ih, (uint64_t)a.T * a.B, (uint64_t)4 * a.H,
+               (uint64_t)a.ld_ih, LSTM_HS, LSTM_ROWS, CU_TENSOR_MAP_SWIZZLE_64B))
+    return GSB200_ERR_BAD_ARG;
   // Cluster form first (h exchanged through distributed shared memory): H <= 384, the slices of a row group in one
   // cluster of H / 32 CTAs (more than 8 needs the non-portable cluster size).  GSB200_LSTM_NO_CLUSTER=1 in the
-  // environment, or a device that cannot host such a cluster, selects the cooperative kernel with global scratch.
-  static int no_cluster = -1;
-  if (no_cluster < 0) {
+  // environment, or a device that cannot host a cluster of that size, selects the cooperative kernel with global
+  // scratch.  What the device can host is asked once per (device, cluster size); a refusal is reported on stderr
+  // once and only switches off that cluster size.
+  static std::atomic<int> no_cluster{-1};
+  int nc = no_cluster.load(std::memory_order_relaxed);
+  if (nc < 0) {
     const char* ev = getenv("GSB200_LSTM_NO_CLUSTER");
-    no_cluster = (ev && ev[0] == '1') ? 1 : 0;
+    nc = (ev && ev[0] == '1') ? 1 : 0;
+    no_cluster.store(nc, std::memory_order_relaxed);
   }
-  if (!no_cluster && p.k_blocks <= LSTMC_MAX_KB && slices <= 16) {
-    static int cluster_state[64];          // 0 unknown, 1 attributes set, -1 unavailable
-    if (dev >= 0 && dev < 64 && cluster_state[dev] == 0) {
+  if (!nc && p.k_blocks <= LSTMC_MAX_KB && slices <= 16) {
+    static std::atomic<int> cluster_state[64][17];          // per (device, cluster size): 0 unknown, 1 usable, -1 not
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LSTM_THREADS);
+    cfg.dynamicSmemBytes = LSTMC_SMEM_BYTES; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = slices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int state = cluster_state[dev][slices].load(std::memory_order_acquire);
+    if (state == 0) {
       cudaError_t ce = cudaFuncSetAttribute(lstm_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LSTMC_SMEM_BYTES);
       if (ce == cudaSuccess && slices > 8)
         ce = cudaFuncSetAttribute(lstm_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-      cluster_state[dev] = ce == cudaSuccess ? 1 : -1;
-      if (ce != cudaSuccess) cudaGetLastError();
-    }
-    if (dev >= 0 && dev < 64 && cluster_state[dev] == 1) {
-      cudaLaunchConfig_t cfg{};
-      cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LSTM_THREADS);
-      cfg.dynamicSmemBytes = LSTMC_SMEM_BYTES; cfg.stream = st;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = slices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr; cfg.numAttrs = 1;
       int max_clusters = 0;
-      cudaError_t ce = cudaOccupancyMaxActiveClusters(&max_clusters, lstm_cluster_kernel, &cfg);
-      if (ce == cudaSuccess && max_clusters >= 1) {
-        ce = cudaLaunchKernelEx(&cfg, lstm_cluster_kernel, tw, tih, p);
-        if (ce == cudaSuccess) return GSB200_OK;
+      if (ce == cudaSuccess) ce = cudaOccupancyMaxActiveClusters(&max_clusters, lstm_cluster_kernel, &cfg);
+      state = (ce == cudaSuccess && max_clusters >= 1) ? 1 : -1;
+      if (state < 0) {
+        cudaGetLastError();
+        fprintf(stderr, "gigaslop_b200: device %d cannot host a cluster of %d LSTM CTAs (%s); using the cooperative kernel\n",
+                dev, slices, ce == cudaSuccess ? "no active cluster fits" : cudaGetErrorName(ce));
       }
-      cudaGetLastError();                  // fall through to the cooperative kernel
-      cluster_state[dev] = -1;
+      cluster_state[dev][slices].store(state, std::memory_order_release);
+    }
+    if (state == 1) {
+      cudaError_t ce = cudaLaunchKernelEx(&cfg, lstm_cluster_kernel, tw, tih, p);
+      if (ce == cudaSuccess) return GSB200_OK;
+      cudaGetLastError();                  // this launch falls through to the cooperative kernel, and says so
+      fprintf(stderr, "gigaslop_b200: cluster launch of the LSTM layer failed (%s); this call uses the cooperative kernel\n",
+              cudaGetErrorName(ce));
     }
   }
+  // the cooperative kernel exchanges h through the scratch; its step counters start at zero
+  cudaError_t e = cudaMemsetAsync(p.flags, 0, (size_t)grid * sizeof(unsigned int), st);
+  if (e != cudaSuccess) return cuda_status(e, "lstm flags memset");
   void* args[3] = {&tw, &tih, &p};
   e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(lstm_recurrent_kernel), dim3(grid), dim3(LSTM_THREADS), args,
                                   LSTM_SMEM_BYTES, st);
@@ -680,5 +665,141 @@ int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st) {
   }
   return launch_lstm_layer(a, g_lstm_static_ptr[dev], LSTM_STATIC_BYTES, st);
 }
+
+// ---- the whole stack behind one call ---------------------------------------------------------------------------
+// Per layer: the hoisted input projection (FP8 GEMM over the T*B rows) and the persistent recurrence; layers
+// alternate direction and hand each other h as E4M3 at the row scale 1/448.  With an auxiliary stream the
+// recurrence of a layer is cut into `time_blocks` launches (the state crosses a cut exactly: h as the E4M3 bytes
+// the kernel itself feeds back, c as the fp16 it carries), and as soon as a block of layer l is done the hoisted
+// projection of layer l + 1 over the same timesteps runs on the auxiliary stream, on the SMs the recurrence
+// leaves idle -- ordered by events only, no kernel waits for another kernel.
+//
+// Workspace: [ih 0][ih 1 (overlap only)][h8 0][h8 1][row scales = 1/448][c 0][c 1][layer scratch]
+__global__ void fill_f32_kernel(float* dst, long long n, float v) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = v;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+size_t lstm_stack_workspace_bytes(long long T, long long B, int H, int overlap) {
+  if (T <= 0 || B <= 0 || H <= 0) return 0;
+  const size_t rows = (size_t)T * (size_t)B;
+  return (overlap ? 2 : 1) * align256(rows * 4 * H * 2) + 2 * align256(rows * H) + align256(rows * 4) +
+         2 * align256((size_t)B * H * 2) + align256(lstm_scratch_bytes(B, H));
+}
+
+int32_t launch_lstm_stack(const uint8_t* x, long long ldx, const float* sx, int C, const gsb200_lstm_layer_t* layers,
+                          int n_layers, int reverse_first, __half* h_out, long long T, long long B, int H,
+                          int time_blocks, void* ws, size_t ws_bytes, cudaStream_t st, cudaStream_t aux) {
+  if (T == 0 || B == 0 || n_layers == 0) return GSB200_OK;
+  if (!x || !sx || !layers || !h_out || !ws || T < 0 || B < 0 || n_layers < 0 || C <= 0) return GSB200_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return GSB200_ERR_BAD_ARG;
+  if (H <= 0 || H % LSTM_HS != 0 || H > LSTM_MAX_KB * 128) return GSB200_ERR_UNSUPPORTED;
+  if ((long long)T * B > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
+  for (int l = 0; l < n_layers; ++l)
+    if (!layers[l].w_ih || !layers[l].s_ih || !layers[l].w_hh || !layers[l].s_hh) return GSB200_ERR_BAD_ARG;
+  const bool overlap = aux != nullptr && aux != st && n_layers > 1;
+  int nb = overlap ? (time_blocks > 0 ? time_blocks : 8) : 1;
+  if (nb > T) nb = (int)T;
+  if (ws_bytes < lstm_stack_workspace_bytes(T, B, H, overlap ? 1 : 0)) return GSB200_ERR_BAD_ARG;
+  int32_t rc = ensure_device();
+  if (rc != GSB200_OK) return rc;
+
+  const size_t rows = (size_t)T * (size_t)B;
+  uint8_t* w = static_cast<uint8_t*>(ws);
+  __half* ih[2];
+  ih[0] = reinterpret_cast<__half*>(w); w += align256(rows * 4 * H * 2);
+  ih[1] = ih[0];
+  if (overlap) { ih[1] = reinterpret_cast<__half*>(w); w += align256(rows * 4 * H * 2); }
+  uint8_t* h8[2];
+  h8[0] = w; w += align256(rows * H);
+  h8[1] = w; w += align256(rows * H);
+  float* row_scale = reinterpret_cast<float*>(w); w += align256(rows * 4);
+  __half* cst[2];
+  cst[0] = reinterpret_cast<__half*>(w); w += align256((size_t)B * H * 2);
+  cst[1] = reinterpret_cast<__half*>(w); w += align256((size_t)B * H * 2);
+  void* scratch = w;
+  const size_t scratch_bytes = align256(lstm_scratch_bytes(B, H));
+
+  if (n_layers > 1) {
+    const long long blocks = ((long long)rows + 255) / 256;
+    fill_f32_kernel<<<(unsigned)blocks, 256, 0, st>>>(row_scale, (long long)rows, 1.0f / 448.0f);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_status(e, "lstm stack: row scale fill");
+  }
+  // hoisted projection of layer l over timesteps [t0, t1) on stream s, at most sm_cap CTAs (0 = all)
+  auto project = [&](int l, long long t0, long long t1, cudaStream_t s, int sm_cap) -> int32_t {
+    GemmArgs g{};
+    g.kind = KIND_F8; g.epi = EPI_DEQUANT;
+    if (l == 0) { g.A = x + (size_t)t0 * B * ldx; g.lda = ldx; g.scale_a = sx + (size_t)t0 * B; g.K = C; }
+    else { g.A = h8[(l - 1) & 1] + (size_t)t0 * B * H; g.lda = H; g.scale_a = row_scale; g.K = H; }
+    g.B0 = layers[l].w_ih; g.ldb = layers[l].ld_w_ih;
+    g.C = ih[l & 1] + (size_t)t0 * B * 4 * H; g.ldc = 4 * H;
+    g.scale_b0 = layers[l].s_ih;
+    g.M = (t1 - t0) * B; g.N = 4 * H;
+    g.sm_cap = sm_cap;
+    return launch_gemm(g, s);
+  };
+  rc = project(0, 0, T, st, 0);
+  if (rc != GSB200_OK) return rc;
+
+  const int groups = (int)((B + LSTM_ROWS - 1) / LSTM_ROWS);
+  const int lstm_ctas = groups * (H / LSTM_HS);
+  int gemm_cap = sm_count_physical() - lstm_ctas;
+  if (gemm_cap < 8) gemm_cap = 8;
+  cudaError_t ce = cudaSuccess;
+  for (int l = 0; l < n_layers; ++l) {
+    const bool last = l == n_layers - 1;
+    const bool rev = ((l % 2) == 0) == (reverse_first != 0);
+    uint8_t* h8_l = h8[l & 1];
+    for (int k = 0; k < nb; ++k) {
+      // block k in processing order covers steps [s0, s1); in time that is [t0, t1)
+      const long long s0 = T * k / nb, s1 = T * (k + 1) / nb;
+      const long long t0 = rev ? T - s1 : s0, t1 = rev ? T - s0 : s1;
+      LstmLayerArgs a{};
+      a.ih = ih[l & 1] + (size_t)t0 * B * 4 * H; a.ld_ih = 4 * H;
+      a.w_hh = layers[l].w_hh; a.ld_w = layers[l].ld_w_hh; a.s_hh = layers[l].s_hh; a.bias = layers[l].bias;
+      if (k > 0) {                       // state at the cut: h of the step processed just before, c of the previous block
+        const long long t_prev = rev ? t1 : t0 - 1;
+        a.h0 = h8_l + (size_t)t_prev * B * H;
+        a.c0 = cst[(k - 1) & 1];
+      }
+      a.h_out = last ? h_out + (size_t)t0 * B * H : nullptr;
+      a.h8_out = h8_l + (size_t)t0 * B * H;
+      a.c_last = k + 1 < nb ? cst[k & 1] : nullptr;
+      a.T = t1 - t0; a.B = B; a.H = H; a.reverse = rev ? 1 : 0;
+      rc = launch_lstm_layer(a, scratch, scratch_bytes, st);
+      if (rc != GSB200_OK) return rc;
+      if (overlap && !last) {
+        cudaEvent_t ev;
+        ce = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (ce != cudaSuccess) return cuda_status(ce, "lstm stack: event");
+        ce = cudaEventRecord(ev, st);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(aux, ev, 0);
+        cudaEventDestroy(ev);            // released by the runtime once the recorded work has completed
+        if (ce != cudaSuccess) return cuda_status(ce, "lstm stack: event");
+        rc = project(l + 1, t0, t1, aux, gemm_cap);
+        if (rc != GSB200_OK) return rc;
+      }
+    }
+    if (!last) {
+      if (overlap) {                     // the next layer starts when its whole projection is there
+        cudaEvent_t ev;
+        ce = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (ce != cudaSuccess) return cuda_status(ce, "lstm stack: event");
+        ce = cudaEventRecord(ev, aux);
+        if (ce == cudaSuccess) ce = cudaStreamWaitEvent(st, ev, 0);
+        cudaEventDestroy(ev);
+        if (ce != cudaSuccess) return cuda_status(ce, "lstm stack: event");
+      } else {
+        rc = project(l + 1, 0, T, st, 0);
+        if (rc != GSB200_OK) return rc;
+      }
+    }
+  }
+  return GSB200_OK;
+}
+
 
 }  // namespace gsb

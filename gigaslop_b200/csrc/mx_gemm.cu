@@ -37,6 +37,8 @@
 //                                from the row groups of the two tiles.
 // M = 65536, N = 2048, K = 512: 104 us (plain) / 276 us (dual) with one pipeline and both operands streamed, 75 / 128 us
 // in the weight-stationary form.
+#include <atomic>
+
 #include "capi_internal.h"
 #include "ptx.cuh"
 
@@ -111,7 +113,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   uint64_t* w_full = acc_empty + 2;                        // WST: resident slice landed
   uint64_t* sfb_ready = w_full + 1;                        // WST: its scale tiles are in TMEM
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sfb_ready + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int OUT_COLS = DUAL ? MX_BN / 2 : MX_BN;          // output columns per tile
   const long long num_tiles = (long long)p.m_blocks * p.n_blocks;
@@ -120,7 +122,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     for (int s = 0; s < 2 * STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], MX_EPI_WARPS); }
     mbar_init(w_full, 1); mbar_init(sfb_ready, 1);
-    *abort_flag = 0;
+    abort_flag.set(0);
     fence_mbar_init();
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1); prefetch_tmap(&tm_c);
   }
@@ -129,7 +131,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const long long budget = spin_budget();          // bound of every wait below, fetched once
+  const unsigned int budget = spin_budget();          // bound of every wait below, fetched once
   // this CTA's tiles: streaming form t = cta, cta + grid, ... (column block fastest); weight-stationary form: a fixed
   // column block and row blocks group, group + n_groups, ...  Tile number `it` of the CTA belongs to pipeline it % 2.
   const int ws_n = WST ? (int)(blockIdx.x % p.n_blocks) : 0;
@@ -337,7 +339,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t v[2][32];                                     // plain: 64 columns; dual: 32 gate | 32 up
       tmem_ld_32x32b_x32(t_row + (DUAL ? half * 32 : half * 64), v[0]);
       tmem_ld_32x32b_x32(t_row + (DUAL ? 64 + half * 32 : half * 64 + 32), v[1]);
-      tmem_ld_wait();
+      tmem_ld_wait(v[0], v[1]);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[as]);
@@ -389,10 +391,6 @@ __global__ void mx_scales_to_tiled_kernel(const uint8_t* __restrict__ src, long 
   dst[i] = (row < rows) ? src[row * ld + b] : (uint8_t)127;   // padding rows: scale 1.0 on zero data
 }
 
-typedef CUresult (*EncodeTiledFnM)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 size_t mx_tiled_scale_bytes(long long rows, int K) {
   return (size_t)((rows + 127) / 128) * (size_t)(K / 128) * 512;
 }
@@ -421,32 +419,22 @@ int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t
   if (N % 32 != 0 || ldc < N || ldc % 8 != 0) return GSB200_ERR_BAD_ARG;
   int32_t rc = ensure_device();
   if (rc != GSB200_OK) return rc;
-  static bool attr_done[64];
+  static std::atomic<int> attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  if (dev < 0 || dev >= 64) return GSB200_ERR_DEVICE;
+  if (!attr_done[dev].load(std::memory_order_acquire)) {
     cudaError_t e1 = cudaFuncSetAttribute(mx_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<false>::BYTES);
     cudaError_t e2 = cudaFuncSetAttribute(mx_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<false>::BYTES);
     cudaError_t e3 = cudaFuncSetAttribute(mx_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<true>::BYTES);
     cudaError_t e4 = cudaFuncSetAttribute(mx_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MxSmem<true>::BYTES);
     if (e1 != cudaSuccess || e2 != cudaSuccess) return cuda_status(e1 != cudaSuccess ? e1 : e2, "cudaFuncSetAttribute(mx gemm)");
     if (e3 != cudaSuccess || e4 != cudaSuccess) return cuda_status(e3 != cudaSuccess ? e3 : e4, "cudaFuncSetAttribute(mx gemm)");
-    attr_done[dev] = true;
+    attr_done[dev].store(1, std::memory_order_release);
   }
-  void* fnp = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fnp, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return GSB200_ERR_DEVICE;
-  EncodeTiledFnM enc = reinterpret_cast<EncodeTiledFnM>(fnp);
   auto map2d = [&](CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows, uint64_t cols,
                    uint64_t ld, uint32_t bc, uint32_t br, CUtensorMapSwizzle sw) {
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {ld * (uint64_t)esz};
-    cuuint32_t box[2] = {bc, br};
-    cuuint32_t es[2] = {1, 1};
-    return enc(m, dt, 2, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return tmap_2d(m, dt, esz, base, rows, cols, ld, bc, br, sw);
   };
   CUtensorMap ta, tb0, tb1, tc;
   const uint32_t brows = dual ? 64 : 128;

@@ -22,7 +22,7 @@ constexpr unsigned int ST_TIMEOUT_MMA      = 1u << 1;
 constexpr unsigned int ST_TIMEOUT_EPILOGUE = 1u << 2;
 constexpr unsigned int ST_TIMEOUT_LSTM     = 1u << 3;
 
-constexpr long long kDefaultSpinBudget = 2000000000ll;   // ~1 s of SM clocks
+constexpr unsigned int kDefaultSpinBudget = 2000000000u;   // ~1 s of SM clocks (kept in 32 bits: one register in every waiting role)
 // Upper bound (ns) a try_wait may keep the thread suspended before it returns to the polling loop; the
 // hardware wakes it as soon as the phase completes, so a waiting role costs almost no issue slots.
 constexpr unsigned int kTryWaitSuspendNs = 20000;
@@ -44,6 +44,20 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+
+// ---- abort flag -------------------------------------------------------------
+// One int in the CTA's shared memory that any role sets when a bounded wait gives up; the other roles poll it
+// and unwind.  Held as its 32-bit shared-window address (one register in every waiting role; a generic pointer
+// costs two, which is what pushed the 56-register front warps of the GEMM into spilling).
+struct AbortFlag {
+  uint32_t addr;
+  __device__ __forceinline__ int get() const {
+    int v; asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory"); return v;
+  }
+  __device__ __forceinline__ void set(int v) const {
+    asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+  }
+};
 
 // ---- mbarrier ---------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -76,24 +90,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Spin budget in SM clocks: read ONCE per thread at kernel start (it lives in global memory; fetching it inside a
 // wait would put an L2 round trip on every blocking hand-off).
-__device__ __forceinline__ long long spin_budget() {
+__device__ __forceinline__ unsigned int spin_budget() {
   const unsigned int v = g_status[2];
-  return v ? (long long)v : kDefaultSpinBudget;
+  return v ? v : kDefaultSpinBudget;
 }
 
 // Bounded wait.  Returns false if the budget ran out or another role already
 // gave up (abort flag in shared memory); the caller must then unwind.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned int fail_code, unsigned int where, long long budget) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, AbortFlag abort_flag,
+                                          unsigned int fail_code, unsigned int where, unsigned int budget) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   int spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > budget) {
-        *abort_flag = 1;
+      if (abort_flag.get()) return false;
+      if (clock64() - t0 > (long long)budget) {
+        abort_flag.set(1);
         atomicOr(&g_status[0], fail_code);
         g_status[1] = where;
         __threadfence();
@@ -132,17 +146,17 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 // Bounded wait on a barrier that threads of other CTAs of the cluster arrive at (same contract as mbar_wait).
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  unsigned int fail_code, unsigned int where, long long budget) {
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, AbortFlag abort_flag,
+                                                  unsigned int fail_code, unsigned int where, unsigned int budget) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   long long t0 = clock64();
   int spins = 0;
   while (true) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((++spins & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > budget) {
-        *abort_flag = 1;
+      if (abort_flag.get()) return false;
+      if (clock64() - t0 > (long long)budget) {
+        abort_flag.set(1);
         atomicOr(&g_status[0], fail_code);
         g_status[1] = where;
         __threadfence();
@@ -337,7 +351,24 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Wait for this thread's TMEM loads.  The registers the loads write are passed through the wait as read-write
+// operands: tcgen05.ld only starts the transfer, and without this tie nothing in the program text would keep a use
+// of those registers (or a copy of them made by the compiler) below the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]) :: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]), "+r"(a[23]), "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]), "+r"(a[30]), "+r"(a[31]) :: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[16], uint32_t (&b)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]) :: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[32], uint32_t (&b)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]), "+r"(a[23]), "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]), "+r"(a[30]), "+r"(a[31]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]), "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]), "+r"(b[21]), "+r"(b[22]), "+r"(b[23]), "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]), "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31]) :: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[16], uint32_t (&b)[16], uint32_t (&c)[16], uint32_t (&d)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]), "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]), "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]), "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]), "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]), "+r"(c[4]), "+r"(c[5]), "+r"(c[6]), "+r"(c[7]), "+r"(c[8]), "+r"(c[9]), "+r"(c[10]), "+r"(c[11]), "+r"(c[12]), "+r"(c[13]), "+r"(c[14]), "+r"(c[15]), "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]), "+r"(d[4]), "+r"(d[5]), "+r"(d[6]), "+r"(d[7]), "+r"(d[8]), "+r"(d[9]), "+r"(d[10]), "+r"(d[11]), "+r"(d[12]), "+r"(d[13]), "+r"(d[14]), "+r"(d[15]) :: "memory");
+}
 
 // ---- packed fp32 pairs (sm_100 f32x2 pipe): each op is two IEEE round-to-nearest results ---------
 // The compiler intrinsics are used rather than inline PTX so that register pairs are allocated by the

@@ -3,7 +3,7 @@ the persistent recurrent kernel; layers alternate direction and feed each other 
 import torch
 
 from ._lib import check, lib
-from .ops import _stream, gemm_fp8
+from .ops import _stream
 
 OUT_SCALE = 1.0 / 448.0
 
@@ -29,23 +29,39 @@ def lstm_layer(ih, W_hh, s_hh, T, B, bias=None, reverse=False, h0=None, c0=None,
     ptr = lambda t: t.data_ptr() if t is not None else None
     check(lib().gsb200_lstm_layer_fp8(ih.data_ptr(), ih.stride(0), W_hh.data_ptr(), W_hh.stride(0), s_hh.data_ptr(),
                                       ptr(bias), ptr(h0), ptr(c0), ptr(h16), ptr(h8), ptr(c_last), T, B, H,
-                                      1 if reverse else 0, scratch.data_ptr(), scratch.numel(), _stream()), "lstm_layer")
+                                      1 if reverse else 0, scratch.data_ptr(), scratch.numel(), _stream(ih)), "lstm_layer")
     return h16, h8, c_last
 
 
-def lstm_stack(x_fp8, sx, layers, T, B, reverse_first=True, scratch=None):
+def lstm_stack_workspace(T, B, H, device, overlap=False):
+    """Workspace of :func:`lstm_stack` (hoisted projections, E4M3 hand-over buffers, layer scratch)."""
+    n = int(lib().gsb200_lstm_stack_workspace_bytes(T, B, H, 1 if overlap else 0))
+    return torch.empty(n, dtype=torch.uint8, device=device)
+
+
+def lstm_stack(x_fp8, sx, layers, T, B, reverse_first=True, workspace=None, aux_stream=None, time_blocks=0, out=None):
     """Stack of layers (dicts with W_ih, s_ih, b, W_hh, s_hh); even layers run reversed when ``reverse_first``.
-    ``x_fp8`` E4M3 ``[T*B, C]`` with per-row scales ``sx``.  Returns the last layer's fp16 ``h`` ``[T*B, H]``."""
-    h16 = None
-    for li, L in enumerate(layers):
-        rev = (li % 2 == 0) == reverse_first
-        ih = gemm_fp8(x_fp8, L["W_ih"], sx, L["s_ih"])                # hoisted projection for all timesteps
-        last = li == len(layers) - 1
-        h16, h8, _ = lstm_layer(ih, L["W_hh"], L["s_hh"], T, B, bias=L["b"], reverse=rev, scratch=scratch,
-                                want_h16=last, want_h8=not last)
-        if not last:
-            x_fp8 = h8
-            sx = torch.full((T * B,), OUT_SCALE, dtype=torch.float32, device=h8.device)
+    ``x_fp8`` E4M3 ``[T*B, C]`` with per-row scales ``sx``.  Returns the last layer's fp16 ``h`` ``[T*B, H]``.
+    One call into the library (``gsb200_lstm_stack_fp8``).  With ``aux_stream`` (a ``torch.cuda.Stream``) the next
+    layer's hoisted projection runs per time block beside the recurrence of the current layer; same bytes."""
+    from ._lib import LstmLayer
+    H = layers[0]["W_hh"].shape[1]
+    C = x_fp8.shape[1]
+    dev = x_fp8.device
+    overlap = aux_stream is not None and len(layers) > 1
+    if workspace is None:
+        workspace = lstm_stack_workspace(T, B, H, dev, overlap)
+    arr = (LstmLayer * len(layers))()
+    for i, L in enumerate(layers):
+        arr[i].w_ih, arr[i].ld_w_ih, arr[i].s_ih = L["W_ih"].data_ptr(), L["W_ih"].stride(0), L["s_ih"].data_ptr()
+        arr[i].w_hh, arr[i].ld_w_hh, arr[i].s_hh = L["W_hh"].data_ptr(), L["W_hh"].stride(0), L["s_hh"].data_ptr()
+        arr[i].bias = L["b"].data_ptr() if L.get("b") is not None else None
+    h16 = out if out is not None else torch.empty((T * B, H), dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().gsb200_lstm_stack_fp8(x_fp8.data_ptr(), x_fp8.stride(0), sx.data_ptr(), C, arr, len(layers),
+                                          1 if reverse_first else 0, h16.data_ptr(), T, B, H, time_blocks,
+                                          workspace.data_ptr(), workspace.numel(), _stream(x_fp8),
+                                          aux_stream.cuda_stream if overlap else None), "lstm_stack")
     return h16
 
 
@@ -63,5 +79,5 @@ def lstm_layer_static(ih, W_hh, s_hh, T, B, bias=None, reverse=False, h0=None, c
     ptr = lambda t: t.data_ptr() if t is not None else None
     check(lib().gsb200_lstm_layer_fp8_static(ih.data_ptr(), ih.stride(0), W_hh.data_ptr(), W_hh.stride(0),
                                              s_hh.data_ptr(), ptr(bias), ptr(h0), ptr(c0), ptr(h16), ptr(h8),
-                                             ptr(c_last), T, B, H, 1 if reverse else 0, _stream()), "lstm_layer_static")
+                                             ptr(c_last), T, B, H, 1 if reverse else 0, _stream(ih)), "lstm_layer_static")
     return h16, h8, c_last

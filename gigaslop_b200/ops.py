@@ -4,20 +4,51 @@ and streams; every byte of compute happens in libgigaslop_b200.so.
 Function names and argument meaning follow the reference's host helpers
 (``quantize_tensor``, ``fp8_quantize_per_token``) and kernels.
 """
+import functools
+
 import torch
 
 from . import _lib
 from ._lib import check, lib
 
 
-def _stream():
-    return torch.cuda.current_stream().cuda_stream
+def _stream(t=None):
+    """Current stream of ``t``'s device (of the current device without ``t``: inside an ``@_on_device`` function
+    that is the tensors' device)."""
+    return torch.cuda.current_stream(t.device if t is not None else None).cuda_stream
 
 
-def _need_cuda(*ts):
+def same_device(*ts):
+    """The one device all given tensors live on.  CPU tensors raise (there is no CPU path); tensors spread over
+    several devices raise (the library launches on one device and would reach the others through peer pointers,
+    with the wrong device's kernel attributes, SM count and static scratch)."""
+    dev = None
     for t in ts:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if t.device.type != "cuda":
             raise RuntimeError("gigaslop_b200 operates on CUDA tensors only (no CPU fallback)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"all tensors of one call must live on one device (got {dev} and {t.device})")
+    return dev
+
+
+_need_cuda = same_device
+
+
+def _on_device(fn):
+    """Run ``fn`` with the device of its tensor arguments current: the C side keys its per-device state on the
+    current device, and ``_stream()`` then returns that device's current stream."""
+    @functools.wraps(fn)
+    def wrapped(*args, **kwargs):
+        dev = same_device(*[a for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor)])
+        if dev is None:
+            return fn(*args, **kwargs)
+        with torch.cuda.device(dev):
+            return fn(*args, **kwargs)
+    return wrapped
 
 
 def _rowmajor(t, name):
@@ -34,6 +65,7 @@ def _dt(t):
     raise TypeError("activations must be float16 or float32")
 
 
+@_on_device
 def quantize_tensor(t, dim=-1, out=None, out_scale=None):
     """Per-row symmetric absmax INT8 quantiser; same contract as the reference's
     ``quantize_tensor`` (cute/bench_quant_i8.py:15-31): returns (int8 [M,K], fp32 dequant scale [M])."""
@@ -49,6 +81,7 @@ def quantize_tensor(t, dim=-1, out=None, out_scale=None):
     return q, s
 
 
+@_on_device
 def fp8_quantize_per_token(x, torch_formulation=True, out=None, out_scale=None):
     """Per-row E4M3 quantiser (fly/rdna_fp8_preshuffle_gemm.py:57-70); ``torch_formulation=False``
     selects the device-kernel arithmetic of fly/rdna_fp8_per_token_quantize.py."""
@@ -76,6 +109,7 @@ _I8 = (torch.int8,)
 _F8 = (torch.float8_e4m3fn, torch.uint8)
 
 
+@_on_device
 def gemm_i8_i32(A, B, out=None):
     """Exact int32 ``A[M,K] . B[N,K]^T`` (cute/ampere_gemm_i8.py TensorOpGemmI8, int32 output)."""
     M, N, K = _check_ab(A, B, _I8)
@@ -94,11 +128,13 @@ def _gemm_f16(fn, name, A, B, scale_a, scale_b, out, flags, dtypes):
     return C
 
 
+@_on_device
 def gemm_i8(A, B, scale_a, scale_b, out=None, flags=0):
     """W8A8 GEMM with per-token x per-channel dequant to fp16 (cute/ampere_gemm_i8_quant_rmem.py)."""
     return _gemm_f16(lib().gsb200_gemm_i8_f16, "gemm_i8", A, B, scale_a, scale_b, out, flags, _I8)
 
 
+@_on_device
 def gemm_fp8(A, B, scale_a, scale_b, out=None, flags=0):
     """FP8 GEMM, ``B`` K-major ``[N,K]`` (fly/rdna_fp8_preshuffle_gemm.py compile_fp8_gemm)."""
     return _gemm_f16(lib().gsb200_gemm_fp8_f16, "gemm_fp8", A, B, scale_a, scale_b, out, flags, _F8)
@@ -119,6 +155,7 @@ def _rotary(fn, name, A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim,
     return C
 
 
+@_on_device
 def gemm_i8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
                    row_offset=0, out=None, flags=0):
     """QKV GEMM + rotary epilogue (cute/ampere_gemm_i8_rotary.py TensorOpGemmI8Rotary)."""
@@ -126,6 +163,7 @@ def gemm_i8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, ro
                    nhead, head_dim, rotary_dim, seqlen, row_offset, out, flags, _I8)
 
 
+@_on_device
 def quantize_gemm_i8_rotary(x, B, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
                             row_offset=0, out=None, out_scale=None, flags=0):
     """``gemm_i8_rotary(*quantize_tensor(x), ...)`` in one launch: fp16 ``x`` [M, K] in, the int8 operand is made on
@@ -152,6 +190,7 @@ def quantize_gemm_i8_rotary(x, B, scale_b, sin_buf, cos_buf, nhead, head_dim, ro
     return C
 
 
+@_on_device
 def gemm_fp8_rotary(A, B, scale_a, scale_b, sin_buf, cos_buf, nhead, head_dim, rotary_dim, seqlen,
                     row_offset=0, out=None, flags=0):
     """FP8 QKV GEMM + rotary (fly/rdna_fp8_gemm_rotary.py compile_fp8_gemm_rotary)."""
@@ -171,18 +210,21 @@ def _dual(fn, name, A, Bg, Bu, scale_a, sbg, sbu, out, flags, dtypes):
     return C
 
 
+@_on_device
 def dual_gemm_i8_silu(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=None, flags=0):
     """``silu(A.Bg^T) * (A.Bu^T)`` (cute/ampere_dual_gemm_i8_silu.py TensorOpDualGemmI8Silu)."""
     return _dual(lib().gsb200_dual_gemm_i8_silu_f16, "dual_gemm_i8_silu", A, B_gate, B_up, scale_a,
                  scale_b_gate, scale_b_up, out, flags, _I8)
 
 
+@_on_device
 def dual_gemm_fp8_silu(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=None, flags=0):
     """FP8 SwiGLU dual GEMM (fly/rdna_fp8_dual_gemm_silu.py compile_fp8_dual_gemm_silu)."""
     return _dual(lib().gsb200_dual_gemm_fp8_silu_f16, "dual_gemm_fp8_silu", A, B_gate, B_up, scale_a,
                  scale_b_gate, scale_b_up, out, flags, _F8)
 
 
+@_on_device
 def mxfp8_quantize(x, out=None, out_scale=None):
     """Activations [M,K] fp16/fp32 -> (float8_e4m3fn [M,K], uint8 E8M0 scales [M,K/32]); one scale per 32 elements."""
     _need_cuda(x)
@@ -195,6 +237,7 @@ def mxfp8_quantize(x, out=None, out_scale=None):
     return q, s
 
 
+@_on_device
 def dual_gemm_fp8_silu_mxfp8(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up, out=None, out_scale=None, flags=0):
     """FP8 SwiGLU dual GEMM emitting MXFP8 (elements + E8M0 scale per 32 output columns); the interface of
     fp8_dual_silu_mxfp8_wrapper (fly/export_fp8_dual_gemm_silu_mxfp8.py:206-236)."""
@@ -210,6 +253,7 @@ def dual_gemm_fp8_silu_mxfp8(A, B_gate, B_up, scale_a, scale_b_gate, scale_b_up,
     return q, s
 
 
+@_on_device
 def gemm_f16(A, B, scale_a=None, scale_b=None, out=None, flags=0):
     """``(A_f16 . B_f16^T) * sA * sB`` -> fp16, scales optional (compile_f16_down_proj,
     fly/rdna_fp8_factored_gemm.py:660-843, is this with no scales and B = dn ``[R, C]``)."""
@@ -222,12 +266,14 @@ def gemm_f16(A, B, scale_a=None, scale_b=None, out=None, flags=0):
     return C
 
 
+@_on_device
 def fp8_down_proj(x_fp8, scale_x, dn_fp8_rc, scale_dn, out=None):
     """``x_down_f16[M,R] = (x_fp8 . dn_fp8^T) * sx[m] * s_dn`` with a single scalar weight scale
     (compile_fp8_down_proj, fly/rdna_fp8_factored_gemm.py:442-651); ``dn`` K-major ``[R, C]``."""
     return gemm_fp8(x_fp8, dn_fp8_rc, scale_x, scale_dn, out=out, flags=_lib.FLAG_SCALAR_SCALE_B)
 
 
+@_on_device
 def fp8_factored_gemm(x_fp8, scale_x, dn_fp8_rc, scale_dn, up_f16_nr, bias, out=None):
     """Hoisted low-rank input projection ``ih = f16(f16((x . dn^T) * sx * s_dn) . up^T + bias)`` in one call
     (compile_fp8_factored_gemm, fly/rdna_fp8_factored_gemm.py:86-435).  ``dn`` ``[R, C]`` E4M3 and ``up``
@@ -249,6 +295,7 @@ def fp8_factored_gemm(x_fp8, scale_x, dn_fp8_rc, scale_dn, up_f16_nr, bias, out=
     return ih
 
 
+@_on_device
 def factored_lstm_step(h_fp8_out, c_inout, hh_down, up_hh, bias_hh, x_down, up_ih, bias_ih):
     """One step of the low-rank hard-gate LSTM cell; argument order of fp8_factored_lstm_wrapper
     (fly/export_fp8_factored_lstm.py:158-182).  ``up_hh`` ``[4H, K_hh]`` and ``up_ih`` ``[4H, R]`` fp16 K-major."""
@@ -266,6 +313,7 @@ def factored_lstm_step(h_fp8_out, c_inout, hh_down, up_hh, bias_hh, x_down, up_i
     return h_fp8_out, c_inout
 
 
+@_on_device
 def mx_scales_to_tiled(scales, K):
     """Row-major E8M0 scales ``[rows, K/32]`` -> the 128 x 4 tile order the block-scaled GEMMs take."""
     _need_cuda(scales)
@@ -276,6 +324,7 @@ def mx_scales_to_tiled(scales, K):
     return out
 
 
+@_on_device
 def gemm_mxfp8(A, sfa_tiled, B, sfb_tiled, out=None):
     """Block-scaled MXFP8 GEMM ``A[M,K] . B[N,K]^T`` (E8M0 scale per 32 K elements on both operands) -> fp16."""
     M, N, K = _check_ab(A, B, _F8)
@@ -285,6 +334,7 @@ def gemm_mxfp8(A, sfa_tiled, B, sfb_tiled, out=None):
     return C
 
 
+@_on_device
 def dual_gemm_mxfp8_silu(A, sfa_tiled, B_gate, B_up, sfb_gate_tiled, sfb_up_tiled, out=None):
     """Block-scaled MXFP8 SwiGLU dual GEMM ``silu(A.Bg^T) * (A.Bu^T)`` -> fp16."""
     M, N, K = _check_ab(A, B_gate, _F8)

@@ -31,17 +31,12 @@ extern "C" {
 #define GSB200_ERR_BAD_ARG (-1)      /* null / misaligned pointer, bad size (reference wrappers return -1 for a bad M) */
 #define GSB200_ERR_UNSUPPORTED (-2)  /* shape outside what the kernels were built for */
 #define GSB200_ERR_DEVICE (-3)       /* current device is not an sm_100 part */
-#define GSB200_ERR_TIMEOUT (-4)      /* a bounded device-side wait gave up (see gsb200_device_status) */
 
 #define GSB200_F16 0
 #define GSB200_F32 1
 
-/* bit flags for the `flags` argument of the GEMM entry points */
-#define GSB200_FLAG_DIRECT_STORE 1   /* diagnostic: epilogue stores straight from registers (no smem + TMA store) */
-#define GSB200_FLAG_ABLATE_STORES 0x100   /* timing ablation, output is NOT written: skip the epilogue's stores */
-#define GSB200_FLAG_ABLATE_EPILOGUE 0x200 /* timing ablation, output is NOT written: skip the epilogue body */
+/* bit flags for the `flags` argument of the GEMM entry points; any other bit is rejected with GSB200_ERR_BAD_ARG */
 #define GSB200_FLAG_SCALAR_SCALE_B 4  /* plain dequant GEMMs: scale_b points to ONE fp32 used for every output column */
-#define GSB200_FLAG_STREAMING 2      /* diagnostic: stream both operands even when the weight slice could stay resident */
 /* Rotary GEMMs share the row blocks of the last, incomplete round among the CTAs that would idle (3.7 % faster alone
  * at M = 65536).  A caller that fills those SMs itself, with another kernel on a second stream, switches that off. */
 #define GSB200_FLAG_OWN_ROW_BLOCKS 8
@@ -63,7 +58,9 @@ int32_t gsb200_device_status(uint32_t out[4]);   /* read-and-clear the device st
 int32_t gsb200_set_spin_budget(uint32_t clocks); /* bound (SM clocks) for device-side waits; 0 restores the default */
 /* The persistent GEMM kernels launch at most `sms` CTAs (one per SM) from now on; 0 restores "all SMs".  A caller that
  * runs another kernel beside a GEMM on a second stream (the quantiser of the next batch, say) leaves it a few SMs
- * this way: a GEMM CTA fills an SM's register file, so nothing else runs on the SMs it occupies. */
+ * this way: a GEMM CTA fills an SM's register file, so nothing else runs on the SMs it occupies.  The cap is one value
+ * for the whole process: it applies to every device and every host thread, and not to the LSTM kernels (whose CTAs
+ * wait on one another and are always launched in full). */
 int32_t gsb200_set_sm_limit(int32_t sms);
 /* Launches one warp that waits on a barrier nothing signals; with a small spin budget the wait gives up and
  * sets bit 2 of the status word.  Exercises the give-up path without hanging the device. */
@@ -234,6 +231,27 @@ int32_t gsb200_lstm_layer_fp8(const void* ih, int64_t ld_ih, const uint8_t* w_hh
                               const float* bias, const uint8_t* h0, const void* c0, void* h_out, uint8_t* h8_out,
                               void* c_last, int64_t T, int64_t B, int32_t H, int32_t reverse, void* scratch,
                               int64_t scratch_bytes, gsb200_stream_t stream);
+
+/* The whole LSTM stack in one call: per layer the hoisted input projection (gsb200_gemm_fp8_f16 over the T*B rows)
+ * and the recurrence (gsb200_lstm_layer_fp8); layer l > 0 consumes the E4M3 h of layer l - 1 at the row scale 1/448;
+ * directions alternate (reverse_first != 0: layers 0, 2, ... walk t = T-1..0).  The reference keeps this loop in
+ * its caller and replays two launches per timestep and layer from a graph (fly/bench_factored_lstm.py:82-85,104-121).
+ * x [T*B, C] E4M3 with per-row scales sx[T*B]; layer 0 has w_ih [4H, C], the others [4H, H]; h_out fp16 [T*B, H] is
+ * the last layer's output.  aux_stream (may be null): a second stream of the caller.  With it, each recurrence is cut
+ * into time_blocks launches (0 = 8) and the next layer's projection of a block's timesteps runs on aux_stream beside
+ * the following block, on the SMs the recurrence leaves idle; the result is the same, bit for bit.  The call returns
+ * with work queued on both streams; `stream` ends up ordered after all of it.
+ * workspace: gsb200_lstm_stack_workspace_bytes(T, B, H, overlap = aux_stream given) bytes, 256-byte aligned. */
+typedef struct {
+  const uint8_t* w_ih; int64_t ld_w_ih; const float* s_ih;   /* input weights E4M3 K-major, per-channel scales [4H] */
+  const uint8_t* w_hh; int64_t ld_w_hh; const float* s_hh;   /* recurrent weights [4H, H], per-channel scales [4H] */
+  const float* bias;                                          /* b_ih + b_hh [4H], or null */
+} gsb200_lstm_layer_t;
+int64_t gsb200_lstm_stack_workspace_bytes(int64_t T, int64_t B, int32_t H, int32_t overlap);
+int32_t gsb200_lstm_stack_fp8(const uint8_t* x, int64_t ldx, const float* sx, int32_t C,
+                              const gsb200_lstm_layer_t* layers, int32_t n_layers, int32_t reverse_first, void* h_out,
+                              int64_t T, int64_t B, int32_t H, int32_t time_blocks, void* workspace,
+                              int64_t workspace_bytes, gsb200_stream_t stream, gsb200_stream_t aux_stream);
 
 /* The same LSTM layer for hosts that may not allocate device memory.  It has no counterpart in the reference.
  * Who needs it: an inference server that hands this library a fixed arena and forbids cudaMalloc after start-up,

@@ -35,15 +35,14 @@ def test_fp8_gemm_golden():
     assert_close(c, ref, atol=float(ref.abs().max()) * 2 ** -7, rtol=2e-2, what="vs reference golden (bf16)")
 
 
-@pytest.mark.parametrize("flags", [0, 1])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (1000, 512, 512), (333, 1536, 512), (256, 512, 2048), (64, 1536, 384)])
-def test_fp8_gemm_random(M, N, K, flags):
+def test_fp8_gemm_random(M, N, K):
     g = need_lib()
     gen = torch.Generator().manual_seed(M + 3 * N + 7 * K)
     x = torch.randn(M, K, generator=gen)
     A, sa = oracle.fp8_quantize_per_token(x)
     W, sb = rand_e4m3(gen, N, K), rand_scales(gen, N)
-    c = g.gemm_fp8(A.cuda(), W.cuda(), sa.cuda(), sb.cuda(), flags=flags)
+    c = g.gemm_fp8(A.cuda(), W.cuda(), sa.cuda(), sb.cuda())
     ref = oracle.fp8_gemm_f16_ref(A, W, sa, sb)
     assert_close(c, ref.half(), atol=float(ref.abs().max()) * 2 ** -9, rtol=2e-2, what="fp8 GEMM vs fp32 reference")
     model = oracle.fp8_gemm_model(A, W, sa, sb)

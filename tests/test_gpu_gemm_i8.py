@@ -8,12 +8,9 @@ import torch
 
 import oracle
 from conftest import load_golden
-from util import T, assert_bitexact, assert_close, f16_equal_up_to_signed_zero, need_lib, rand_i8, rand_scales
+from util import T, assert_bitexact, assert_close, f16_equal_up_to_signed_zero, need_lib, rand_i8, rand_scales, rotary_rows
 
 pytestmark = pytest.mark.gpu
-
-DIRECT = 1        # epilogue stores straight from registers
-STREAM = 2        # stream both operands even where the weight slice could stay resident
 
 
 def test_gemm_i32_golden():
@@ -43,15 +40,15 @@ def test_gemm_i32_worst_case_magnitude():
     assert_bitexact(c, oracle.gemm_i32(A, B))
 
 
-@pytest.mark.parametrize("flags", [0, DIRECT, STREAM])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (16384, 512, 512), (257, 520, 512), (64, 1536, 512), (2000, 512, 2048),
-                                   (5000, 1536, 384), (3000, 4096, 512)])
-def test_gemm_dequant(M, N, K, flags):
+                                   (5000, 1536, 384), (3000, 4096, 512), (700, 1536, 640), (40000, 512, 1024)])
+def test_gemm_dequant(M, N, K):
+    """K <= 512 runs the weight-stationary schedule, larger K the streaming one."""
     g = need_lib()
     gen = torch.Generator().manual_seed(1000 + M + N + K)
     A, B = rand_i8(gen, M, K), rand_i8(gen, N, K)
     sa, sb = rand_scales(gen, M, 5e-3, 5e-2), rand_scales(gen, N)
-    c = g.gemm_i8(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), flags=flags)
+    c = g.gemm_i8(A.cuda(), B.cuda(), sa.cuda(), sb.cuda())
     exact = oracle.gemm_dequant_exact(A, B, sa, sb)
     assert f16_equal_up_to_signed_zero(c, exact) == 0, "fp16 output differs from the exact-accumulator model"
     ref = oracle.gemm_dequant_ref(A, B, sa, sb)
@@ -72,15 +69,14 @@ def test_gemm_dequant_strided_views():
     assert float(Cbig[:, 264:].abs().max()) == 0.0, "wrote outside the N columns"
 
 
-@pytest.mark.parametrize("flags", [0, DIRECT])
-def test_rotary_reference_scenario(flags):
+def test_rotary_reference_scenario():
     """The reference's own JIT parity case: M=64 (4x16), K=512, N=1536 (cute/test_gemm_i8_rotary_vs_openfish.py)."""
     g = need_lib()
     gold = load_golden("rotary")
     nhead, head_dim, rotary_dim, seqlen = (int(v) for v in gold["dims"])
     a, b, sa, sb, sn, cs = (T(gold[k]) for k in ("a", "b", "sa", "sb", "sin", "cos"))
     c = g.gemm_i8_rotary(a.cuda(), b.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(),
-                         nhead, head_dim, rotary_dim, seqlen, flags=flags)
+                         nhead, head_dim, rotary_dim, seqlen)
     ref16 = T(gold["c"]).half()
     err = (c.cpu().float() - ref16.float()).abs().max().item()
     assert err <= 0.05, f"max abs err {err} vs the reference's 0.05 gate"
@@ -88,12 +84,13 @@ def test_rotary_reference_scenario(flags):
     assert f16_equal_up_to_signed_zero(c, exact) == 0
 
 
-@pytest.mark.parametrize("M,seqlen,row_offset,flags", [(256, 1024, 0, 0), (256, 333, 0, 0), (4096, 2048, 0, 0),
-                                                       (1000, 2048, 1536, 0), (130, 16, 5, DIRECT), (20000, 2048, 0, 0),
-                                                       (4096, 2048, 0, STREAM), (700, 77, 3, STREAM)])
-def test_rotary_shapes(M, seqlen, row_offset, flags):
+@pytest.mark.parametrize("M,seqlen,row_offset,K", [(256, 1024, 0, 512), (256, 333, 0, 512), (4096, 2048, 0, 512),
+                                                   (1000, 2048, 1536, 512), (130, 16, 5, 512), (20000, 2048, 0, 512),
+                                                   (4096, 2048, 0, 1024), (700, 77, 3, 640)])
+def test_rotary_shapes(M, seqlen, row_offset, K):
+    """K <= 512 runs the activation-stationary schedule, larger K the streaming one."""
     g = need_lib()
-    nhead, head_dim, rotary_dim, K = 8, 64, 64, 512
+    nhead, head_dim, rotary_dim = 8, 64, 64
     N = 3 * nhead * head_dim
     gen = torch.Generator().manual_seed(2000 + M + seqlen)
     X = torch.randn(M, K, generator=gen)
@@ -101,7 +98,7 @@ def test_rotary_shapes(M, seqlen, row_offset, flags):
     B, sb = rand_i8(gen, N, K), rand_scales(gen, N)
     sn, cs = oracle.rope_tables(max(seqlen, 16), rotary_dim // 2, head_dim)
     c = g.gemm_i8_rotary(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(),
-                         nhead, head_dim, rotary_dim, seqlen, row_offset=row_offset, flags=flags)
+                         nhead, head_dim, rotary_dim, seqlen, row_offset=row_offset)
     # the oracle indexes angle rows by m % seqlen: emulate the shard offset by prepending rows
     pad = row_offset
     Ap = torch.cat([torch.zeros(pad, K, dtype=torch.int8), A])
@@ -130,26 +127,26 @@ def test_rotary_identity_table_equals_plain_gemm():
     assert f16_equal_up_to_signed_zero(c, exact) == 0
 
 
-@pytest.mark.parametrize("flags", [0, DIRECT])
-def test_dual_silu_golden(flags):
+def test_dual_silu_golden():
     g = need_lib()
     gold = load_golden("dual_silu")
     a, bg, bu, sa, sbg, sbu = (T(gold[k]) for k in ("a", "bg", "bu", "sa", "sbg", "sbu"))
-    c = g.dual_gemm_i8_silu(a.cuda(), bg.cuda(), bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda(), flags=flags)
+    c = g.dual_gemm_i8_silu(a.cuda(), bg.cuda(), bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda())
     ref = T(gold["c"])
     assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="SwiGLU vs reference golden")
 
 
-@pytest.mark.parametrize("flags", [0, STREAM])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 2048, 512), (4096, 2048, 512), (65, 136, 512), (9000, 2048, 512)])
-def test_dual_silu_shapes(M, N, K, flags):
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 2048, 512), (4096, 2048, 512), (65, 136, 512), (9000, 2048, 512),
+                                   (1000, 2048, 640), (4096, 1024, 768)])
+def test_dual_silu_shapes(M, N, K):
+    """K <= 512 runs the weight-stationary schedule, larger K the streaming one."""
     g = need_lib()
     gen = torch.Generator().manual_seed(3000 + M + N)
     X = torch.randn(M, K, generator=gen)
     A, sa = oracle.quantize_tensor(X)
     Bg, Bu = rand_i8(gen, N, K), rand_i8(gen, N, K)
     sbg, sbu = rand_scales(gen, N), rand_scales(gen, N)
-    c = g.dual_gemm_i8_silu(A.cuda(), Bg.cuda(), Bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda(), flags=flags)
+    c = g.dual_gemm_i8_silu(A.cuda(), Bg.cuda(), Bu.cuda(), sa.cuda(), sbg.cuda(), sbu.cuda())
     model = oracle.dual_gemm_silu_model(A, Bg, Bu, sa, sbg, sbu)
     assert_close(c, model, atol=2 * float(model.float().abs().max()) * 2 ** -11, rtol=2e-3, what="vs kernel model")
     ref = oracle.dual_gemm_silu_ref(A, Bg, Bu, sa, sbg, sbu)
@@ -218,6 +215,9 @@ def test_bad_arguments_are_rejected_before_launch():
         g.gemm_i8_rotary(A, B, s, s, sn64, sn64, 1, 128, 128, 16)  # unsupported head_dim
     with pytest.raises(RuntimeError):
         g.gemm_i8(A.cpu(), B.cpu(), s.cpu(), s.cpu())        # no CPU path
+    for bad_flags in (1, 2, 0x100, 0x200, 16):
+        with pytest.raises(RuntimeError):
+            g.gemm_i8(A, B, s, s, flags=bad_flags)           # diagnostic / unknown flag bits are not part of the ABI
     assert g.device_status()[0] == 0
 
 
@@ -312,6 +312,13 @@ def test_fused_quantise_rotary_equals_two_calls(M, K, nhead, seqlen):
     assert g.device_status()[0] == 0
     assert_bitexact(s_out.cpu(), s.cpu(), "token scales of the fused kernel")
     assert_bitexact(got.cpu(), want.cpu(), "fused quantise + rotary GEMM vs two calls")
+    # and against the CPU oracle (quantize_tensor, then the rotary epilogue on exact accumulators) on row slices
+    xc, gc = x.cpu(), got.cpu()
+    for lo, hi in [(0, min(M, 200)), (max(0, M // 2 - 70), min(M, M // 2 + 70)), (max(0, M - 130), M)]:
+        q_ref, s_ref = oracle.quantize_tensor(xc[lo:hi].float())
+        assert_bitexact(s_out[lo:hi].cpu(), s_ref, f"fused token scales vs oracle, rows {lo}:{hi}")
+        exact = rotary_rows(oracle.rotary_exact, q_ref, s_ref, W.cpu(), sw.cpu(), sn.cpu(), cs.cpu(), nhead, 64, 64, seqlen, lo + 3)
+        assert f16_equal_up_to_signed_zero(gc[lo:hi], exact) == 0, f"fused kernel vs oracle, rows {lo}:{hi}"
 
 
 def test_sm_limit_changes_the_grid_not_the_result():
@@ -353,6 +360,11 @@ def test_rotary_shared_leftover_row_blocks(M):
     W, sw = rand_i8(gen, N, K).cuda(), rand_scales(gen, N).cuda()
     sn, cs = (t.cuda() for t in oracle.rope_tables(seqlen, 32, 64))
     got = g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, seqlen, row_offset=11).cpu()
+    # the shared row blocks are the last ones: they and the first block against the CPU model, bit for bit
+    for lo, hi in [(0, 128), (M - 300, M)]:
+        exact = rotary_rows(oracle.rotary_exact, A[lo:hi].cpu(), sa[lo:hi].cpu(), W.cpu(), sw.cpu(), sn.cpu(), cs.cpu(),
+                            8, 64, 64, seqlen, lo + 11)
+        assert f16_equal_up_to_signed_zero(got[lo:hi], exact) == 0, f"rows {lo}:{hi} vs oracle"
     try:
         for limit in (1, 37):
             assert L.gsb200_set_sm_limit(limit) == 0

@@ -1,11 +1,12 @@
 """GPU checks of the persistent LSTM recurrence and the layer stack (full-rank sigmoid/tanh cell of the
 benchmark stack: parity unpinned by the reference, the oracle is this repository's CPU statement with the
-same rounding points).  h and c live in [-1, 1] / O(1), so the gate is an absolute one."""
+same rounding points).  Gate: the benchmark's rtol 2e-2, with an absolute floor because h and c live in [-1, 1] / O(1)
+and cross zero (an element passes if abs err <= atol OR rel err <= 2e-2), plus a bound on the mean error."""
 import pytest
 import torch
 
 import oracle
-from util import need_lib, rand_scales
+from util import assert_close, need_lib, rand_scales
 
 pytestmark = pytest.mark.gpu
 
@@ -24,13 +25,17 @@ def cuda_layer(L):
 
 
 def check_h(got, ref, what, tol=0.03, mean_tol=3e-3):
+    assert_close(got, ref, atol=tol, rtol=2e-2, what=what)
     err = (got.float().cpu() - ref.float()).abs()
-    assert float(err.max()) <= tol, f"{what}: max abs err {float(err.max())}"
     assert float(err.mean()) <= mean_tol, f"{what}: mean abs err {float(err.mean())}"
 
 
 @pytest.mark.parametrize("T,B,H,reverse,init", [(12, 130, 64, False, False), (40, 256, 384, True, True),
-                                                (7, 128, 32, False, True), (25, 512, 384, False, False)])
+                                                (7, 128, 32, False, True), (25, 512, 384, False, False),
+                                                # H > 384: the cooperative kernel (h through global scratch), four K blocks,
+                                                # zero-padded K pieces of W and h when H % 128 != 0
+                                                (10, 256, 512, False, True), (8, 130, 416, True, True),
+                                                (20, 512, 512, True, False), (6, 300, 448, False, False)])
 def test_recurrent_kernel_vs_oracle(T, B, H, reverse, init):
     g = need_lib()
     gen = torch.Generator().manual_seed(T * 7 + B + H)
@@ -56,8 +61,33 @@ def test_two_layer_stack_vs_oracle():
     x8, sx = oracle.fp8_quantize_per_token(x)
     layers = [make_layer(gen, H, C), make_layer(gen, H, H)]
     ref = oracle.lstm_fullrank_stack_ref(x8, sx, layers, T, B, reverse_first=True)
-    out = g.lstm_stack(x8.cuda(), sx.cuda(), [cuda_layer(L) for L in layers], T, B, reverse_first=True)
+    dl = [cuda_layer(L) for L in layers]
+    out = g.lstm_stack(x8.cuda(), sx.cuda(), dl, T, B, reverse_first=True)
     check_h(out, ref, "stack output", tol=0.05, mean_tol=5e-3)
+    # cut into time blocks, the next layer's projection on a second stream: the same bytes
+    for nb in (3, 16):
+        out2 = g.lstm_stack(x8.cuda(), sx.cuda(), dl, T, B, reverse_first=True, aux_stream=torch.cuda.Stream(), time_blocks=nb)
+        torch.cuda.synchronize()
+        assert torch.equal(out, out2), f"{nb} time blocks"
+    assert g.device_status()[0] == 0
+
+
+def test_three_layer_stack_h512_forward_first():
+    """H = 512 (cooperative kernel), three layers, first layer forward, ragged batch."""
+    g = need_lib()
+    gen = torch.Generator().manual_seed(56)
+    T, B, C, H = 9, 200, 128, 512
+    x = torch.randn(T * B, C, generator=gen)
+    x8, sx = oracle.fp8_quantize_per_token(x)
+    layers = [make_layer(gen, H, C), make_layer(gen, H, H), make_layer(gen, H, H)]
+    ref = oracle.lstm_fullrank_stack_ref(x8, sx, layers, T, B, reverse_first=False)
+    dl = [cuda_layer(L) for L in layers]
+    out = g.lstm_stack(x8.cuda(), sx.cuda(), dl, T, B, reverse_first=False)
+    check_h(out, ref, "stack output", tol=0.05, mean_tol=5e-3)
+    out2 = g.lstm_stack(x8.cuda(), sx.cuda(), dl, T, B, reverse_first=False, aux_stream=torch.cuda.Stream(), time_blocks=4)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+    assert g.device_status()[0] == 0
 
 
 def test_long_sequence_drift():

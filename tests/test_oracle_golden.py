@@ -134,3 +134,54 @@ def test_mx_roundtrip_properties():
     scaled = amax.squeeze(-1) / oracle.e8m0_decode(s)
     nz = amax.squeeze(-1) > 0
     assert bool(((scaled >= 256) & (scaled < 512))[nz].all())
+
+
+def test_fp8_fused_refs_are_the_pinned_formulas():
+    """``fp8_rotary_ref`` and ``fp8_dual_silu_ref`` restate inline script code of the reference
+    (fly/bench_fp8_gemm_rotary_vs_openfish.py:91-122, fly/bench_fp8_dual_gemm_silu.py:62-68) for which no function
+    could be executed to make a golden vector.  They are pinned through the pieces they are made of: the formula
+    (dequantise, fp32 matmul, then rotate / silu * up) does not depend on the operand type, so fed with the INT8
+    golden inputs they must reproduce the INT8 golden outputs made by the reference's own ``rotary_ref`` and
+    ``dual_gemm_silu_ref``; and their matmul is ``fp8_gemm_f16_ref``, which the FP8 GEMM golden pins."""
+    g = load_golden("rotary")
+    nhead, head_dim, rotary_dim, seqlen = (int(v) for v in g["dims"])
+    c = oracle.fp8_rotary_ref(T(g["a"]), T(g["b"]), T(g["sa"]), T(g["sb"]), T(g["sin"]), T(g["cos"]),
+                              nhead, head_dim, rotary_dim, seqlen)
+    np.testing.assert_allclose(c.numpy(), g["c"], rtol=1e-5, atol=1e-6)
+    g = load_golden("dual_silu")
+    c = oracle.fp8_dual_silu_ref(*[T(g[k]) for k in ("a", "bg", "bu", "sa", "sbg", "sbu")])
+    np.testing.assert_allclose(c.numpy(), g["c"], rtol=1e-5, atol=1e-6)
+    # on FP8 operands: the rotary reference is the pinned FP8 matmul followed by the pinned rotation, and with an
+    # identity table it is that matmul
+    g = load_golden("fp8_gemm")
+    aq = T(g["aq"]).view(torch.float8_e4m3fn)
+    w_nk = T(g["wq_kn"]).view(torch.float8_e4m3fn).t().contiguous()
+    sa, sb = T(g["asc"]), T(g["ws"])
+    w_nk, sb = torch.cat([w_nk.view(torch.uint8), w_nk.view(torch.uint8)[:64]]).view(torch.float8_e4m3fn), torch.cat([sb, sb[:64]])
+    M, nh = aq.shape[0], 1                                # 192 weight rows = Q | K | V of one 64-wide head
+    plain = oracle.fp8_gemm_f16_ref(aq, w_nk, sa, sb)
+    ident = oracle.fp8_rotary_ref(aq, w_nk, sa, sb, torch.zeros(M, 32), torch.ones(M, 32), nh, 64, 64, M)
+    assert torch.equal(ident, plain)
+    sn, cs = oracle.rope_tables(M, 32, 64)
+    rot = oracle.fp8_rotary_ref(aq, w_nk, sa, sb, sn, cs, nh, 64, 64, M)
+    x0, x1 = plain[:, :32], plain[:, 32:64]
+    assert torch.equal(rot[:, :32], x0 * cs - x1 * sn) and torch.equal(rot[:, 32:64], x0 * sn + x1 * cs)
+    assert torch.equal(rot[:, 128:], plain[:, 128:])
+
+
+def test_same_device_guard():
+    """Host-side guard of the torch-facing layer: CPU tensors and tensors spread over several devices are refused
+    before anything reaches the library (fake tensors: only ``.device`` is looked at)."""
+    import types
+
+    import pytest
+
+    from gigaslop_b200.ops import same_device
+    d0 = types.SimpleNamespace(device=torch.device("cuda", 0))
+    d1 = types.SimpleNamespace(device=torch.device("cuda", 1))
+    assert same_device(d0, None, d0) == torch.device("cuda", 0)
+    assert same_device() is None
+    with pytest.raises(ValueError):
+        same_device(d0, d1)
+    with pytest.raises(RuntimeError):
+        same_device(d0, torch.zeros(1))

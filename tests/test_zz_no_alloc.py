@@ -28,10 +28,14 @@ def _run(lib, static, ih, W, s, b, T, B, H, reverse, scratch=None):
 
 
 def test_static_scratch_entry_point_matches_caller_scratch_twice():
+    """Shapes with H > 384 run the cooperative kernel, the one that exchanges h through the scratch and counts steps
+    in it: with the static entry point that is the array built into the library, reused by the second call (another
+    shape, reversed) with the first call's h bytes and counters still in it.  Same kernel, same inputs: the two entry
+    points must agree bit for bit.  The third shape (H = 384) takes the cluster kernel, which needs no scratch."""
     import gigaslop_b200 as g
     lib = g.lib()
     gen = torch.Generator().manual_seed(909)
-    for (T, B, H, reverse) in [(20, 256, 384, False), (9, 130, 64, True)]:     # second call: other shape, reversed
+    for (T, B, H, reverse) in [(6, 256, 512, False), (5, 130, 448, True), (20, 256, 384, False)]:
         W = ((torch.rand(4 * H, H, generator=gen) * 2 - 1) * 44.8).to(torch.float8_e4m3fn).cuda()
         s = (torch.full((4 * H,), 1 / 448.0) * (0.9 + 0.2 * torch.rand(4 * H, generator=gen))).cuda()
         b = (0.05 * torch.randn(4 * H, generator=gen)).cuda()
@@ -40,11 +44,8 @@ def test_static_scratch_entry_point_matches_caller_scratch_twice():
         ref = _run(lib, False, ih, W, s, b, T, B, H, reverse, scratch)
         got = _run(lib, True, ih, W, s, b, T, B, H, reverse)
         for name, a, r in zip(("h fp16", "h e4m3", "c"), got, ref):
-            # the tolerance of the LSTM tests (0.03 abs on h); the two paths run the same kernel, so expect equality
-            err = (a.float() - r.float()).abs()
-            if name == "h e4m3":
-                err = (a.view(torch.float8_e4m3fn).float() - r.view(torch.float8_e4m3fn).float()).abs() / 448.0
-            assert float(err.max()) <= 0.03, f"{name}: max abs difference {float(err.max())}"
+            assert torch.equal(a, r), f"{name}: static-scratch and caller-scratch entry points differ (T={T}, B={B}, H={H})"
+        assert float(got[0].float().abs().max()) > 0.05, "output is all (near) zero: the layer did not run"
         assert g.device_status()[0] == 0
 
 

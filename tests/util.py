@@ -56,3 +56,16 @@ def rand_scales(gen, n, lo=1e-3, hi=1e-2):
 
 def T(a):
     return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def rotary_rows(fn, A_rows, sa_rows, B, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen, first_pos):
+    """Oracle rotary GEMM (``fn`` = oracle.rotary_exact / rotary_ref / fp8_rotary_ref) for a slice of rows whose first
+    row sits at sequence position ``first_pos``: the oracle takes the angle row from the row index, so the slice is
+    prefixed with ``first_pos % seqlen`` zero rows that are dropped again."""
+    pad = int(first_pos) % int(seqlen)
+    Ap = torch.cat([torch.zeros(pad, A_rows.shape[1], dtype=A_rows.dtype), A_rows])
+    sap = torch.cat([torch.ones(pad), sa_rows])
+    return fn(Ap, B, sap, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)[pad:]
+
+
+SAMPLE_SLICES_64K = [(0, 256), (32768 - 64, 32768 + 64), (65536 - 256, 65536), (12345, 12345 + 77)]
