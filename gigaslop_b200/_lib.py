@@ -22,6 +22,8 @@ SIGNATURES = {
     "gsb200_set_spin_budget": (_i32, [C.c_uint32]),
     "gsb200_set_sm_limit": (_i32, [_i32]),
     "gsb200_selftest_wait_timeout": (_i32, [_p]),
+    "gsb200_tensor_peak_probe": (_i32, [_i32, _i32, _i32, _p, C.POINTER(C.c_int32), _p]),
+    "gsb200_tensor_map_encodes": (_i64, []),
     "gsb200_ptq_int8": (_i32, [_p, _i32, _i64, _p, _i64, _p, _i64, _i32, _p]),
     "gsb200_ptq_fp8": (_i32, [_p, _i32, _i64, _p, _i64, _p, _i64, _i32, _i32, _p]),
     "gsb200_gemm_i8_i32": (_i32, [_p, _i64, _p, _i64, _p, _i64, _i64, _i32, _i32, _p]),

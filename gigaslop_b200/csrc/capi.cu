@@ -27,6 +27,16 @@ int32_t gsb200_set_sm_limit(int32_t sms) {
 
 int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream) { return selftest_wait_timeout(S(stream)); }
 
+int32_t gsb200_tensor_peak_probe(int32_t kind, int32_t n, int32_t mmas, int64_t* clocks, int32_t* ctas_out,
+                                 gsb200_stream_t stream) {
+  int ctas = 0;
+  const int32_t rc = launch_tensor_peak_probe(kind, n, mmas, reinterpret_cast<long long*>(clocks), &ctas, S(stream));
+  if (ctas_out) *ctas_out = ctas;
+  return rc;
+}
+
+int64_t gsb200_tensor_map_encodes(void) { return static_cast<int64_t>(tmap_encode_count()); }
+
 int32_t gsb200_ptq_int8(const void* x, int32_t x_dtype, int64_t ldx, int8_t* q, int64_t ldq, float* scale, int64_t M,
                         int32_t K, gsb200_stream_t stream) {
   return launch_ptq(x, x_dtype, ldx, q, ldq, scale, M, K, 0, S(stream));

@@ -62,6 +62,7 @@ int32_t launch_mx_scales_to_tiled(const uint8_t* src, long long ld, long long ro
 int32_t launch_mx_gemm(bool dual, const uint8_t* A, long long lda, const uint8_t* sfa, const uint8_t* B0,
                        const uint8_t* B1, long long ldb, const uint8_t* sfb0, const uint8_t* sfb1, void* C,
                        long long ldc, long long M, int N, int K, cudaStream_t st);
+int32_t launch_tensor_peak_probe(int kind, int n, int mmas, long long* clocks, int* ctas_out, cudaStream_t st);
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached), capped by set_sm_limit
 int sm_count_physical();          // SMs of the current device, whatever the cap

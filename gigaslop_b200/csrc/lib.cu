@@ -5,4 +5,5 @@
 #include "lstm.cu"
 #include "factored.cu"
 #include "mx_gemm.cu"
+#include "probe.cu"
 #include "capi.cu"

@@ -45,11 +45,14 @@ class QkvRotaryHostPipeline:
         self.free_o = [torch.cuda.Event() for _ in range(depth)]  # o slot downloaded
         self.issued = 0                                           # chunks queued since construction (slot = issued % depth)
 
-    def run(self, x_host, out_host, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0, join=True):
+    def run(self, x_host, out_host, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0, join=True,
+            copy_only=False):
         """Enqueue one pass over all rows; returns after the work is queued.  ``finish()`` waits for it.
 
         ``join=True`` makes the current stream wait for the pass; with ``join=False`` the caller calls ``join()``
         (or ``finish()``) after the last of a series of passes, and may not touch ``out_host`` before that.
+        ``copy_only=True`` queues the same copies with the same dependencies but launches no kernel (``out_host`` then
+        receives whatever the device slots hold): the time of such a pass is the ceiling the host link sets.
         """
         if not (x_host.is_pinned() and out_host.is_pinned()):
             raise ValueError("host buffers must be pinned (page-locked) for asynchronous copies")
@@ -74,10 +77,12 @@ class QkvRotaryHostPipeline:
                 self.cmp.wait_event(self.up[b])
                 if reuse:
                     self.cmp.wait_event(self.free_o[b])
-                ops.quantize_tensor(self.x[b][:rows], out=self.q[b][:rows], out_scale=self.s[b][:rows])
+                if not copy_only:
+                    ops.quantize_tensor(self.x[b][:rows], out=self.q[b][:rows], out_scale=self.s[b][:rows])
                 self.free_x[b].record(self.cmp)
-                ops.gemm_i8_rotary(self.q[b][:rows], w, self.s[b][:rows], s_w, sin, cos, nhead, head_dim,
-                                   rotary_dim, seqlen, row_offset=row_offset + r0, out=self.o[b][:rows])
+                if not copy_only:
+                    ops.gemm_i8_rotary(self.q[b][:rows], w, self.s[b][:rows], s_w, sin, cos, nhead, head_dim,
+                                       rotary_dim, seqlen, row_offset=row_offset + r0, out=self.o[b][:rows])
                 self.done[b].record(self.cmp)
             with torch.cuda.stream(self.d2h):
                 self.d2h.wait_event(self.done[b])

@@ -66,6 +66,19 @@ int32_t gsb200_set_sm_limit(int32_t sms);
  * sets bit 2 of the status word.  Exercises the give-up path without hanging the device. */
 int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream);
 
+/* Measurement utilities (no reference counterpart).
+ * gsb200_tensor_peak_probe: one CTA per SM issues `mmas` tcgen05.mma (M = 128, N = n in {128, 256}, K = 32 bytes;
+ * kind 0 = kind::i8, 1 = kind::f8f6f4 on E4M3) back to back on operands that never leave shared memory.  Time the
+ * launch with events: 2 * 128 * n * 32 * mmas * CTAs operations.  clocks: device int64 [2 * SMs]; per CTA the SM clocks of
+ * the issue loop and of the whole window up to the last MMA's completion (-1 if the bounded wait gave up).  ctas_out
+ * (host, may be null) receives the number of CTAs launched.  This is how the tensor-side roofline denominator of the
+ * benchmark is measured on the box instead of taken from a datasheet.
+ * gsb200_tensor_map_encodes: TMA tensor maps encoded by this process so far (they are cached per host thread; a
+ * steady-state launch on buffers seen before encodes none). */
+int32_t gsb200_tensor_peak_probe(int32_t kind, int32_t n, int32_t mmas, int64_t* clocks, int32_t* ctas_out,
+                                 gsb200_stream_t stream);
+int64_t gsb200_tensor_map_encodes(void);
+
 /* Per-token symmetric absmax INT8 quantiser: qs = (1/amax)*127 (as PyTorch evaluates 127/amax), q = rne(x*qs), scale = 1/qs.
  * Stands in for quantize_tensor (cute/bench_quant_i8.py:15-31); the reference has no
  * GPU kernel for it.  Bit-exact with that function on fp32(x). */

@@ -373,3 +373,25 @@ def test_rotary_shared_leftover_row_blocks(M):
     finally:
         assert L.gsb200_set_sm_limit(0) == 0
     assert g.device_status()[0] == 0
+
+
+def test_tensor_maps_are_cached_per_thread():
+    """A launch on buffers this host thread has launched on before encodes no TMA tensor map (they are a pure function
+    of pointer, shape and stride); a new output buffer costs exactly the one map that names it."""
+    g = need_lib()
+    L = g.lib()
+    gen = torch.Generator().manual_seed(5)
+    A, W = rand_i8(gen, 1000, 512).cuda(), rand_i8(gen, 1536, 512).cuda()
+    sa, sw = rand_scales(gen, 1000).cuda(), rand_scales(gen, 1536).cuda()
+    sn, cs = (t.cuda() for t in oracle.rope_tables(128, 32, 64))
+    out = torch.empty(1000, 1536, dtype=torch.float16, device="cuda")
+    first = g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, 128, out=out).clone()
+    n0 = int(L.gsb200_tensor_map_encodes())
+    for _ in range(5):
+        g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, 128, out=out)
+    assert int(L.gsb200_tensor_map_encodes()) == n0
+    assert torch.equal(out, first)
+    out2 = torch.empty_like(out)
+    g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, 128, out=out2)
+    assert int(L.gsb200_tensor_map_encodes()) == n0 + 1
+    assert torch.equal(out2, first)

@@ -145,3 +145,23 @@ def test_cluster_and_cooperative_kernels_agree(tmp_path):
     assert torch.equal(h8.cpu().view(torch.uint8), ref["h8"])
     assert torch.equal(c.cpu(), ref["c"])
     assert g.device_status()[0] == 0
+
+
+def test_gemm_sm_cap_does_not_reject_the_lstm():
+    """gsb200_set_sm_limit caps the grids of the persistent GEMMs only: a layer whose 48 CTAs fit the GPU still runs
+    (and gives the same bytes) while the cap is 40."""
+    g = need_lib()
+    L = g.lib()
+    gen = torch.Generator().manual_seed(31)
+    T, B, H = 5, 512, 384
+    Lw = make_layer(gen, H, 64)
+    ih = (torch.randn(T * B, 4 * H, generator=gen) * 0.5).half().cuda()
+    args = (ih, Lw["W_hh"].cuda(), Lw["s_hh"].cuda(), T, B)
+    want = g.lstm_layer(*args, bias=Lw["b"].cuda())[0]
+    try:
+        assert L.gsb200_set_sm_limit(40) == 0
+        got = g.lstm_layer(*args, bias=Lw["b"].cuda())[0]
+    finally:
+        assert L.gsb200_set_sm_limit(0) == 0
+    assert torch.equal(got, want)
+    assert g.device_status()[0] == 0
