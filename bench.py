@@ -346,16 +346,30 @@ def build_op(op, M, sets=None):
     raise SystemExit(f"unknown op {op!r}; one of {', '.join(OPS)}")
 
 
-def time_op(fn, iters, warm):
-    """CUDA events on the current stream around ``iters`` calls after ``warm`` untimed ones: microseconds per call."""
+def time_op(fn, iters, warm, graph=True):
+    """Microseconds per call: ``iters`` calls after ``warm`` untimed ones, timed with CUDA events on the launching
+    stream.  With ``graph`` the timed calls are captured into one CUDA graph and replayed (the warm-up runs eagerly and
+    does every first-call set-up): kernels of 5-20 us are otherwise timed at the rate the Python host can launch them.
+    The reference times its per-step LSTM launches the same way (fly/bench_factored_lstm.py:104-121)."""
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        fn(warm + i)
-    e1.record()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(warm + i)
+        g.replay()                       # once untimed: the first replay uploads the graph
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            fn(warm + i)
+        e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / max(iters, 1) * 1e3
 
@@ -382,7 +396,7 @@ def run_only(args):
                    "gemm_i8": 16384, "gemm_fp8": 16384, "ptq_int8": 65536, "fac_gemm": 131072,
                    "factored_lstm_step": 256}.get(args.only, 65536)
     fn, ops_, byts, bound = build_op(args.only, M)
-    us = time_op(fn, args.iters, args.warmup if args.warmup < 100 else 5)
+    us = time_op(fn, args.iters, args.warmup if args.warmup < 100 else 5, graph=False)
     line = f"{args.only} M={M}: {us:.2f} us per call, {byts / us / 1e3:.0f} GB/s algorithmic"
     if ops_:
         line += f", {ops_ / us / 1e6:.0f} T(FL)OPS"
@@ -423,26 +437,63 @@ def tensor_peak_probe(G):
 
 
 def host_us_per_call(G):
-    """Wall-clock host time of one C-ABI call once the tensor maps of its buffers are cached (500 calls queued
-    without synchronising, fewer than the launch queue holds)."""
+    """Wall-clock host time of one C-ABI call once the tensor maps of its buffers are cached: 500 calls queued without
+    synchronising (fewer than the launch queue holds), (a) straight through ctypes with prepared pointers, which is what
+    a C/C++ host pays plus the ctypes marshalling, and (b) through the torch-facing wrappers of ``gigaslop_b200.ops``."""
     from gigaslop_b200 import ops
     L = G.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(7)
     out = {}
-    fn, _, _, _ = build_op("rotary_i8", 128, sets=1)
-    step, _, _, _ = build_op("factored_lstm_step", 256, sets=1)
-    for name, f, calls_per in (("gsb200_gemm_i8_rotary_f16", fn, 1), ("gsb200_factored_lstm_step + fp8_down_proj_wrapper", step, 2)):
-        for _ in range(20):
-            f(0)
-        torch.cuda.synchronize()
-        enc0 = int(L.gsb200_tensor_map_encodes())
-        n = 500 // calls_per
-        t0 = time.perf_counter()
-        for _ in range(n):
-            f(0)
-        t1 = time.perf_counter()
-        torch.cuda.synchronize()
-        out[name] = {"host_us": round((t1 - t0) / n * 1e6, 2), "tensor_maps_encoded": int(L.gsb200_tensor_map_encodes()) - enc0,
-                     "calls": n, "through": "gigaslop_b200.ops (ctypes + torch device guard included)"}
+    # QKV + rotary GEMM on a 128-row problem
+    M, N, K = 128, 1536, 512
+    A, W = _i8(g, M, K), _i8(g, N, K)
+    sa, sb = _scales(g, M), _scales(g, N)
+    sin, cos = torch.randn(2048, 32, generator=g).to(DEV), torch.randn(2048, 32, generator=g).to(DEV)
+    C_ = torch.empty(M, N, dtype=torch.float16, device=DEV)
+    rot_args = (A.data_ptr(), K, W.data_ptr(), K, C_.data_ptr(), N, sa.data_ptr(), sb.data_ptr(), sin.data_ptr(), cos.data_ptr(),
+                M, N, K, 8, 64, 64, 2048, 0, 0, st)
+    rot_py = lambda: ops.gemm_i8_rotary(A, W, sa, sb, sin, cos, 8, 64, 64, 2048, out=C_)
+    # one timestep of the reference's low-rank LSTM cell: recurrent down-projection + cell, B = 256
+    B, H, Kh, R = 256, 1024, 128, 128
+    h8 = _f8(g, B, H); sx = torch.full((B,), 1 / 448.0, device=DEV)
+    dn, sdn = _f8(g, Kh, H), torch.tensor([1e-3], device=DEV)
+    up_hh = (torch.randn(4 * H, Kh, generator=g) * 0.1).half().to(DEV)
+    up_ih = (torch.randn(4 * H, R, generator=g) * 0.1).half().to(DEV)
+    bhh, bih = torch.zeros(4 * H, device=DEV), torch.zeros(4 * H, device=DEV)
+    x_down = (torch.randn(B, R, generator=g) * 0.3).half().to(DEV)
+    c = torch.zeros(B, H, device=DEV)
+    hh_down = torch.empty(B, Kh, dtype=torch.float16, device=DEV)
+    hout = torch.empty(B, H, dtype=torch.uint8, device=DEV)
+    dp_args = (h8.data_ptr(), H, dn.data_ptr(), H, hh_down.data_ptr(), Kh, sx.data_ptr(), sdn.data_ptr(), B, Kh, H, 4, st)
+    cell_args = (hout.data_ptr(), c.data_ptr(), hh_down.data_ptr(), up_hh.data_ptr(), bhh.data_ptr(), x_down.data_ptr(),
+                 up_ih.data_ptr(), bih.data_ptr(), B, H, Kh, R, st)
+
+    def step_c():
+        L.gsb200_gemm_fp8_f16(*dp_args)
+        L.gsb200_factored_lstm_step(*cell_args)
+
+    def step_py():
+        ops.fp8_down_proj(h8, sx, dn, sdn, out=hh_down)
+        ops.factored_lstm_step(hout, c, hh_down, up_hh, bhh, x_down, up_ih, bih)
+
+    for name, f_c, f_py, calls in (("gsb200_gemm_i8_rotary_f16", lambda: L.gsb200_gemm_i8_rotary_f16(*rot_args), rot_py, 1),
+                                   ("gsb200_gemm_fp8_f16 + gsb200_factored_lstm_step (one LSTM timestep)", step_c, step_py, 2)):
+        rec = {"c_abi_calls_per_sample": calls}
+        for key, f in (("c_abi_us", f_c), ("python_wrapper_us", f_py)):
+            for _ in range(20):
+                f()
+            torch.cuda.synchronize()
+            enc0 = int(L.gsb200_tensor_map_encodes())
+            n = 400 // calls
+            t0 = time.perf_counter()
+            for _ in range(n):
+                f()
+            t1 = time.perf_counter()
+            torch.cuda.synchronize()
+            rec[key] = round((t1 - t0) / n * 1e6, 2)
+            rec["tensor_maps_encoded"] = int(L.gsb200_tensor_map_encodes()) - enc0
+        out[name] = rec
     return out
 
 
@@ -478,8 +529,8 @@ def run_config_legs(hbm_peak, tensor_meas, iters):
         out[cfg] = {}
         for name, op, M in legs:
             fn, ops_, byts, bound = build_op(op, M)
-            big = op.startswith("lstm_stack") or op == "ih_proj"
-            us = time_op(fn, 3 if big else iters, 2 if big else 5)
+            big = op.startswith("lstm") or op == "ih_proj"
+            us = time_op(fn, 3 if big else iters, 2 if big else 5, graph=not big)
             rec = kernel_record(us, ops_, byts, bound, hbm_peak, tensor_meas)
             rec["rows"] = M
             if op == "lstm_layer":
@@ -527,16 +578,27 @@ def run_native(args):
     outs = [torch.empty(M, N, dtype=torch.float16, device=dev) for _ in range(NSETS)]
     row_offset = rank * M
 
-    # A step = quantise batch b, then the QKV+rotary GEMM on it.  Steps are queued through the package's two-stream
-    # pipeline: the quantiser of step i+1 runs on a second stream under the ramp and tail of the GEMM of step i
-    # (every step's two kernels are launched, and finish, inside the timed region).
-    from gigaslop_b200.devpipe import QkvRotaryStreamPipeline
-    spipe = QkvRotaryStreamPipeline(M, K, N, dev, depth=NSETS)
+    # A step = quantise batch b, then the QKV+rotary GEMM on it.  The steps are captured into a CUDA graph, twelve to
+    # a replay (four passes over the three buffer sets), so that the two kernels of a step follow each other without
+    # the gap an eager launch leaves; every step's two kernels are launched, and finish, inside the timed region.
+    # Steps that do not fill a replay are launched eagerly, also inside the timed region.
+    from gigaslop_b200.devpipe import QkvRotaryGraph
+    runner = QkvRotaryGraph(M, K, N, dev, slots=NSETS)
+    runner.capture(xs, outs, w, s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"], cfg["seqlen"],
+                   row_offset=row_offset, repeat=4, time_gemms=True)
+    G = runner.steps
 
-    def step(i, events=None):
+    def eager_step(i):
         b = i % NSETS
-        spipe.submit(xs[b], outs[b], w, s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
-                     cfg["seqlen"], row_offset=row_offset, events=events)
+        g.quantize_tensor(xs[b], out=runner.q[b], out_scale=runner.s[b])
+        g.gemm_i8_rotary(runner.q[b], w, runner.s[b], s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
+                         cfg["seqlen"], row_offset=row_offset, out=outs[b])
+
+    def run_steps(n):
+        for _ in range(n // G):
+            runner.replay()
+        for i in range(n % G):
+            eager_step(i)
 
     def barrier():
         torch.cuda.synchronize()
@@ -550,26 +612,33 @@ def run_native(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for i in range(args.warmup):
-        step(i)
-    spipe.join()
+    run_steps(args.warmup)
     barrier()
     sampler = ClockSampler(local)
     sampler.sample()
     sampler.start()
-    n_ev = min(args.steps, 512)
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_ev)]
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
-    for i in range(args.steps):
-        step(i, evs[i] if i < n_ev else None)
-    spipe.join()                                     # the timing stream (and t1) waits for the last GEMM
+    run_steps(args.steps)
     t1.record()
     barrier()
     sampler.sample()
     sampler.stop_flag = True
-    gemm_ms = [a.elapsed_time(b) for a, b in evs]
     ms_step = max_over_ranks(t0.elapsed_time(t1)) / args.steps
+    # duration of the GEMM launches inside the timed region: the events captured around each GEMM of the graph hold
+    # the times of the region's last replay (twelve launches); with fewer steps than a replay, eager launches are timed
+    if args.steps >= G:
+        gemm_ms = [a.elapsed_time(b) for a, b in runner.gemm_events]
+    else:
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(args.steps, 1))]
+        for i, (ea_, eb_) in enumerate(evs):
+            b = i % NSETS
+            ea_.record()
+            g.gemm_i8_rotary(runner.q[b], w, runner.s[b], s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
+                             cfg["seqlen"], row_offset=row_offset, out=outs[b])
+            eb_.record()
+        torch.cuda.synchronize()
+        gemm_ms = [a.elapsed_time(b) for a, b in evs]
     st = g.device_status()
     if st[0] != 0:
         raise RuntimeError(f"device status word reports a timed-out wait: {st}")
@@ -577,12 +646,10 @@ def run_native(args):
     # ---- the same step repeated for over a second: what the GPU sustains once power and clocks have settled ----
     sus_sampler = ClockSampler(local)
     sus_sampler.start()
-    n_sus = max(200, int(1.2e3 / max(ms_step, 1e-3)))
+    n_sus = max(20, int(1.2e3 / max(ms_step, 1e-3)) // G) * G
     s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
     s0.record()
-    for i in range(n_sus):
-        step(i)
-    spipe.join()
+    run_steps(n_sus)
     s1.record()
     barrier()
     sus_sampler.sample()
@@ -599,7 +666,7 @@ def run_native(args):
         if i == 3:
             ea.record()
         b = i % NSETS
-        g.gemm_i8_rotary(spipe.q[b], w, spipe.s[b], s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
+        g.gemm_i8_rotary(runner.q[b], w, runner.s[b], s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
                          cfg["seqlen"], row_offset=row_offset, out=outs[b])
     eb.record()
     torch.cuda.synchronize()
@@ -634,7 +701,7 @@ def run_native(args):
 
     # ---- every other kernel and chain of the five configurations, the tensor-peak probe, host time per call ----
     hbm_peak, bf16_peak, which = peaks()
-    del xs, outs, pipe, out_host
+    del xs, outs, pipe, out_host, runner
     torch.cuda.empty_cache()
     DEV = f"cuda:{local}"
     probe = tensor_peak_probe(g)
@@ -677,7 +744,7 @@ def run_native(args):
         "config": {"workload": WORKLOAD,
                    "M_per_gpu": M, "N": N, "K": K, "parallelism": f"row-sharded x{world}, no collective",
                    "l2": f"{NSETS} rotating buffer sets of 302 MB (> 126 MB L2)",
-                   "streams": "devpipe.QkvRotaryStreamPipeline: quantiser of step i+1 on a second stream beside the GEMM of step i"},
+                   "launch": "devpipe.QkvRotaryGraph: the steps are captured into a CUDA graph (12 steps per replay, one stream) and replayed"},
         "tokens_per_s": world * M / (ms_step * 1e-3),
         "kernel_tops": {"qkv_rotary_gemm": gemm_tops,
                         "frac_of_nominal_4500": gemm_tops / NOMINAL_TENSOR_TOPS,
@@ -688,7 +755,7 @@ def run_native(args):
                      "frac": achieved / hbm_peak, "traffic": GEMM_DRAM_TRAFFIC, "peak_source": which,
                      "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS,
                      "kernel": "gemm_tcgen05_kernel<i8, rotary>", "bytes_per_launch": gemm_bytes,
-                     "timed": "CUDA events around each GEMM launch of the timed region, on the GEMM's stream, the next step's quantiser running beside it",
+                     "timed": "CUDA events captured around each GEMM launch of the step graph, on the launching stream: the 12 launches of the timed region's last replay",
                      "achieved_alone": gemm_bytes / (gemm_alone_ms * 1e-3) / 1e9,
                      "frac_alone": gemm_bytes / (gemm_alone_ms * 1e-3) / 1e9 / hbm_peak},
         "e2e": {"value": world * ops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,

@@ -763,9 +763,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                 __syncwarp();
               }
             };
+            uint4 held[2];                       // direct stores: the even piece of a 32-byte sector waits for the odd one
             auto put = [&](int which, int n, int piece, uint4 o) {
               if constexpr (DIRECT) {
-                if (row_ok && n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(drow0 + n + piece * 8) = o;
+                if ((piece & 1) == 0) { held[which] = o; }
+                else if (row_ok) {
+                  __half* dst = drow0 + n + (piece - 1) * 8;
+                  if (n + piece * 8 + 8 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) stg_v8(dst, held[which], o);
+                  else {
+                    if (n + piece * 8 <= p.N) *reinterpret_cast<uint4*>(dst) = held[which];
+                    if (n + piece * 8 + 8 <= p.N) *reinterpret_cast<uint4*>(dst + 8) = o;
+                  }
+                }
               } else {
                 *reinterpret_cast<uint4*>(out_buf + (lane < 16 ? buf_a : buf_b) * OUT_BUF_BYTES + stg_off[which * 4 + piece]) = o;
               }

@@ -23,6 +23,16 @@
 
 namespace gsb {
 
+#ifdef GSB200_LSTM_PROF
+// Tuning aid (never in the shipped library): SM clock stamps of one step of CTA 0, threads 0 and 128.
+__device__ long long g_lstm_prof[2][16];
+#define LPROF(slot) do { if (blockIdx.x == 0 && s == 100 && (tid == 0 || tid == 128)) g_lstm_prof[tid == 128][slot] = clock64(); } while (0)
+#define LPROF2(who, slot) do { if (blockIdx.x == 0 && (s == 100 || s == 101)) g_lstm_prof[who][(slot) + 8 * (s - 100)] = clock64(); } while (0)
+#else
+#define LPROF(slot) do { } while (0)
+#define LPROF2(who, slot) do { } while (0)
+#endif
+
 constexpr int LSTM_THREADS = 256;            // 8 warps: all load / do gate math; warp 0 lane 0 also issues TMA + MMA
 constexpr int LSTMC_MMA_TID = 128;           // cluster kernel: the thread (lane 0 of warp 4) that issues the MMAs
 constexpr int LSTMC_IH_TID = 0;              // cluster kernel: the thread that issues the TMA loads of the ih tiles (on a thread of warp 7 the step is 12 % slower)
@@ -426,10 +436,12 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   for (int s = 0; s < p.T; ++s) {
     if (abort_flag.get() || !ok) break;
+    LPROF(0);
     // ---- 2. gate math on this thread's row ---------------------------------------------------------------------
     ok = mbar_wait(&ih_full[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20, budget) &&
          mbar_wait(mma_done, s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30, budget);
     ok = __all_sync(0xffffffffu, ok);
+    LPROF(1);
     if (ok) {
       tc_fence_after();
       uint32_t acc[4][16];
@@ -437,6 +449,7 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
       for (int g = 0; g < 4; ++g) tmem_ld_32x32b_x16(t_row + g * LSTM_HS + half * 16, acc[g]);
       tmem_ld_wait(acc[0], acc[1], acc[2], acc[3]);
+      LPROF(2);
       const uint8_t* ihb = ih_s + (s & 1) * LSTM_IH_BYTES;
       float hv[16];
 #pragma unroll
@@ -471,19 +484,24 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(hv[4 * i + 2] * 448.f, hv[4 * i + 3] * 448.f), __NV_SATFINITE, __NV_E4M3);
         w8[i] = lo | (hi << 16);
       }
+      LPROF(3);
       // ---- 3. stage this CTA's piece of h_s (K chunk `half`, 16 bytes per row) ...
       uint8_t* stg = stg_s + (s & 1) * LSTMC_PIECE;
       *reinterpret_cast<uint4*>(stg + half * LSTMC_CHUNK + r_loc * 16) =
           row_ok ? make_uint4(w8[0], w8[1], w8[2], w8[3]) : make_uint4(0, 0, 0, 0);
+      LPROF(4);
       fence_proxy_async_smem();                       // generic-proxy staging stores before the bulk copies read them
       tc_fence_before();
       __syncthreads();
+      LPROF(5);
       // ---- 4. ... and send it into buffer s & 1 of every CTA of the row group, one bulk copy each --------------
       if (s + 1 < p.T && tid < p.slices) {
         const uint32_t dst = mapa_shared(smem_u32(h_s + (s & 1) * LSTMC_HBUF + slc * LSTMC_PIECE), (uint32_t)tid);
         bulk_copy_to_cluster(dst, stg, LSTMC_PIECE, mapa_shared(smem_u32(&h_ready[s & 1]), (uint32_t)tid));
       }
+      LPROF(6);
       if (tid == LSTMC_IH_TID && s + 2 < p.T) issue_ih(s + 2);
+      LPROF(7);
       // ---- 5. the layer's outputs ------------------------------------------------------------------------------------
       if (row_ok) {
         const size_t toff = (size_t)step_t(s) * B * H + (size_t)row * H + my_col;
@@ -496,13 +514,16 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           *reinterpret_cast<uint4*>(p.h_out + toff + 8) = make_uint4(w16[4], w16[5], w16[6], w16[7]);
         }
       }
+      LPROF(8);
       // ---- 6. the next step's MMAs: the tile of h_s (buffer s & 1) is complete once every slice has arrived ---------
       if (tid == LSTMC_MMA_TID && s + 1 < p.T) {
         const bool got = mbar_wait_cluster(&h_ready[s & 1], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x40, budget);
+        LPROF(9);
         if (got) {
           // arm this buffer's next use: h_{s+2} arrives in it if there is a step s + 3
           if (s + 3 < p.T) mbar_arrive_expect_tx(&h_ready[s & 1], p.slices * LSTMC_PIECE);
           issue_mmas(s & 1);
+          LPROF(10);
         } else {
           abort_flag.set(1);
         }
@@ -520,6 +541,312 @@ lstm_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_before();
   __syncthreads();
   if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, LSTM_NCOL); }
+  cluster_sync_all();                    // nobody leaves while another CTA of the cluster may still store into it
+}
+
+// ---- cluster form, two interleaved 64-row halves per CTA -----------------------------------------------------------
+// The step of the kernel above is one serial chain per CTA: gather h (about 1700 clocks from the CTA barrier until the
+// last slice's piece has crossed the cluster), issue the MMAs (about 100 clocks each), wait for the accumulator, gate
+// math, stage, barrier, send.  Nothing in it is busy for long; it is latency end to end.  Here a CTA still owns 128
+// batch rows x 32 hidden units, but as TWO independent halves of 64 rows that take turns: while the pieces of one half
+// are in flight and its MMAs run, the eight compute warps do the gate math of the other half.  What makes that work:
+//  * M = 64 MMAs.  Their accumulator sits in the lower 16 lanes of each TMEM lane quarter, and tcgen05.ld.16x256b hands
+//    a warp 16 rows x 16 columns as 2 rows x (2 + 2) column pairs per thread, so all 256 compute threads share a half's
+//    64 x 128 gate values evenly: 8 cells each (2 rows x 4 hidden units, all four gates of a cell in one thread).
+//  * a ninth warp that only issues MMAs (and the TMA loads of the ih tiles), so no compute thread ever waits for a gather;
+//  * one mbarrier per (half, buffer, source slice): the K step that reads slice k's 32 bytes of h is issued as soon as
+//    that slice's piece has landed, so the MMA issue overlaps the gather instead of following it.
+// The outputs leave through the staged images of the piece (whole 32-byte / 64-byte runs per row, written by
+// cooperating threads) instead of 16-byte slivers per row.  Arithmetic per cell is that of the other two kernels (a test
+// holds all three to the same bytes).
+constexpr int L64_ROWS = 64;
+constexpr int L2_THREADS = 320;                                // 8 compute warps + the MMA warp + the send warp
+constexpr int L2_COMPUTE = 256;
+constexpr int L64_CHUNK = L64_ROWS * 16;                       // one 16-byte K chunk of all 64 rows
+constexpr int L64_PIECE = L64_ROWS * LSTM_HS;                  // 2 KiB: this CTA's piece of a half's h (two chunks = one K step)
+constexpr int L64_HBUF = LSTMC_MAX_KB * 8 * L64_CHUNK;         // 24 KiB: a half's 64 x 384 tile of h as 24 chunks
+constexpr int L64_IH_GATE = L64_ROWS * LSTM_HS * 2;            // 4 KiB: one gate's 64 x 32 fp16 box
+constexpr int L64_IH_BYTES = 4 * L64_IH_GATE;                  // 16 KiB
+constexpr int L64_H16_BYTES = L64_ROWS * LSTM_HS * 2;          // 4 KiB: fp16 image of the piece (layer output)
+constexpr int L2_MAX_SLICES = 12;
+constexpr int L2_SMEM_W = 0;
+constexpr int L2_SMEM_H = L2_SMEM_W + LSTMC_MAX_KB * LSTM_KB_BYTES;          // [half][buffer]
+constexpr int L2_SMEM_IH = L2_SMEM_H + 4 * L64_HBUF;                         // [half][buffer]
+constexpr int L2_SMEM_STG = L2_SMEM_IH + 4 * L64_IH_BYTES;                   // [half][buffer]
+constexpr int L2_SMEM_H16 = L2_SMEM_STG + 4 * L64_PIECE;                     // [half]
+constexpr int L2_SMEM_SC = L2_SMEM_H16 + 2 * L64_H16_BYTES;
+constexpr int L2_SMEM_BAR = L2_SMEM_SC + 1024;
+constexpr int L2_SMEM_USED = L2_SMEM_BAR + 512;
+constexpr int L2_SMEM_BYTES = L2_SMEM_USED + 1024;
+static_assert(L2_SMEM_BYTES <= 227 * 1024 && L2_SMEM_BYTES > 116 * 1024, "one CTA per SM");
+
+__global__ void __launch_bounds__(L2_THREADS, 1)
+lstm_cluster2_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_ih,
+                     const LstmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* w_s = smem + L2_SMEM_W;
+  uint8_t* h_s = smem + L2_SMEM_H;                 // + (2 * half + buffer) * L64_HBUF
+  uint8_t* ih_s = smem + L2_SMEM_IH;               // + (2 * half + buffer) * L64_IH_BYTES
+  uint8_t* stg_s = smem + L2_SMEM_STG;             // + (2 * half + buffer) * L64_PIECE
+  uint8_t* h16_base = smem + L2_SMEM_H16;          // + half * L64_H16_BYTES
+  float* sc_s = reinterpret_cast<float*>(smem + L2_SMEM_SC);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L2_SMEM_BAR);
+  uint64_t* w_full = bars;
+  uint64_t* ih_full = bars + 1;                    // [half][buffer]
+  uint64_t* mma_done = bars + 5;                   // [half]
+  uint64_t* staged = bars + 7;                     // [half]: this CTA's piece of the step's h is staged, the send warp may copy it
+  uint64_t* h_ready = bars + 9;                    // [half][buffer]: every slice's piece of h has landed (bytes counted)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = blockIdx.x / p.slices;        // 128-row group = cluster
+  const int slc = blockIdx.x % p.slices;        // hidden slice = rank inside the cluster
+  const int row0 = grp * LSTM_ROWS;
+  const int hid0 = slc * LSTM_HS;
+  const int H = p.H, B = p.B;
+  const int halves = (B - row0 > L64_ROWS) ? 2 : 1;     // the last group may have rows for one half only
+
+  if (tid == 0) {
+    mbar_init(w_full, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&ih_full[i], 1);
+    mbar_init(&mma_done[0], 1); mbar_init(&mma_done[1], 1);
+    mbar_init(&staged[0], 1); mbar_init(&staged[1], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&h_ready[i], 1);
+    // arm the first use of each tile barrier: h_0 arrives in buffer 0 (if there is a step 1), h_1 in buffer 1
+    for (int hf = 0; hf < halves; ++hf) {
+      if (p.T > 1) mbar_arrive_expect_tx(&h_ready[2 * hf + 0], p.slices * L64_PIECE);
+      if (p.T > 2) mbar_arrive_expect_tx(&h_ready[2 * hf + 1], p.slices * L64_PIECE);
+    }
+    abort_flag.set(0);
+    fence_mbar_init();
+    prefetch_tmap(&tm_w); prefetch_tmap(&tm_ih);
+  }
+  if (warp == 8) { tmem_alloc(tmem_slot, 2 * LSTM_NCOL); tmem_relinquish(); }
+  if (tid < LSTM_NCOL) {
+    const int n = (tid >> 5) * H + hid0 + (tid & 31);
+    sc_s[tid] = __ldg(p.s_hh + n) * (1.0f / 448.0f);
+    sc_s[LSTM_NCOL + tid] = p.bias ? __ldg(p.bias + n) : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  cluster_sync_all();                    // every CTA's barriers exist (and are armed) before anyone sends to them
+  const uint32_t tmem_base = *tmem_slot;
+  const unsigned int budget = spin_budget();
+  const bool rank_ok = cluster_ctarank() == (uint32_t)slc;
+  if (!rank_ok && tid == 0) { abort_flag.set(1); atomicOr(&g_status[0], ST_TIMEOUT_LSTM); g_status[1] = 0x50; }
+
+  auto step_t = [&](int s) { return p.reverse ? p.T - 1 - s : s; };
+  auto issue_ih = [&](int hf, int s) {     // one thread: TMA the four gate boxes of step s, half hf
+    const int ib = 2 * hf + (s & 1);
+    uint8_t* dst = ih_s + ib * L64_IH_BYTES;
+    mbar_arrive_expect_tx(&ih_full[ib], L64_IH_BYTES);
+    const int r = step_t(s) * B + row0 + hf * L64_ROWS;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) tma_load_2d(dst + g * L64_IH_GATE, &tm_ih, &ih_full[ib], g * H + hid0, r);
+  };
+
+  // this thread's cells of a half (compute warps): rows ra and ra + 8, hidden units u0 + {0, 1} and u0 + 8 + {0, 1} of
+  // the slice; cell index = 4 * k + 2 * rowsel + j, the order in which tcgen05.ld.16x256b.x2 delivers them
+  const int q = warp & 3, hh = (warp >> 2) & 1;
+  const int ra = 16 * q + (lane >> 2);
+  const int u0 = 16 * hh + 2 * (lane & 3);
+  auto cell_row = [&](int i) { return ra + ((i >> 1) & 1) * 8; };
+  auto cell_u = [&](int i) { return u0 + (i >> 2) * 8 + (i & 1); };
+  float c[2][8];
+  float2 sc2[4][2], bi2[4][2];
+  int ih_off[4];
+  if (warp >= 8) {
+    if (warp == 8 && lane == 0) {         // W slice and the first two ih tiles of each half
+      mbar_arrive_expect_tx(w_full, p.k_blocks * LSTM_KB_BYTES);
+      for (int kb = 0; kb < p.k_blocks; ++kb)
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          tma_load_2d(w_s + kb * LSTM_KB_BYTES + g * (LSTM_HS * 128), &tm_w, w_full, kb * 128, g * H + hid0);
+      for (int hf = 0; hf < halves; ++hf) { issue_ih(hf, 0); if (p.T > 1) issue_ih(hf, 1); }
+    }
+  } else {
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = row0 + hf * L64_ROWS + cell_row(i);
+        c[hf][i] = (p.c0 && row < B) ? __half2float(p.c0[(long long)row * H + hid0 + cell_u(i)]) : 0.f;
+      }
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int col = g * LSTM_HS + u0 + 8 * k;
+        sc2[g][k] = make_float2(sc_s[col], sc_s[col + 1]);
+        bi2[g][k] = make_float2(sc_s[LSTM_NCOL + col], sc_s[LSTM_NCOL + col + 1]);
+      }
+    // byte offsets of this thread's ih values inside a gate box (64-byte swizzle): one half2 per (k, rowsel)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = i >> 1, row = ra + (i & 1) * 8;
+      ih_off[i] = row * 64 + (((2 * hh + k) ^ ((row >> 1) & 3)) << 4) + 4 * (lane & 3);
+    }
+    // step 0 reads h_0 (or zeros) from buffer 1 of each half, staged by this CTA's own compute threads
+    const int chunks_per_row = H >> 4;
+    for (int hf = 0; hf < halves; ++hf)
+      for (int id = tid; id < L64_ROWS * chunks_per_row; id += L2_COMPUTE) {
+        const int r = id / chunks_per_row, cc = id % chunks_per_row;
+        const int row = row0 + hf * L64_ROWS + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (p.h0 && row < B) v = __ldcg(reinterpret_cast<const uint4*>(p.h0 + (size_t)row * H + cc * 16));
+        *reinterpret_cast<uint4*>(h_s + (2 * hf + 1) * L64_HBUF + cc * L64_CHUNK + r * 16) = v;
+      }
+    fence_proxy_async_smem();
+  }
+  __syncthreads();                       // h_0 is staged before the first MMAs read it
+
+  if (warp == 8) {
+    // ------------------------------ MMA warp: one thread issues the MMAs and the ih loads ------------------------------
+    if (lane == 0) {
+      bool ok = rank_ok && mbar_wait(w_full, 0, abort_flag, ST_TIMEOUT_LSTM, 0x10, budget);
+      constexpr uint32_t idesc = umma_idesc(1, 0, 0, L64_ROWS, LSTM_NCOL);
+      const uint64_t b_base = umma_smem_desc_sw128(smem_u32(w_s));
+      const int ksteps = H >> 5;                        // one K step (32 bytes of h) per hidden slice
+      for (int s = 0; ok && s < p.T; ++s) {
+        for (int hf = 0; ok && hf < halves; ++hf) {
+          // gates of step s, half hf: h_{s-1} sits in buffer (s + 1) & 1 (step 0: h_0 or zeros, staged locally)
+          LPROF2(1, 4 * hf + 0);
+          const int hb = 2 * hf + ((s + 1) & 1);
+          const uint64_t a_desc = umma_smem_desc_kchunks(smem_u32(h_s + hb * L64_HBUF), L64_CHUNK);
+          if (s > 0) {
+            if (!mbar_wait_cluster(&h_ready[hb], (uint32_t)((s - 1) >> 1) & 1u, abort_flag, ST_TIMEOUT_LSTM, 0x40, budget)) { ok = false; break; }
+            if (s + 2 < p.T) mbar_arrive_expect_tx(&h_ready[hb], p.slices * L64_PIECE);   // its next use: h_{s+1}, read by step s + 2
+          }
+          for (int ks = 0; ks < ksteps; ++ks) {
+            if (ks == 0) { tc_fence_after(); LPROF2(1, 4 * hf + 1); }
+            umma_f8(tmem_base + hf * LSTM_NCOL, a_desc + (uint64_t)(ks * (2 * L64_CHUNK >> 4)),
+                    b_base + (uint64_t)((ks >> 2) * (LSTM_KB_BYTES >> 4) + 2 * (ks & 3)), idesc, ks != 0);
+          }
+          if (!ok) break;
+          LPROF2(1, 4 * hf + 2);
+          umma_commit(&mma_done[hf]);
+          // every slice's piece of h_{s-1} is here, our own included, and that one was sent after the compute warps'
+          // barrier of step s - 1: the ih tile of step s - 1 has been consumed and its buffer can take step s + 1
+          if (s > 0 && s + 1 < p.T) issue_ih(hf, s + 1);
+          LPROF2(1, 4 * hf + 3);
+        }
+      }
+      if (!ok) abort_flag.set(1);
+    }
+  } else if (warp == 9) {
+    // ------------------------------ send warp: the all-gather of h through distributed shared memory ------------------------------
+    // One bulk copy per destination CTA (lane = destination rank), issued when the compute warps have staged the piece;
+    // its bytes are counted by the destination's barrier of that half and buffer.  A copy costs the SM about 220 clocks,
+    // one after the other whichever threads issue them: twelve are ~2700 clocks, which no compute warp pays here and
+    // which pass while the other half is computed.
+    for (int s = 0; s + 1 < p.T; ++s) {
+      bool ok = true;
+      for (int hf = 0; hf < halves; ++hf) {
+        const int ib = 2 * hf + (s & 1);
+        ok = mbar_wait(&staged[hf], s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x60, budget);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane < p.slices) {
+          const uint32_t dst = mapa_shared(smem_u32(h_s + ib * L64_HBUF + slc * L64_PIECE), (uint32_t)lane);
+          bulk_copy_to_cluster(dst, stg_s + ib * L64_PIECE, L64_PIECE, mapa_shared(smem_u32(&h_ready[ib]), (uint32_t)lane));
+        }
+      }
+      if (!ok) break;
+    }
+  } else {
+    // ------------------------------ compute warps: the halves take turns ------------------------------
+    bool ok = true;
+    for (int s = 0; ok && s < p.T; ++s) {
+      for (int hf = 0; hf < halves; ++hf) {
+        if (tid == 0) LPROF2(0, 4 * hf + 0);
+        const int ib = 2 * hf + (s & 1);
+        bool mine = mbar_wait(&ih_full[ib], (s >> 1) & 1, abort_flag, ST_TIMEOUT_LSTM, 0x20, budget) &&
+                    mbar_wait(&mma_done[hf], s & 1, abort_flag, ST_TIMEOUT_LSTM, 0x30, budget);
+        mine = __all_sync(0xffffffffu, mine);
+        uint8_t* stg = stg_s + ib * L64_PIECE;
+        uint8_t* h16_s = h16_base + (halves == 2 ? hf : (s & 1)) * L64_H16_BYTES;
+        if (tid == 0) LPROF2(0, 4 * hf + 1);
+        if (mine) {
+          tc_fence_after();
+          uint32_t acc[4][8];
+          const uint32_t t_row = tmem_base + hf * LSTM_NCOL + ((uint32_t)(q * 32) << 16);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) tmem_ld_16x256b_x2(t_row + g * LSTM_HS + hh * 16, acc[g]);
+          tmem_ld_wait(acc[0], acc[1], acc[2], acc[3]);
+          const uint8_t* ihb = ih_s + ib * L64_IH_BYTES;
+          float hv[8];
+#pragma unroll
+          for (int kr = 0; kr < 4; ++kr) {              // (k, rowsel): two adjacent hidden units of one row
+            const int k = kr >> 1, rs = kr & 1;
+            float pre[4][2];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(ihb + g * L64_IH_GATE + ih_off[kr]));
+              pre[g][0] = fmaf(__uint_as_float(acc[g][4 * k + 2 * rs + 0]), sc2[g][k].x, f.x + bi2[g][k].x);
+              pre[g][1] = fmaf(__uint_as_float(acc[g][4 * k + 2 * rs + 1]), sc2[g][k].y, f.y + bi2[g][k].y);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int i = 4 * k + 2 * rs + j;
+              const float ig = sigmoid_f(pre[0][j]), fg = sigmoid_f(pre[1][j]), gg = tanh_f(pre[2][j]), og = sigmoid_f(pre[3][j]);
+              const float cprev = hf ? c[1][i] : c[0][i];
+              const float cn = fmaf(fg, cprev, ig * gg);
+              hv[i] = og * tanh_f(cn);
+              const float cr = __half2float(__float2half_rn(cn));       // the cell state is carried in fp16
+              if (hf) c[1][i] = cr; else c[0][i] = cr;
+            }
+          }
+          // stage this thread's bytes of the CTA's piece: chunk hh, 2 bytes per (k, rowsel); rows past the batch as zeros
+#pragma unroll
+          for (int kr = 0; kr < 4; ++kr) {
+            const int k = kr >> 1, rs = kr & 1, i = 4 * k + 2 * rs;
+            const int r = ra + rs * 8;
+            const bool live = row0 + hf * L64_ROWS + r < B;
+            const uint32_t b2 = live ? (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(hv[i] * 448.f, hv[i + 1] * 448.f), __NV_SATFINITE, __NV_E4M3) : 0u;
+            *reinterpret_cast<uint16_t*>(stg + hh * L64_CHUNK + r * 16 + 8 * k + 2 * (lane & 3)) = (uint16_t)b2;
+            if (p.h_out)    // fp16 image: rows of 64 bytes, 16-byte pieces XOR-swizzled by the row pair like the ih boxes
+              *reinterpret_cast<uint32_t*>(h16_s + r * 64 + (((2 * hh + k) ^ ((r >> 1) & 3)) << 4) + 4 * (lane & 3)) = pack_half2(hv[i], hv[i + 1]);
+          }
+          fence_proxy_async_smem();                     // the staging stores before the bulk copies read them
+        }
+        tc_fence_before();
+        if (tid == 0) LPROF2(0, 4 * hf + 2);
+        ok = named_barrier_and(1, L2_COMPUTE, mine) != 0;    // all compute warps go on, or all leave, together
+        if (tid == 0) LPROF2(0, 4 * hf + 3);
+        if (!ok) break;
+        if (tid == 0 && s + 1 < p.T) mbar_arrive(&staged[hf]);   // the send warp takes it from here
+        // the layer's outputs, from the staged images: whole 32-byte (E4M3) / 64-byte (fp16) runs per row
+        const size_t trow = (size_t)step_t(s) * B + row0 + hf * L64_ROWS;
+        const int rows_live = B - (row0 + hf * L64_ROWS);
+        if (p.h8_out && tid >= 128) {                   // (the upper compute warps: the lower ones issue the sends)
+          const int r = (tid - 128) >> 1, cch = tid & 1;
+          if (r < rows_live)
+            *reinterpret_cast<uint4*>(p.h8_out + (trow + r) * H + hid0 + 16 * cch) = *reinterpret_cast<const uint4*>(stg + cch * L64_CHUNK + r * 16);
+        }
+        if (p.h_out) {
+          const int r = tid >> 2, pc = tid & 3;
+          if (r < rows_live)
+            *reinterpret_cast<uint4*>(p.h_out + (trow + r) * H + hid0 + 8 * pc) =
+                *reinterpret_cast<const uint4*>(h16_s + r * 64 + ((pc ^ ((r >> 1) & 3)) << 4));
+        }
+      }
+    }
+    if (p.c_last) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = row0 + hf * L64_ROWS + cell_row(i);
+          if (hf < halves && row < B) p.c_last[(long long)row * H + hid0 + cell_u(i)] = __float2half_rn(c[hf][i]);
+        }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * LSTM_NCOL); }
   cluster_sync_all();                    // nobody leaves while another CTA of the cluster may still store into it
 }
 
@@ -579,49 +906,65 @@ int32_t launch_lstm_layer(const LstmLayerArgs& a, void* scratch, size_t scratch_
       !tmap_2d(&tih, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.ih, (uint64_t)a.T * a.B, (uint64_t)4 * a.H,
                (uint64_t)a.ld_ih, LSTM_HS, LSTM_ROWS, CU_TENSOR_MAP_SWIZZLE_64B))
     return GSB200_ERR_BAD_ARG;
-  // Cluster form first (h exchanged through distributed shared memory): H <= 384, the slices of a row group in one
-  // cluster of H / 32 CTAs (more than 8 needs the non-portable cluster size).  GSB200_LSTM_NO_CLUSTER=1 in the
-  // environment, or a device that cannot host a cluster of that size, selects the cooperative kernel with global
-  // scratch.  What the device can host is asked once per (device, cluster size); a refusal is reported on stderr
-  // once and only switches off that cluster size.
-  static std::atomic<int> no_cluster{-1};
-  int nc = no_cluster.load(std::memory_order_relaxed);
-  if (nc < 0) {
-    const char* ev = getenv("GSB200_LSTM_NO_CLUSTER");
-    nc = (ev && ev[0] == '1') ? 1 : 0;
-    no_cluster.store(nc, std::memory_order_relaxed);
+  // Cluster forms first (h exchanged through distributed shared memory): H <= 384, the slices of a 128-row group in one
+  // cluster of H / 32 CTAs (more than 8 needs the non-portable cluster size).  The default runs a CTA's rows as two
+  // interleaved 64-row halves.  In the environment, GSB200_LSTM_ROWS128=1 selects the older cluster kernel (one
+  // 128-row tile per CTA, a thread per row) and GSB200_LSTM_NO_CLUSTER=1 the cooperative kernel with global scratch; a
+  // device that cannot host a cluster of that size falls back the same way.  What the device can host is asked once per
+  // (device, kernel, cluster size); a refusal is reported on stderr once and only switches off that combination.
+  static std::atomic<int> env_state{-1};
+  int env = env_state.load(std::memory_order_relaxed);
+  if (env < 0) {
+    const char* e1 = getenv("GSB200_LSTM_NO_CLUSTER");
+    const char* e2 = getenv("GSB200_LSTM_ROWS128");
+    env = ((e1 && e1[0] == '1') ? 1 : 0) | ((e2 && e2[0] == '1') ? 2 : 0);
+    env_state.store(env, std::memory_order_relaxed);
   }
-  if (!nc && p.k_blocks <= LSTMC_MAX_KB && slices <= 16) {
-    static std::atomic<int> cluster_state[64][17];          // per (device, cluster size): 0 unknown, 1 usable, -1 not
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(LSTM_THREADS);
-    cfg.dynamicSmemBytes = LSTMC_SMEM_BYTES; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = slices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    int state = cluster_state[dev][slices].load(std::memory_order_acquire);
-    if (state == 0) {
-      cudaError_t ce = cudaFuncSetAttribute(lstm_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, LSTMC_SMEM_BYTES);
-      if (ce == cudaSuccess && slices > 8)
-        ce = cudaFuncSetAttribute(lstm_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-      int max_clusters = 0;
-      if (ce == cudaSuccess) ce = cudaOccupancyMaxActiveClusters(&max_clusters, lstm_cluster_kernel, &cfg);
-      state = (ce == cudaSuccess && max_clusters >= 1) ? 1 : -1;
-      if (state < 0) {
-        cudaGetLastError();
-        fprintf(stderr, "gigaslop_b200: device %d cannot host a cluster of %d LSTM CTAs (%s); using the cooperative kernel\n",
-                dev, slices, ce == cudaSuccess ? "no active cluster fits" : cudaGetErrorName(ce));
+  if (!(env & 1) && p.k_blocks <= LSTMC_MAX_KB && slices <= 16) {
+    static std::atomic<int> cluster_state[2][64][17];       // [64-row form][device][cluster size]: 0 unknown, 1 usable, -1 not
+    auto try_cluster = [&](bool rows64, int cgrid, const CUtensorMap& tih_k) -> bool {
+      void (*kern)(const CUtensorMap, const CUtensorMap, const LstmParams) = rows64 ? lstm_cluster2_kernel : lstm_cluster_kernel;
+      const int smem_bytes = rows64 ? L2_SMEM_BYTES : LSTMC_SMEM_BYTES;
+      cudaLaunchConfig_t cfg{};
+      cfg.gridDim = dim3(cgrid); cfg.blockDim = dim3(rows64 ? L2_THREADS : LSTM_THREADS);
+      cfg.dynamicSmemBytes = smem_bytes; cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = slices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr; cfg.numAttrs = 1;
+      std::atomic<int>& slot = cluster_state[rows64 ? 1 : 0][dev][slices];
+      int state = slot.load(std::memory_order_acquire);
+      if (state == 0) {
+        cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (ce == cudaSuccess && slices > 8) ce = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        int max_clusters = 0;
+        if (ce == cudaSuccess) ce = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+        state = (ce == cudaSuccess && max_clusters >= 1) ? 1 : -1;
+        if (getenv("GSB200_LSTM_VERBOSE"))
+          fprintf(stderr, "gigaslop_b200: LSTM cluster form (%s), cluster of %d: %d clusters can be resident (%d CTAs asked)\n",
+                  rows64 ? "two 64-row halves" : "128-row tile", slices, max_clusters, cgrid);
+        if (state < 0) {
+          cudaGetLastError();
+          fprintf(stderr, "gigaslop_b200: device %d cannot host a cluster of %d LSTM CTAs (%s: %s)\n", dev, slices,
+                  rows64 ? "two 64-row halves" : "128-row tile", ce == cudaSuccess ? "no active cluster fits" : cudaGetErrorName(ce));
+        }
+        slot.store(state, std::memory_order_release);
       }
-      cluster_state[dev][slices].store(state, std::memory_order_release);
+      if (state != 1) return false;
+      cudaError_t ce = cudaLaunchKernelEx(&cfg, kern, tw, tih_k, p);
+      if (ce == cudaSuccess) return true;
+      cudaGetLastError();
+      fprintf(stderr, "gigaslop_b200: cluster launch of the LSTM layer failed (%s); trying the next form\n", cudaGetErrorName(ce));
+      return false;
+    };
+    if (!(env & 2) && slices <= L2_MAX_SLICES) {          // two interleaved 64-row halves per CTA: ih boxes of 64 rows
+      CUtensorMap tih64;
+      if (tmap_2d(&tih64, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.ih, (uint64_t)a.T * a.B, (uint64_t)4 * a.H,
+                  (uint64_t)a.ld_ih, LSTM_HS, L64_ROWS, CU_TENSOR_MAP_SWIZZLE_64B) &&
+          try_cluster(true, grid, tih64))
+        return GSB200_OK;
     }
-    if (state == 1) {
-      cudaError_t ce = cudaLaunchKernelEx(&cfg, lstm_cluster_kernel, tw, tih, p);
-      if (ce == cudaSuccess) return GSB200_OK;
-      cudaGetLastError();                  // this launch falls through to the cooperative kernel, and says so
-      fprintf(stderr, "gigaslop_b200: cluster launch of the LSTM layer failed (%s); this call uses the cooperative kernel\n",
-              cudaGetErrorName(ce));
-    }
+    if (try_cluster(false, grid, tih)) return GSB200_OK;
   }
   // the cooperative kernel exchanges h through the scratch; its step counters start at zero
   cudaError_t e = cudaMemsetAsync(p.flags, 0, (size_t)grid * sizeof(unsigned int), st);
@@ -665,6 +1008,14 @@ int32_t launch_lstm_layer_static(const LstmLayerArgs& a, cudaStream_t st) {
   }
   return launch_lstm_layer(a, g_lstm_static_ptr[dev], LSTM_STATIC_BYTES, st);
 }
+
+#ifdef GSB200_LSTM_PROF
+}  // namespace gsb
+extern "C" int gsb200_debug_lstm_prof(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, gsb::g_lstm_prof, sizeof(long long) * 32);
+}
+namespace gsb {
+#endif
 
 // ---- the whole stack behind one call ---------------------------------------------------------------------------
 // Per layer: the hoisted input projection (FP8 GEMM over the T*B rows) and the persistent recurrence; layers

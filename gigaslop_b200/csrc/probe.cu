@@ -12,6 +12,9 @@
 
 namespace gsb {
 
+#ifndef PROBE_M
+#define PROBE_M 128   // rows of the probe's MMAs (an experiment build may set 64)
+#endif
 constexpr int PROBE_THREADS = 128;
 constexpr int PROBE_A_BYTES = 4 * 128 * 128;        // 4 A tiles of 128 rows x 128 K-bytes
 constexpr int PROBE_B_BYTES = 4 * 256 * 128;        // 4 K blocks of up to 256 rows x 128 K-bytes
@@ -39,7 +42,7 @@ __global__ void __launch_bounds__(PROBE_THREADS, 1) tensor_peak_probe_kernel(lon
   const uint32_t tm = slot;
   if (threadIdx.x == 0) {
     const uint32_t a0 = smem_u32(smem), b0 = smem_u32(smem + PROBE_A_BYTES);
-    constexpr uint32_t idesc = KIND == 0 ? umma_idesc(2, 1, 1, 128, N) : umma_idesc(1, 0, 0, 128, N);
+    constexpr uint32_t idesc = KIND == 0 ? umma_idesc(2, 1, 1, PROBE_M, N) : umma_idesc(1, 0, 0, PROBE_M, N);
     const long long t0 = clock64();
     for (int r = 0; r < mmas; ++r) {
       const int kk = r & 3, kb = (r >> 2) & 3, tile = (r >> 4) & 3;

@@ -88,6 +88,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of a phase (no suspend): for a thread that polls several barriers in turn.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// One try_wait that may keep the thread suspended for up to `ns` nanoseconds (woken early when the phase completes).
+__device__ __forceinline__ bool mbar_try_wait_ns(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Spin budget in SM clocks: read ONCE per thread at kernel start (it lives in global memory; fetching it inside a
 // wait would put an L2 round trip on every blocking hand-off).
 __device__ __forceinline__ unsigned int spin_budget() {
@@ -124,6 +149,12 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 // Address of the same shared-memory location in CTA `rank` of this cluster.
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t rank) {
   uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank)); return r;
+}
+__device__ __forceinline__ uint4 ld_cluster_v4(uint32_t cluster_addr) {
+  uint4 v;
+  asm volatile("ld.shared::cluster.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(cluster_addr) : "memory");
+  return v;
 }
 __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint4 v) {
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};"
@@ -351,6 +382,25 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 256 bit, twice (16 consecutive 32-bit columns): the layout of an M = 64 accumulator, whose 64 rows sit in
+// the lower 16 lanes of each 32-lane quarter.  Thread i of the warp gets rows i / 4 and i / 4 + 8 of its quarter's 16:
+// v[4k + 0..1] = columns col + 8k + 2 (i % 4) + {0, 1} of row i / 4, v[4k + 2..3] = the same columns of row i / 4 + 8.
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&a)[8], uint32_t (&b)[8], uint32_t (&c)[8], uint32_t (&d)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                 "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
+                 "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]), "+r"(c[4]), "+r"(c[5]), "+r"(c[6]), "+r"(c[7]),
+                 "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]), "+r"(d[4]), "+r"(d[5]), "+r"(d[6]), "+r"(d[7])
+               :: "memory");
+}
+
 // Wait for this thread's TMEM loads.  The registers the loads write are passed through the wait as read-write
 // operands: tcgen05.ld only starts the transfer, and without this tie nothing in the program text would keep a use
 // of those registers (or a copy of them made by the compiler) below the wait.
@@ -390,6 +440,12 @@ __device__ __forceinline__ float tanh_approx(float x) {
 // instead of the two (exp and reciprocal) of g / (1 + exp(-g)).  Takes h, returns silu(2h), for a pair.
 __device__ __forceinline__ float2 silu_from_half2(float2 h) {
   return __ffma2_rn(h, make_float2(tanh_approx(h.x), tanh_approx(h.y)), h);
+}
+
+// 32-byte (one full sector) global store; the address must be 32-byte aligned.
+__device__ __forceinline__ void stg_v8(void* p, uint4 a, uint4 b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
 }
 
 // ---- misc -----------------------------------------------------------------------

@@ -72,3 +72,60 @@ class QkvRotaryStreamPipeline:
         """The host waits for every batch queued so far."""
         self.join()
         torch.cuda.current_stream(self.dev).synchronize()
+
+
+class QkvRotaryGraph:
+    """The quantise + QKV-rotary step of a ring of device-resident batches, captured once into a CUDA graph.
+
+    ``capture(xs, outs, ...)`` records ``repeat`` passes over the given batches (one quantiser and one GEMM launch
+    per batch, on one stream, in order); ``replay()`` launches them all with one call.  Launched this way the two
+    kernels of a step follow each other without the gap an eager launch leaves (83 us per 65536-token step against
+    89-97 us for eager launches on one or two streams, B200).  The reference drives its per-step LSTM launches the same
+    way (fly/bench_factored_lstm.py:104-121).  Results are those of the direct calls: same kernels, same arguments.
+
+    ``gemm_events``: after a replay, pairs of CUDA events around each captured GEMM launch (``elapsed_time`` gives the
+    kernel's duration inside the step).
+    """
+
+    def __init__(self, M, K, N, device, slots=3):
+        self.M, self.K, self.N = M, K, N
+        self.dev = torch.device(device)
+        self.q = [torch.empty(M, K, dtype=torch.int8, device=self.dev) for _ in range(slots)]
+        self.s = [torch.empty(M, dtype=torch.float32, device=self.dev) for _ in range(slots)]
+        self.graph = None
+        self.gemm_events = []
+        self.steps = 0
+
+    def capture(self, xs, outs, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0, repeat=1,
+                time_gemms=False):
+        if len(xs) != len(outs) or len(xs) > len(self.q):
+            raise ValueError("one output per batch, and no more batches than slots")
+        def one(b, ev):
+            ops.quantize_tensor(xs[b], out=self.q[b], out_scale=self.s[b])
+            if ev is not None:
+                ev[0].record()
+            ops.gemm_i8_rotary(self.q[b], w, self.s[b], s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen,
+                               row_offset=row_offset, out=outs[b])
+            if ev is not None:
+                ev[1].record()
+        with torch.cuda.device(self.dev):
+            for b in range(len(xs)):                 # eager once: first-call set-up happens outside the capture
+                one(b, None)
+            torch.cuda.synchronize()
+            self.gemm_events = []
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                for r in range(repeat):
+                    for b in range(len(xs)):
+                        ev = None
+                        if time_gemms:
+                            ev = (torch.cuda.Event(enable_timing=True, external=True),
+                                  torch.cuda.Event(enable_timing=True, external=True))
+                            self.gemm_events.append(ev)
+                        one(b, ev)
+            self.steps = repeat * len(xs)
+        return self
+
+    def replay(self):
+        """Launch every captured step on the current stream."""
+        self.graph.replay()

@@ -3,7 +3,7 @@ the persistent recurrent kernel; layers alternate direction and feed each other 
 import torch
 
 from ._lib import check, lib
-from .ops import _stream
+from .ops import _on_device, _stream
 
 OUT_SCALE = 1.0 / 448.0
 
@@ -15,6 +15,7 @@ def lstm_scratch(B, H, device):
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
+@_on_device
 def lstm_layer(ih, W_hh, s_hh, T, B, bias=None, reverse=False, h0=None, c0=None, scratch=None,
                want_h16=True, want_h8=True, want_c=False):
     """Recurrent half of one layer.  ``ih`` fp16 ``[T*B, 4H]`` (row = t*B + b), ``W_hh`` E4M3 ``[4H, H]``.
@@ -65,6 +66,7 @@ def lstm_stack(x_fp8, sx, layers, T, B, reverse_first=True, workspace=None, aux_
     return h16
 
 
+@_on_device
 def lstm_layer_static(ih, W_hh, s_hh, T, B, bias=None, reverse=False, h0=None, c0=None,
                       want_h16=True, want_h8=True, want_c=False):
     """:func:`lstm_layer` for hosts that must not allocate device memory inside the library call: the kernel's

@@ -43,8 +43,9 @@ def _on_device(fn):
     current device, and ``_stream()`` then returns that device's current stream."""
     @functools.wraps(fn)
     def wrapped(*args, **kwargs):
-        dev = same_device(*[a for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor)])
-        if dev is None:
+        dev = same_device(*[a for a in args if isinstance(a, torch.Tensor)],
+                          *[a for a in kwargs.values() if isinstance(a, torch.Tensor)])
+        if dev is None or dev.index == torch.cuda.current_device():      # the common case costs no context switch
             return fn(*args, **kwargs)
         with torch.cuda.device(dev):
             return fn(*args, **kwargs)

@@ -112,10 +112,12 @@ def test_lstm_rejects_unsupported_shapes():
         g.lstm_layer(ih, W, torch.ones(4 * 48, device="cuda"), 4, 8)        # H % 32 != 0
 
 
-def test_cluster_and_cooperative_kernels_agree(tmp_path):
-    """The recurrence has two kernels: the cluster form (h exchanged through distributed shared memory, H <= 384) and
-    the cooperative form with global scratch (any H <= 512, and the fallback).  Same arithmetic, so the same bytes:
-    the cooperative form is forced in a child process through GSB200_LSTM_NO_CLUSTER=1."""
+@pytest.mark.parametrize("env_key", ["GSB200_LSTM_NO_CLUSTER", "GSB200_LSTM_ROWS128"])
+def test_cluster_and_cooperative_kernels_agree(tmp_path, env_key):
+    """The recurrence has three kernels: the cluster form on 64-row groups (the default while twice the CTAs fit the
+    GPU), the cluster form on 128-row groups (h exchanged through distributed shared memory, H <= 384) and the
+    cooperative form with global scratch (any H <= 512, and the fallback).  Same arithmetic per cell, so the same
+    bytes: the other two forms are forced in a child process through the environment."""
     import os
     import subprocess
     import sys
@@ -135,7 +137,7 @@ def test_cluster_and_cooperative_kernels_agree(tmp_path):
         "                          h0=d['h0'].cuda(), want_c=True)\n"
         "torch.save(dict(h16=h16.cpu(), h8=h8.cpu().view(torch.uint8), c=c.cpu()), %r)\n"
     ) % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), str(inp), str(out))
-    env = dict(os.environ, GSB200_LSTM_NO_CLUSTER="1")
+    env = dict(os.environ, **{env_key: "1"})
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     ref = torch.load(out)
