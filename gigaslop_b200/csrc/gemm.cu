@@ -34,7 +34,7 @@ static EncodeTiledFn encode_fn() {
 
 // 2-D row-major tensor [rows, cols] of `esz`-byte elements, row stride ld_elems, box of box_cols x box_rows.
 // A tensor map is a pure function of these arguments (it holds the address, not the data), so the last maps a
-// host thread built are kept in a small per-thread table: a caller that launches the same kernels on the same
+// host thread built are kept in a small per-thread table (set-associative): a caller that launches the same kernels on the same
 // buffers step after step -- the per-timestep LSTM wrapper, a pipeline over a ring of buffers -- encodes nothing
 // in steady state.  Per thread, so no lock and no sharing between the host threads that drive different GPUs.
 struct TmapKey {
@@ -44,19 +44,26 @@ struct TmapKey {
            box_rows == o.box_rows && dt == o.dt && esz == o.esz && swz == o.swz;
   }
 };
-constexpr int kTmapCacheSlots = 64;
+constexpr int kTmapSets = 32, kTmapWays = 4;             // 128 maps per host thread, 4-way set-associative
 struct TmapSlot { TmapKey key; CUtensorMap map; bool used; };
 static std::atomic<unsigned long long> g_tmap_encodes{0};      // encodes since load (test / benchmark hook)
 
+static inline uint64_t mix64(uint64_t x) {
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull; x ^= x >> 27; x *= 0x94D049BB133111EBull; x ^= x >> 31;
+  return x;
+}
+
 bool tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, uint64_t rows, uint64_t cols,
              uint64_t ld_elems, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swz) {
-  static thread_local TmapSlot cache[kTmapCacheSlots];
+  static thread_local TmapSlot cache[kTmapSets][kTmapWays];
+  static thread_local unsigned victim[kTmapSets];
   const TmapKey key{base, rows, cols, ld_elems, box_cols, box_rows, (int)dt, esz, (int)swz};
-  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
-  h = (h ^ (rows * 0x9E3779B97F4A7C15ull) ^ (cols << 17) ^ (ld_elems << 29) ^ ((uint64_t)box_rows << 41) ^
-       ((uint64_t)box_cols << 47) ^ ((uint64_t)dt << 53)) * 0xD6E8FEB86659FD93ull;
-  TmapSlot& slot = cache[(h >> 40) % kTmapCacheSlots];
-  if (slot.used && slot.key == key) { *m = slot.map; return true; }
+  uint64_t h = mix64(reinterpret_cast<uintptr_t>(base));
+  h = mix64(h ^ (rows * 0x9E3779B97F4A7C15ull) ^ (cols << 21) ^ (ld_elems << 42));
+  h = mix64(h ^ ((uint64_t)box_rows << 8) ^ ((uint64_t)box_cols << 24) ^ ((uint64_t)dt << 40) ^ ((uint64_t)swz << 48));
+  TmapSlot* set = cache[h % kTmapSets];
+  for (int w = 0; w < kTmapWays; ++w)
+    if (set[w].used && set[w].key == key) { *m = set[w].map; return true; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -70,7 +77,10 @@ bool tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const void* base, 
     return false;
   }
   g_tmap_encodes.fetch_add(1, std::memory_order_relaxed);
-  slot.key = key; slot.map = *m; slot.used = true;
+  int w = 0;
+  while (w < kTmapWays && set[w].used) ++w;
+  if (w == kTmapWays) w = (int)(victim[h % kTmapSets]++ % kTmapWays);     // round robin inside the set
+  set[w].key = key; set[w].map = *m; set[w].used = true;
   return true;
 }
 unsigned long long tmap_encode_count() { return g_tmap_encodes.load(std::memory_order_relaxed); }

@@ -83,8 +83,10 @@ class QkvRotaryGraph:
     89-97 us for eager launches on one or two streams, B200).  The reference drives its per-step LSTM launches the same
     way (fly/bench_factored_lstm.py:104-121).  Results are those of the direct calls: same kernels, same arguments.
 
-    ``gemm_events``: after a replay, pairs of CUDA events around each captured GEMM launch (``elapsed_time`` gives the
-    kernel's duration inside the step).
+    ``time_gemms=True`` additionally captures a second graph of the same steps with a pair of CUDA events around
+    every GEMM launch (``replay(timed=True)``; afterwards ``gemm_events[i][0].elapsed_time(gemm_events[i][1])`` is the
+    duration of the i-th GEMM inside the step).  The event nodes cost several microseconds per step, which is why they
+    live in a graph of their own.
     """
 
     def __init__(self, M, K, N, device, slots=3):
@@ -93,6 +95,7 @@ class QkvRotaryGraph:
         self.q = [torch.empty(M, K, dtype=torch.int8, device=self.dev) for _ in range(slots)]
         self.s = [torch.empty(M, dtype=torch.float32, device=self.dev) for _ in range(slots)]
         self.graph = None
+        self.timed_graph = None
         self.gemm_events = []
         self.steps = 0
 
@@ -117,15 +120,19 @@ class QkvRotaryGraph:
             with torch.cuda.graph(self.graph):
                 for r in range(repeat):
                     for b in range(len(xs)):
-                        ev = None
-                        if time_gemms:
+                        one(b, None)
+            if time_gemms:
+                self.timed_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.timed_graph):
+                    for r in range(repeat):
+                        for b in range(len(xs)):
                             ev = (torch.cuda.Event(enable_timing=True, external=True),
                                   torch.cuda.Event(enable_timing=True, external=True))
                             self.gemm_events.append(ev)
-                        one(b, ev)
+                            one(b, ev)
             self.steps = repeat * len(xs)
         return self
 
-    def replay(self):
-        """Launch every captured step on the current stream."""
-        self.graph.replay()
+    def replay(self, timed=False):
+        """Launch every captured step on the current stream (``timed``: the copy with events around the GEMMs)."""
+        (self.timed_graph if timed else self.graph).replay()
