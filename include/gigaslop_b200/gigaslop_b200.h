@@ -227,7 +227,8 @@ int32_t gsb200_dual_gemm_mxfp8_silu_f16(const uint8_t* A, int64_t lda, const uin
                                         const uint8_t* sfb_up_tiled, void* C, int64_t ldc, int64_t M, int32_t N,
                                         int32_t K, gsb200_stream_t stream);
 
-/* LSTM layer, recurrent half: T sequential steps in one persistent cooperative kernel.
+/* LSTM layer, recurrent half: T sequential steps in one persistent kernel (thread-block clusters exchanging h through
+ * distributed shared memory for H <= 384; a cooperative kernel with global scratch otherwise).
  *   gates[b,4H] = ih[t,b,:] + (h_{t-1} . W_hh^T) * (s_hh[n]/448) + bias[n]   (gate blocks i|f|g|o, each H wide)
  *   c_t = sigmoid(f) c_{t-1} + sigmoid(i) tanh(g),  h_t = sigmoid(o) tanh(c_t)
  * ih is the hoisted input projection of all timesteps ([T*B, 4H] fp16, row = t*B + b; produce it with
