@@ -297,3 +297,14 @@ GSB200_MODULE_HOOKS(gemm_i8_std)
 GSB200_MODULE_HOOKS(gemm_i8_rotary_N1536_K512_H8D64R64S1024)
 GSB200_MODULE_HOOKS(gemm_i8_rotary_N1536_K512_H8D64R64S2048)
 GSB200_MODULE_HOOKS(gemm_i8_dual_silu_N2048_K512)
+
+#ifdef GSB200_GEMM_PROF
+// Profiling builds only: copy out (and clear) the per-CTA role timers of the GEMM kernels.
+extern "C" int32_t gsb200_debug_gemm_prof(long long* out /* [160][16] */) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, gsb::g_gemm_prof, sizeof(long long) * 160 * 16);
+  if (e != cudaSuccess) return -1;
+  static long long zeros[160 * 16];
+  e = cudaMemcpyToSymbol(gsb::g_gemm_prof, zeros, sizeof(zeros));
+  return e == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -8,7 +8,8 @@
 #define GSB200_DIAG_FLAG_ABLATE_EPILOGUE 0x200  // output is NOT written: skip the epilogue body
 #define GSB200_DIAG_FLAG_ABLATE_MAINLOOP 0x400  // accumulators are garbage: skip the loads and the MMAs
 #ifdef GSB200_DIAG
-#define GSB200_DIAG_FLAG_MASK 0x703
+#define GSB200_DIAG_FLAG_ABLATE_HALF_WARPS 0x800 // half of the output is NOT written: the epilogue warps of the second column half skip their body
+#define GSB200_DIAG_FLAG_MASK 0xF03
 #else
 #define GSB200_DIAG_FLAG_MASK 0
 #endif

@@ -94,6 +94,9 @@ static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const v
 // ---- per-device state -------------------------------------------------------------------------
 // Atomics: the contract allows one host thread per GPU, and two of them may meet here.
 constexpr int kMaxDevices = 64;
+constexpr int kPairMinRowBlocks = 4 * 148;     // below this many 128-row blocks the single-CTA kernels are used
+constexpr bool kDefaultTwelveWarps = false;    // defaults of the variant choice (see Variant below)
+constexpr bool kDefaultPairs = false;
 static std::atomic<int> g_dev_ok[kMaxDevices];       // 0 unknown, 1 ok, -1 unsupported
 static std::atomic<int> g_dev_sms[kMaxDevices];
 
@@ -106,6 +109,116 @@ static cudaError_t set_attr() {
   return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               GEMM_SMEM_BYTES);
 }
+
+// ---- kernel variants -------------------------------------------------------------------------------
+// The dequant / rotary / SwiGLU epilogues on 8-bit operands exist in four forms: eight or twelve epilogue warps,
+// one CTA or a CTA pair per tile.
+//   Twelve warps (three per SM sub-partition, working on 64-column items): the eight-warp epilogue is bound by the
+//   latency of each warp's own chain, not by a shared resource, so more warps finish a tile sooner.  That form
+//   re-splits its registers with setmaxnreg, which WAITS until the CTA's pool has them: it may only be launched when
+//   the registers the kernel was compiled with, times its 512 threads, cover the re-split (checked here, once).
+//   CTA pairs (tcgen05.mma.cta_group::2): two CTAs of a cluster share every MMA, 256 rows (128 each) x 256
+//   accumulator columns, each CTA holding half of the tile's W rows: half the W traffic from L2 and a third less
+//   shared-memory traffic per tile.
+template <int KIND, int EPI, bool PAIR, int EW>
+struct Variant {
+  static constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
+  static constexpr int THREADS = 32 * (FRONT_WARPS + EW);
+  using Fn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams);
+  static Fn kernel(bool resident) {
+    return resident ? (Fn)gemm_tcgen05_kernel<KIND, EPI, RES, false, PAIR, EW>
+                    : (Fn)gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM, false, PAIR, EW>;
+  }
+  static cudaLaunchConfig_t config(int grid, cudaStream_t st, cudaLaunchAttribute* attr) {
+    attr->id = cudaLaunchAttributeClusterDimension;
+    attr->val.clusterDim.x = PAIR ? 2 : 1; attr->val.clusterDim.y = 1; attr->val.clusterDim.z = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(THREADS, 1, 1);
+    cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cfg;
+  }
+  // Scheduling units (CTAs, or CTA pairs) that can be resident at once on the current device; 0 = this variant must
+  // not be launched here.  Looked up once per device.
+  static int capacity(bool resident) {
+    static std::atomic<int> cap[kMaxDevices][2];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    int c = cap[dev][resident].load(std::memory_order_acquire);
+    if (c == 0) {
+      Fn k = kernel(resident);
+      c = -1;
+      cudaFuncAttributes fa{};
+      bool ok = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) == cudaSuccess &&
+                cudaFuncGetAttributes(&fa, k) == cudaSuccess;
+      if (ok && EW == 12) ok = fa.numRegs * THREADS >= EW12_REG_POOL_NEEDED && fa.numRegs * THREADS <= 65536;
+      if (ok) {
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (PAIR) {
+          cudaLaunchAttribute attr;
+          cudaLaunchConfig_t cfg = config(2 * (sms / 2), nullptr, &attr);
+          int n = 0;
+          if (cudaOccupancyMaxActiveClusters(&n, k, &cfg) == cudaSuccess && n > 0) c = n;
+        } else if (sms > 0) {
+          c = sms;
+        }
+      }
+      (void)cudaGetLastError();
+      cap[dev][resident].store(c, std::memory_order_release);
+      if (getenv("GSB200_GEMM_VERBOSE"))
+        fprintf(stderr, "gigaslop_b200: gemm variant pair=%d epilogue warps=%d: %d units resident (registers %d)\n", (int)PAIR, EW, c, fa.numRegs);
+    }
+    return c > 0 ? c : 0;
+  }
+  static cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1, const CUtensorMap& tc,
+                            const GemmParams& p, int grid, bool resident, cudaStream_t st) {
+    cudaLaunchAttribute attr;
+    cudaLaunchConfig_t cfg = config(grid, st, &attr);
+    return cudaLaunchKernelEx(&cfg, kernel(resident), ta, tb0, tb1, tc, p);
+  }
+};
+
+// One of the variants, picked at run time: capacity (launch = false) or launch.
+template <int KIND, int EPI>
+static int variant_call(bool pair, bool ew12, bool launch, const CUtensorMap& ta, const CUtensorMap& tb0, const CUtensorMap& tb1,
+                        const CUtensorMap& tc, const GemmParams& p, int grid, bool resident, cudaStream_t st) {
+  if (pair && ew12) return launch ? (int)Variant<KIND, EPI, true, 12>::launch(ta, tb0, tb1, tc, p, grid, resident, st) : Variant<KIND, EPI, true, 12>::capacity(resident);
+  if (pair) return launch ? (int)Variant<KIND, EPI, true, 8>::launch(ta, tb0, tb1, tc, p, grid, resident, st) : Variant<KIND, EPI, true, 8>::capacity(resident);
+  if (ew12) return launch ? (int)Variant<KIND, EPI, false, 12>::launch(ta, tb0, tb1, tc, p, grid, resident, st) : Variant<KIND, EPI, false, 12>::capacity(resident);
+  return launch ? (int)Variant<KIND, EPI, false, 8>::launch(ta, tb0, tb1, tc, p, grid, resident, st) : Variant<KIND, EPI, false, 8>::capacity(resident);
+}
+static int variant_dispatch(int kind, int epi, bool pair, bool ew12, bool launch, const CUtensorMap& ta, const CUtensorMap& tb0,
+                            const CUtensorMap& tb1, const CUtensorMap& tc, const GemmParams& p, int grid, bool resident, cudaStream_t st) {
+  const bool i8 = kind == KIND_I8;
+  switch (epi) {
+    case EPI_DEQUANT:
+      return i8 ? variant_call<KIND_I8, EPI_DEQUANT>(pair, ew12, launch, ta, tb0, tb1, tc, p, grid, resident, st)
+                : variant_call<KIND_F8, EPI_DEQUANT>(pair, ew12, launch, ta, tb0, tb1, tc, p, grid, resident, st);
+    case EPI_ROTARY:
+      return i8 ? variant_call<KIND_I8, EPI_ROTARY>(pair, ew12, launch, ta, tb0, tb1, tc, p, grid, resident, st)
+                : variant_call<KIND_F8, EPI_ROTARY>(pair, ew12, launch, ta, tb0, tb1, tc, p, grid, resident, st);
+    default:
+      return i8 ? variant_call<KIND_I8, EPI_SILU>(pair, ew12, launch, ta, tb0, tb1, tc, p, grid, resident, st)
+                : variant_call<KIND_F8, EPI_SILU>(pair, ew12, launch, ta, tb0, tb1, tc, p, grid, resident, st);
+  }
+}
+
+// Environment switches for comparisons: GSB200_GEMM_PAIR = 0 never / 1 whenever the shape allows (unset: by size);
+// GSB200_GEMM_EW = 8 / 12 epilogue warps (unset: the default below).
+static int env_choice(const char* name, std::atomic<int>& state) {
+  int s = state.load(std::memory_order_relaxed);
+  if (s == 0) {
+    const char* e = getenv(name);
+    s = e ? 2 + atoi(e) : 1;               // 1 = unset, 2 + value otherwise
+    state.store(s, std::memory_order_relaxed);
+  }
+  return s;
+}
+static std::atomic<int> g_env_pair{0}, g_env_ew{0};
 
 int32_t ensure_device() {
   int dev = 0;
@@ -238,7 +351,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.rot_cols = rot_cols;
   p.row_offset = (int)(a.row_offset % p.seqlen);
   p.direct_store = (a.flags & GSB200_DIAG_FLAG_MASK & GSB200_DIAG_FLAG_DIRECT_STORE) ? 1 : 0;
-  p.ablate = ((a.flags & GSB200_DIAG_FLAG_MASK) >> 8) & 7;
+  p.ablate = ((a.flags & GSB200_DIAG_FLAG_MASK) >> 8) & 15;
   p.x_f16 = a.x_f16; p.ldx = a.ldx; p.scale_a_out = a.scale_a_out;
   const long long tiles = (long long)p.m_blocks * p.n_blocks;
   if (tiles > 0x7fffffffll) return GSB200_ERR_BAD_ARG;
@@ -267,6 +380,27 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   int sms = sm_count();
   if (a.sm_cap > 0 && a.sm_cap < sms) sms = a.sm_cap;
   if (a.epi == EPI_BIAS && !resident) return GSB200_ERR_UNSUPPORTED;     // only built for K <= 512 bytes of A per row
+  // CTA pairs: 8-bit operands, the dequant / rotary / SwiGLU epilogues, at least two K blocks (the deeper rings' scale
+  // buffers need that), and enough row blocks that pairs of SMs stay busy.  From here on a "row block" of the
+  // schedule is the pair's 256 rows and `sms` counts pairs.
+  bool pair = false, ew12 = false;
+  const bool variants = !fused && !p.direct_store && (a.kind == KIND_I8 || a.kind == KIND_F8) &&
+                        (a.epi == EPI_DEQUANT || a.epi == EPI_ROTARY || a.epi == EPI_SILU);
+  if (variants) {
+    const int ew = env_choice("GSB200_GEMM_EW", g_env_ew), pm = env_choice("GSB200_GEMM_PAIR", g_env_pair);
+    ew12 = ew == 1 ? kDefaultTwelveWarps : ew == 2 + 12;
+    const bool want_pair = p.k_blocks >= 2 && sms >= 2 && (pm == 1 ? (kDefaultPairs && p.m_blocks >= kPairMinRowBlocks) : pm == 2 + 1);
+    if (ew12 && !variant_dispatch(a.kind, a.epi, false, true, false, ta, tb0, tb1, tc, p, 0, resident, st)) ew12 = false;
+    if (want_pair) {
+      int cap = variant_dispatch(a.kind, a.epi, true, ew12, false, ta, tb0, tb1, tc, p, 0, resident, st);
+      if (cap > 0) {
+        pair = true;
+        sms = sms / 2 < cap ? sms / 2 : cap;
+        p.m_blocks = (p.m_blocks + 1) / 2;
+      }
+    }
+  }
+  const long long sched_tiles = (long long)p.m_blocks * p.n_blocks;
   if (resident && !a_stationary) {
     int groups = sms / p.n_blocks;
     if (groups < 1) groups = 1;
@@ -287,9 +421,14 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
       if (S > 1) p.ares_split = S;
     }
   } else {
-    grid = (int)(tiles < sms ? tiles : sms);
+    grid = (int)(sched_tiles < sms ? sched_tiles : sms);
   }
   cudaError_t e = cudaErrorInvalidValue;
+  if (pair || ew12) {
+    if (pair) grid *= 2;
+    e = (cudaError_t)variant_dispatch(a.kind, a.epi, pair, ew12, true, ta, tb0, tb1, tc, p, grid, resident, st);
+    return cuda_status(e, "gemm launch");
+  }
   if (a.kind == KIND_I8) {
     switch (a.epi) {
       case EPI_I32: e = launch_inst<KIND_I8, EPI_I32>(ta, tb0, tb1, tc, p, grid, resident, st); break;

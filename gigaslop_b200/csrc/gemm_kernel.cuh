@@ -70,32 +70,41 @@ constexpr int SCALE_BUF_BYTES = BN * 4;                 // channel scales of one
 //   STREAM: [ring 3 x (A 16 KiB | B 32 KiB)]              [staging 8 warps x 4 x 2 KiB][scales 6 x 1 KiB][barriers]
 //   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales 1 KiB][barriers]
 //   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 3 x 2 KiB][scales 6 x 1 KiB][barriers]
-template <int SCHED>
+//   PAIR (two CTAs on one tcgen05.mma.cta_group::2): a CTA holds only HALF of the tile's W rows (16 KiB per K block), and
+//   the memory that frees goes into deeper rings (4 stages streaming, 6 with a resident operand).
+//   EW = 12 (twelve epilogue warps, each working on 64-column items): one box pair (4 KiB) of staging per warp.
+template <int SCHED, bool PAIR = false, int EW = EPI_WARPS>
 struct SmemMap {
-  static constexpr int RES_BYTES = SCHED == SCHED_WRES ? RES_MAX_KBLOCKS * B_STAGE_BYTES
+  static constexpr int B_BYTES = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;      // W bytes per K block in one CTA
+  static constexpr int NSTAGE = !PAIR ? gsb::NSTAGE : SCHED == SCHED_STREAM ? 4 : 6;
+  static constexpr int RES_BYTES = SCHED == SCHED_WRES ? RES_MAX_KBLOCKS * B_BYTES
                                  : SCHED == SCHED_ARES ? RES_MAX_KBLOCKS * A_STAGE_BYTES : 0;
   static constexpr int STAGE_BYTES = SCHED == SCHED_WRES ? A_STAGE_BYTES
-                                   : SCHED == SCHED_ARES ? B_STAGE_BYTES : A_STAGE_BYTES + B_STAGE_BYTES;
+                                   : SCHED == SCHED_ARES ? B_BYTES : A_STAGE_BYTES + B_BYTES;
   static constexpr int RING_OFF = RES_BYTES;
-  static constexpr int OUT_BUFS = SCHED == SCHED_STREAM ? 4 : 3;   // 32x32 fp16 staging boxes per epilogue warp
+  static constexpr int OUT_BUFS = EW == 12 ? 2 : SCHED == SCHED_STREAM ? 4 : 3;   // 2 KiB staging boxes per epilogue warp
   // Channel-scale buffers, filled by the producer beside each tile's first K block.  A weight-stationary
   // CTA keeps one column block, hence one buffer.  Otherwise tile j uses buffer j % 6: when the producer
   // fills it again (tile j + 6) it holds a ring slot the MMA warp freed at most ceil(NSTAGE / k_blocks) <= 3
-  // tiles earlier, the MMA warp of tile t has been given the accumulator stage of tile t - 2 by every
+  // tiles earlier (the deeper rings of a pair need k_blocks >= 2 for that; the host sends other shapes elsewhere), the MMA warp of tile t has been given the accumulator stage of tile t - 2 by every
   // epilogue warp, and a warp that has released tile t - 2 is done with tile t - 3: 3 + 3 = 6.
   static constexpr int SCALE_BUFS = SCHED == SCHED_WRES ? 1 : 6;
   static constexpr int OUT_OFF = RING_OFF + NSTAGE * STAGE_BYTES;
-  static constexpr int SCALE_OFF = OUT_OFF + EPI_WARPS * OUT_BUFS * OUT_BUF_BYTES;
+  static constexpr int SCALE_OFF = OUT_OFF + EW * OUT_BUFS * OUT_BUF_BYTES;
   // fused activation quantiser (activation-stationary only): the token scales of up to four row blocks in flight
   static constexpr int SA_OFF = SCALE_OFF + SCALE_BUFS * SCALE_BUF_BYTES;
   static constexpr int SA_BUFS = 4;
   static constexpr int SA_BYTES = SCHED == SCHED_ARES ? SA_BUFS * BM * 4 : 0;
   static constexpr int BAR_OFF = SA_OFF + SA_BYTES;
-  static constexpr int USED = BAR_OFF + 256;
+  static constexpr int USED = BAR_OFF + 512;
 };
 constexpr int GEMM_SMEM_BYTES = 227 * 1024;             // request the maximum; the base is aligned up to 1 KiB
-static_assert(SmemMap<0>::USED <= GEMM_SMEM_BYTES && SmemMap<1>::USED <= GEMM_SMEM_BYTES &&
-              SmemMap<2>::USED <= GEMM_SMEM_BYTES, "shared memory budget");
+static_assert(SmemMap<0>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<1>::USED + 1024 <= GEMM_SMEM_BYTES &&
+              SmemMap<2>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<0, true>::USED + 1024 <= GEMM_SMEM_BYTES &&
+              SmemMap<1, true>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<2, true>::USED + 1024 <= GEMM_SMEM_BYTES &&
+              SmemMap<0, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<1, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES &&
+              SmemMap<2, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES,
+              "shared memory budget");
 static_assert(GEMM_SMEM_BYTES > 116 * 1024, "one CTA per SM is what makes the 512-column TMEM allocation safe");
 
 constexpr unsigned int ST_BAD_SMEM_ALIGN = 1u << 8;
@@ -124,12 +133,27 @@ struct GemmParams {
   float* scale_a_out;          //   optional: the token scales [M], as quantize_tensor would return them
   // Diagnostics, honoured only by a library built with -DGSB200_DIAG (never by the shipped one):
   int direct_store;            // 1: plain st.global from registers instead of smem + TMA store
-  int ablate;                  // timing ablations (results are then wrong): 1 = skip the output stores, 2 = skip the epilogue body, 4 = skip the main loop
+  int ablate;                  // timing ablations (results are then wrong): 1 = skip the output stores, 2 = skip the epilogue body, 4 = skip the main loop, 8 = half of the epilogue warps skip their body
 };
 #ifdef GSB200_DIAG
 constexpr bool kDiag = true;
 #else
 constexpr bool kDiag = false;
+#endif
+
+// Role timers of a profiling build (-DGSB200_GEMM_PROF, never the shipped library): clocks spent in each role's
+// waits, summed per CTA.
+#ifdef GSB200_GEMM_PROF
+__device__ long long g_gemm_prof[160][16];
+#define GP_DECL(n) long long gp_##n = 0
+#define GP_BEGIN(t) const long long t = clock64()
+#define GP_END(n, t) gp_##n += clock64() - t
+#define GP_STORE(slot, n) g_gemm_prof[blockIdx.x % 160][slot] = gp_##n
+#else
+#define GP_DECL(n) do { } while (0)
+#define GP_BEGIN(t) do { } while (0)
+#define GP_END(n, t) do { } while (0)
+#define GP_STORE(slot, n) do { } while (0)
 #endif
 
 template <int KIND>
@@ -184,8 +208,11 @@ struct false_tag { static constexpr bool value = false; };
 //   WRES:               fixed column block, row blocks group, group + n_groups, ...
 //   ARES, STREAM m_major: row blocks cta, cta + grid, ...; all column blocks of one before the next
 //   STREAM:             tiles cta, cta + grid, ... with the column block fastest
-template <int SCHED>
+//   PAIR: the walk's unit is the CTA pair (pair = blockIdx.x / 2) and a "row block" is 256 rows, 128 per CTA.
+template <int SCHED, bool PAIR = false>
 struct TileWalk {
+  static __device__ __forceinline__ int cta() { return PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x; }
+  static __device__ __forceinline__ int ncta() { return PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x; }
   int m, n;
   int dm, dn;      // STREAM with the column block fastest: what one step of `grid` tiles adds
   int n_lo, n_hi;  // row-block-major walks: this CTA's column blocks of row block m are [n_lo, n_hi)
@@ -194,15 +221,15 @@ struct TileWalk {
   // keep some SMs busy for a whole row block while the others idle: with the activation-stationary schedule each of
   // them is shared by p.ares_split CTAs, which take consecutive column blocks of it (each loads the A block).
   __device__ __forceinline__ void set_visit(const GemmParams& p) {
-    const int grid = (int)gridDim.x, full = p.m_blocks / grid, rem = p.m_blocks - full * grid;
+    const int grid = ncta(), full = p.m_blocks / grid, rem = p.m_blocks - full * grid;
     m = p.m_blocks;                                   // nothing left unless one of the cases below applies
     n_lo = 0; n_hi = p.n_blocks;
     if (visit < full) {
-      m = (int)blockIdx.x + visit * grid;
+      m = cta() + visit * grid;
     } else if (visit == full && rem > 0) {
       const int S = (SCHED == SCHED_ARES && p.ares_split > 1) ? p.ares_split : 1;
       const int per = (p.n_blocks + S - 1) / S;
-      const int c = (int)blockIdx.x;
+      const int c = cta();
       if (c < rem * S && (c % S) * per < p.n_blocks) {
         m = full * grid + c / S;
         n_lo = (c % S) * per;
@@ -214,12 +241,12 @@ struct TileWalk {
   __device__ __forceinline__ void start(const GemmParams& p) {
     dm = dn = 0; n_lo = 0; n_hi = p.n_blocks; visit = 0;
     if constexpr (SCHED == SCHED_WRES) {
-      n = blockIdx.x % p.n_blocks; m = blockIdx.x / p.n_blocks;
+      n = cta() % p.n_blocks; m = cta() / p.n_blocks;
     } else {
       if (SCHED == SCHED_ARES || p.m_major) set_visit(p);
       else {
-        m = blockIdx.x / p.n_blocks; n = blockIdx.x % p.n_blocks;
-        dm = gridDim.x / p.n_blocks; dn = gridDim.x % p.n_blocks;
+        m = cta() / p.n_blocks; n = cta() % p.n_blocks;
+        dm = ncta() / p.n_blocks; dn = ncta() % p.n_blocks;
       }
     }
   }
@@ -243,17 +270,33 @@ struct TileWalk {
   }
 };
 
-template <int KIND, int EPI, int SCHED, bool FUSEQ = false>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// Register budgets of the twelve-epilogue-warp form (512 threads compiled at 128 registers: 128 x 56 + 384 x 152 = 65536).
+constexpr int EW12_THREADS = 32 * (FRONT_WARPS + 12);
+constexpr int EW12_FRONT_REGS = 56;
+constexpr int EW12_EPI_REGS = 152;
+constexpr int EW12_REG_POOL_NEEDED = 32 * (FRONT_WARPS * EW12_FRONT_REGS + 12 * EW12_EPI_REGS);
+
+template <int KIND, int EPI, int SCHED, bool FUSEQ = false, bool PAIR = false, int EW = EPI_WARPS>
+__global__ void __launch_bounds__(32 * (FRONT_WARPS + EW), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_c,
                     const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  using Map = SmemMap<SCHED>;
+  using Map = SmemMap<SCHED, PAIR, EW>;
+  static_assert(EW == EPI_WARPS || (EW == 12 && !FUSEQ && (EPI == EPI_DEQUANT || EPI == EPI_ROTARY || EPI == EPI_SILU)),
+                "twelve epilogue warps: built for the dequant, rotary and SwiGLU epilogues");
+  constexpr int NTHREADS = 32 * (FRONT_WARPS + EW);
+  // EW = 12: the epilogue's unit of work is an ITEM, 32 rows x 64 output columns; every item hands its part of the
+  // accumulator stage back by itself
+  constexpr int ITEMS = (EPI == EPI_SILU || EPI == EPI_SILU_MX) ? 2 : 4;
+  constexpr int ACC_RELEASES = (EW == 12 ? 4 * ITEMS : EPI_WARPS) * (PAIR ? 2 : 1);
+  using Walk = TileWalk<SCHED, PAIR>;
+  constexpr int NSTAGE = Map::NSTAGE;
   constexpr bool WRES = SCHED == SCHED_WRES;
   constexpr bool ARES = SCHED == SCHED_ARES;
   constexpr int OUT_BUFS = Map::OUT_BUFS;
+  // (the offset of the dynamic window is the same in every CTA of a launch, so both CTAs of a pair take this exit or neither)
   if (smem + Map::USED > smem_raw + GEMM_SMEM_BYTES) {     // cannot happen with a 1 KiB-aligned window; never run off the end
     if (threadIdx.x == 0) atomicOr(&g_status[0], ST_BAD_SMEM_ALIGN);
     return;
@@ -270,7 +313,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   uint64_t* res_full = acc_empty + ACC_STAGES;             // [RES_MAX_KBLOCKS] resident piece landed (WRES uses [0] only)
   uint64_t* res_empty = res_full + RES_MAX_KBLOCKS;        // [RES_MAX_KBLOCKS] ARES: A piece no longer needed
   uint64_t* sa_ready = res_empty + RES_MAX_KBLOCKS;        // [SA_BUFS] FUSEQ: token scales of a row block written
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sa_ready + Map::SA_BUFS);
+  uint64_t* sc_full = sa_ready + Map::SA_BUFS;             // [SCALE_BUFS] PAIR: channel scales of a tile landed (in this CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_full + Map::SCALE_BUFS);
+  static_assert(!(PAIR && FUSEQ), "the fused quantiser is built for the single-CTA kernel");
+  // PAIR: CTA rank 0 of the pair issues the MMAs; its barriers collect both CTAs' loads and releases
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  auto rowblk = [&](int m) { return PAIR ? 2 * m + (int)rank : m; };      // walk unit -> 128-row block of this CTA
   float* sa_s = reinterpret_cast<float*>(smem + Map::SA_OFF);
   static_assert(!FUSEQ || (SCHED == SCHED_ARES && KIND == KIND_I8), "the fused quantiser feeds the resident int8 A block");
   const AbortFlag abort_flag{smem_u32(tmem_slot + 1)};
@@ -282,7 +330,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NSTAGE; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
+    for (int s = 0; s < ACC_STAGES; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], ACC_RELEASES); }
+    for (int s = 0; s < Map::SCALE_BUFS; ++s) mbar_init(&sc_full[s], 1);
     // FUSEQ: the two quantiser warps both report a finished A block
     for (int s = 0; s < RES_MAX_KBLOCKS; ++s) { mbar_init(&res_full[s], FUSEQ ? 2 : 1); mbar_init(&res_empty[s], 1); }
     for (int s = 0; s < Map::SA_BUFS; ++s) mbar_init(&sa_ready[s], 2);
@@ -291,16 +340,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     prefetch_tmap(&tm_a); prefetch_tmap(&tm_b0); prefetch_tmap(&tm_b1);
     if (EPI != EPI_I32) prefetch_tmap(&tm_c);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (warp == 1) {
+    if constexpr (PAIR) { tmem_alloc_pair(tmem_slot, TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  }
   // Channel scales normally arrive by bulk copy from the producer; without a per-channel vector (none given,
   // or one scalar for all columns) every buffer is filled with the constant once, here.
   const bool copy_scales = EPI != EPI_I32 && p.scale_b0 != nullptr && !p.scale_b_scalar;
   if (EPI != EPI_I32 && !copy_scales) {
     const float v = p.scale_b0 ? __ldg(p.scale_b0) : 1.f;
-    for (int i = threadIdx.x; i < Map::SCALE_BUFS * BN; i += GEMM_THREADS) scale_base[i] = v;
+    for (int i = threadIdx.x; i < Map::SCALE_BUFS * BN; i += NTHREADS) scale_base[i] = v;
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();             // the other CTA's barriers are initialised before anything arrives at them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const unsigned int budget = spin_budget();          // bound of every wait below, fetched once
@@ -308,11 +361,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   // The register re-split sits inside each role's branch: code placed after the point where the two
   // branches meet would be compiled for the smaller budget.
   if (warp < FRONT_WARPS) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FUSEQ ? FRONT_REGS_FUSEQ : FRONT_REGS));
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(EW == 12 ? EW12_FRONT_REGS : FUSEQ ? FRONT_REGS_FUSEQ : FRONT_REGS));
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int s = 0; uint32_t ph = 0; bool ok = true;
+      GP_DECL(p_total); GP_DECL(p_empty); GP_BEGIN(gp_p0);
       // channel scales of the tile whose first output column is n0 -> buffer dst, bytes reported to bar
       auto scale_bytes = [&](int n0) -> uint32_t {
         return copy_scales ? (uint32_t)((DUAL ? 2 : 1) * min(OUT_COLS_PER_TILE, p.N - n0) * 4) : 0u;
@@ -323,24 +377,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         bulk_load(dst, p.scale_b0 + n0, bytes, bar);
         if constexpr (DUAL) bulk_load(dst + BN / 2, p.scale_b1 + n0, bytes, bar);
       };
+      // `bytes` = what ONE CTA loads onto the barrier; of a pair only the first CTA arrives, for both
+      auto expect = [&](uint64_t* bar, uint32_t bytes) {
+        if constexpr (!PAIR) mbar_arrive_expect_tx(bar, bytes);
+        else if (rank == 0) mbar_arrive_expect_tx(bar, 2 * bytes);
+      };
+      auto load_a = [&](void* dst, uint64_t* bar, int x, int y) {
+        if constexpr (PAIR) tma_load_2d_pair(dst, &tm_a, mapa_shared(smem_u32(bar), 0), x, y);
+        else tma_load_2d(dst, &tm_a, bar, x, y);
+      };
+      // the tile's W rows: both halves, or of a pair the half of this CTA (first CTA: rows n0.., second: rows n1..)
+      auto load_b = [&](uint8_t* dst, uint64_t* bar, int x, int n0, int n1) {
+        if constexpr (PAIR) {
+          tma_load_2d_pair(dst, rank ? &tm_b1 : &tm_b0, mapa_shared(smem_u32(bar), 0), x, rank ? n1 : n0);
+        } else {
+          tma_load_2d(dst, &tm_b0, bar, x, n0);
+          tma_load_2d(dst + (BN / 2) * BK, &tm_b1, bar, x, n1);
+        }
+      };
+      // PAIR: a tile's channel scales report to a barrier of this CTA (an untiled bulk copy cannot report to the other CTA)
+      auto load_scales_own = [&](int sb, int n0) {
+        const uint32_t bytes = scale_bytes(n0);
+        if (bytes) { mbar_arrive_expect_tx(&sc_full[sb], bytes); load_scales(scale_base + sb * BN, n0, &sc_full[sb]); }
+      };
       int sbuf = 0;                           // scale buffer of the current tile
       if constexpr (WRES) {
-        const int n0 = (blockIdx.x % p.n_blocks) * OUT_COLS_PER_TILE;
+        const int n0 = (Walk::cta() % p.n_blocks) * OUT_COLS_PER_TILE;
         const int n1 = DUAL ? n0 : n0 + BN / 2;
-        mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES + scale_bytes(n0));
-        load_scales(scale_base, n0, &res_full[0]);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          uint8_t* sb = res_base + kb * B_STAGE_BYTES;
-          tma_load_2d(sb, &tm_b0, &res_full[0], kb * BK, n0);
-          tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &res_full[0], kb * BK, n1);
+        if constexpr (PAIR) {
+          load_scales_own(0, n0);
+          expect(&res_full[0], p.k_blocks * Map::B_BYTES);
+        } else {
+          mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES + scale_bytes(n0));
+          load_scales(scale_base, n0, &res_full[0]);
         }
+        for (int kb = 0; kb < p.k_blocks; ++kb) load_b(res_base + kb * Map::B_BYTES, &res_full[0], kb * BK, n0, n1);
       }
       uint32_t rph = 0;                       // ARES: phase of the resident-A barriers, flips per row block
       int rot = 0;                            // WRES: it % n_blocks, which CTA of a group asks for the L2 prefetch
-      TileWalk<SCHED> tw; tw.start(p);
+      Walk tw; tw.start(p);
       for (int it = 0; ok && !(kDiag && (p.ablate & 4)) && tw.valid(p); ++it, tw.next(p)) {
-        const int m_blk = tw.m, n_blk = tw.n;
-        const int m0 = m_blk * BM;
+        const int n_blk = tw.n;
+        const int m0 = rowblk(tw.m) * BM;
         const int n0 = n_blk * OUT_COLS_PER_TILE;
         const int n1 = DUAL ? n0 : n0 + BN / 2;
         const bool rb_first = tw.first();      // first tile of this CTA's stay on the row block
@@ -349,48 +427,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         //   WRES: the row block two tiles on (one CTA of the group asks, the others find it in L2)
         //   ARES: this CTA's next row block, at the start of the current one
         if constexpr (WRES) {
-          const int pm = m_blk + 2 * p.n_groups;
+          const int pm = tw.m + 2 * p.n_groups;
           if (pm < p.m_blocks && rot == n_blk)
-            for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, pm * BM);
+            for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, rowblk(pm) * BM);
           if (++rot == p.n_blocks) rot = 0;
         } else if constexpr (ARES) {
           if (!FUSEQ && rb_first) {
             const int nm = tw.next_row_block(p);
             if (nm >= 0)
-              for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, nm * BM);
+              for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, rowblk(nm) * BM);
           }
         }
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if constexpr (ARES && !FUSEQ) {
             if (rb_first) {                   // new row block: refill this K piece of A once its last reader retired
               if (!mbar_wait(&res_empty[kb], rph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | 0x300 | kb, budget)) { ok = false; break; }
-              mbar_arrive_expect_tx(&res_full[kb], A_STAGE_BYTES);
-              tma_load_2d(res_base + kb * A_STAGE_BYTES, &tm_a, &res_full[kb], kb * BK, m0);
+              expect(&res_full[kb], A_STAGE_BYTES);
+              load_a(res_base + kb * A_STAGE_BYTES, &res_full[kb], kb * BK, m0);
             }
           }
+          GP_BEGIN(gp_t);
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, ST_TIMEOUT_PRODUCER, (0u << 16) | s, budget)) { ok = false; break; }
+          GP_END(p_empty, gp_t);
           uint8_t* st = ring + s * Map::STAGE_BYTES;
-          const uint32_t sc_bytes = (!WRES && kb == 0) ? scale_bytes(n0) : 0u;   // the scales ride on the first K block
+          // the scales ride on the first K block (of a pair: on a barrier of their own)
+          const uint32_t sc_bytes = (!PAIR && !WRES && kb == 0) ? scale_bytes(n0) : 0u;
+          if (PAIR && !WRES && kb == 0) load_scales_own(sbuf, n0);
           if constexpr (WRES) {
-            mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES);
-            tma_load_2d(st, &tm_a, &full_bar[s], kb * BK, m0);
+            expect(&full_bar[s], A_STAGE_BYTES);
+            load_a(st, &full_bar[s], kb * BK, m0);
           } else if constexpr (ARES) {
-            mbar_arrive_expect_tx(&full_bar[s], B_STAGE_BYTES + sc_bytes);
-            if (kb == 0) load_scales(scale_base + sbuf * BN, n0, &full_bar[s]);
-            tma_load_2d(st, &tm_b0, &full_bar[s], kb * BK, n0);
-            tma_load_2d(st + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
+            expect(&full_bar[s], Map::B_BYTES + sc_bytes);
+            if (!PAIR && kb == 0) load_scales(scale_base + sbuf * BN, n0, &full_bar[s]);
+            load_b(st, &full_bar[s], kb * BK, n0, n1);
           } else {
-            uint8_t* sb = st + A_STAGE_BYTES;
-            mbar_arrive_expect_tx(&full_bar[s], A_STAGE_BYTES + B_STAGE_BYTES + sc_bytes);
-            if (kb == 0) load_scales(scale_base + sbuf * BN, n0, &full_bar[s]);
-            tma_load_2d(st, &tm_a, &full_bar[s], kb * BK, m0);
-            tma_load_2d(sb, &tm_b0, &full_bar[s], kb * BK, n0);
-            tma_load_2d(sb + (BN / 2) * BK, &tm_b1, &full_bar[s], kb * BK, n1);
+            expect(&full_bar[s], A_STAGE_BYTES + Map::B_BYTES + sc_bytes);
+            if (!PAIR && kb == 0) load_scales(scale_base + sbuf * BN, n0, &full_bar[s]);
+            load_a(st, &full_bar[s], kb * BK, m0);
+            load_b(st + A_STAGE_BYTES, &full_bar[s], kb * BK, n0, n1);
           }
           if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
         if (!WRES && ++sbuf == Map::SCALE_BUFS) sbuf = 0;
       }
+      GP_END(p_total, gp_p0); GP_STORE(3, p_empty); GP_STORE(4, p_total);
       if (!ok) {                       // give copies already in flight time to land before the CTA exits
         long long t0 = clock64();
         while (clock64() - t0 < 2000000) { }
@@ -398,33 +478,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       // s8 x s8 -> s32 | e4m3 x e4m3 -> f32 | f16 x f16 -> f32 (format code 0 means e4m3 resp. f16 in its kind)
-      constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, BM, BN) : umma_idesc(1, 0, 0, BM, BN);
+      constexpr int MMA_M = PAIR ? 2 * BM : BM;          // a pair's MMA spans both CTAs' 128 rows
+      constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, MMA_M, BN) : umma_idesc(1, 0, 0, MMA_M, BN);
+      // completion of the MMAs issued so far -> the barrier (of a pair: the same barrier in both CTAs)
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (PAIR) { umma_commit_pair(smem_u32(bar)); umma_commit_pair(mapa_shared(smem_u32(bar), 1)); }
+        else umma_commit(bar);
+      };
       int s = 0; uint32_t ph = 0; bool ok = true;
+      GP_DECL(m_total); GP_DECL(m_acc); GP_DECL(m_full); GP_BEGIN(gp_m0);
       if (WRES && !(kDiag && (p.ablate & 4))) {
         ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200, budget);
         tc_fence_after();
       }
       uint32_t rph = 0;
-      TileWalk<SCHED> tw; tw.start(p);
+      Walk tw; tw.start(p);
       for (int it = 0; ok && tw.valid(p); ++it, tw.next(p)) {
-        const int n_blk = tw.n;
         const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
+        // (of a pair: the other CTA's epilogue warps arrive here too; what they hand over is tensor memory, ordered by the
+        // tcgen05 fences on both sides)
+        GP_BEGIN(gp_ta);
         if (!mbar_wait(&acc_empty[as], aph ^ 1, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x100 | as, budget)) { ok = false; break; }
+        GP_END(m_acc, gp_ta);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
         const bool rb_first = tw.first(), rb_last = tw.last();
         if (ARES && rb_first && it != 0) rph ^= 1;
         for (int kb = 0; kb < p.k_blocks && !(kDiag && (p.ablate & 4)); ++kb) {
+          GP_BEGIN(gp_tf);
           if constexpr (ARES) {
             if (rb_first && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
           }
           if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s, budget)) { ok = false; break; }
+          GP_END(m_full, gp_tf);
           tc_fence_after();
           uint32_t a_addr, b_addr;
           const uint32_t st = smem_u32(ring + s * Map::STAGE_BYTES);
-          if constexpr (WRES) { a_addr = st; b_addr = smem_u32(res_base + kb * B_STAGE_BYTES); }
+          if constexpr (WRES) { a_addr = st; b_addr = smem_u32(res_base + kb * Map::B_BYTES); }
           else if constexpr (ARES) { a_addr = smem_u32(res_base + kb * A_STAGE_BYTES); b_addr = st; }
           else { a_addr = st; b_addr = st + A_STAGE_BYTES; }
           const uint64_t a_desc = umma_smem_desc_sw128(a_addr);
@@ -432,16 +524,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t koff = (uint64_t)((k * UMMA_K) >> 4);
-            if constexpr (KIND == KIND_I8) umma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
-            else if constexpr (KIND == KIND_F16) umma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
-            else umma_f8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+            if constexpr (PAIR) {
+              if constexpr (KIND == KIND_I8) umma_i8_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+              else if constexpr (KIND == KIND_F16) umma_f16_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+              else umma_f8_pair(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+            } else {
+              if constexpr (KIND == KIND_I8) umma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+              else if constexpr (KIND == KIND_F16) umma_f16(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+              else umma_f8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+            }
           }
-          umma_commit(&empty_bar[s]);          // ring stage reusable once these MMAs retire
-          if (ARES && rb_last) umma_commit(&res_empty[kb]);   // last reader of this A piece
+          commit(&empty_bar[s]);               // ring stage reusable once these MMAs retire
+          if (ARES && rb_last) commit(&res_empty[kb]);        // last reader of this A piece
           if (++s == NSTAGE) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(&acc_full[as]);     // accumulator complete
+        if (ok) commit(&acc_full[as]);          // accumulator complete
       }
+      GP_END(m_total, gp_m0); GP_STORE(0, m_total); GP_STORE(1, m_acc); GP_STORE(2, m_full);
     }
   } else if constexpr (FUSEQ) {
     // ------------------------------ activation quantiser (warps 2 and 3) ------------------------------
@@ -541,6 +640,194 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
   }
+  } else if constexpr (EW == 12) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(EW12_EPI_REGS));
+    // ------------------------------ epilogue, twelve warps ----------------------------------
+    // Three warps per SM sub-partition (the eight-warp epilogue is bound by the latency of each warp's own chain:
+    // tensor-memory load -> arithmetic -> staging -> store issue).  Warp e reads TMEM lane quarter e % 4.  The
+    // quarter's work is a stream of items -- (tile, 64-column group): a head of the QKV projection, 64 gate + 64 up
+    // columns of the SwiGLU -- dealt to its three warps in turn.  An item loads its accumulator columns, returns
+    // them to the MMA warp at once (the stage's barrier counts items), computes, stages one pair of 16-row boxes and
+    // issues their TMA stores.
+    const int e = warp - FRONT_WARPS;      // 0..11
+    const int q = warp & 3;                // TMEM lane quarter
+    const int j = e >> 2;                  // which of the quarter's three warps
+    uint8_t* out_buf = out_base + e * 2 * OUT_BUF_BYTES;
+    // this thread's 128-byte box row (lanes 0-15: first box, 16-31: second); its 16-byte piece pc sits at
+    // ((pc ^ (lane & 7)) << 4) in the row (128-byte swizzle)
+    uint8_t* const stg_row = out_buf + (lane < 16 ? 0 : OUT_BUF_BYTES) + (lane & 15) * 128;
+    const int stg_sw = lane & 7;
+    float sa = 0.f;
+    float2 sn2[EPI == EPI_ROTARY ? 16 : 1], cs2[EPI == EPI_ROTARY ? 16 : 1];
+    int cur_m_blk = -1;
+    bool trig_scaled = false;
+    int sbuf = 0;
+    int base3 = 0;                         // (tiles so far * ITEMS) % 3
+    Walk tw; tw.start(p);
+    for (int it = 0; tw.valid(p); ++it, tw.next(p)) {
+      const int m_blk = rowblk(tw.m), n_blk = tw.n;
+      const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
+      const int n0 = n_blk * OUT_COLS_PER_TILE;
+      const int row_base = m_blk * BM + q * 32;
+      int first = j - base3; if (first < 0) first += 3;          // this warp's first item of the tile
+      base3 += ITEMS % 3; if (base3 >= 3) base3 -= 3;
+      // per-row state of a new row block, asked for before the accumulator wait
+      if (first < ITEMS && m_blk != cur_m_blk) {
+        cur_m_blk = m_blk;
+        const long long r = (long long)row_base + lane;
+        sa = (r < p.M) ? (p.scale_a ? ldg_f_here(p.scale_a + r) : 1.f) : 0.f;
+        if constexpr (EPI == EPI_ROTARY) {
+          trig_scaled = false;
+          const int pos = r < p.M ? (int)((r + p.row_offset) % p.seqlen) : 0;
+          const float* s4 = p.sin_tab + (long long)pos * 32;
+          const float* c4 = p.cos_tab + (long long)pos * 32;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(sn2[2 * k].x), "=f"(sn2[2 * k].y), "=f"(sn2[2 * k + 1].x), "=f"(sn2[2 * k + 1].y) : "l"(s4 + 4 * k));
+            asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(cs2[2 * k].x), "=f"(cs2[2 * k].y), "=f"(cs2[2 * k + 1].x), "=f"(cs2[2 * k + 1].y) : "l"(c4 + 4 * k));
+          }
+        }
+      }
+      // every warp follows every tile's barrier (also tiles in which it has no item), so the phase it waits for is
+      // always the next one
+      const bool got = mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as, budget);
+      uint32_t agreed = __all_sync(0xffffffffu, got) ? 1u : 0u;
+      if (!agreed) break;
+      asm volatile("" : "+r"(agreed));     // the scale address below stays dependent on the wait
+      tc_fence_after();
+      if constexpr (PAIR) {
+        if (copy_scales) {
+          const bool have = mbar_wait(&sc_full[sbuf], (uint32_t)(WRES ? 0 : it / Map::SCALE_BUFS) & 1u, abort_flag,
+                                      ST_TIMEOUT_EPILOGUE, (2u << 16) | 0x600 | sbuf, budget);
+          if (!__all_sync(0xffffffffu, have)) break;
+        }
+      }
+      const uint32_t sc_tile = smem_u32(scale_base + sbuf * BN) + ((agreed - 1u) << 2);
+      if (!WRES && ++sbuf == Map::SCALE_BUFS) sbuf = 0;
+      const uint32_t t_tile = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
+      const float2 sa2 = pk2(sa, sa);
+#pragma unroll 1
+      for (int c = first; c < ITEMS; c += 3) {
+        const int n = n0 + 64 * c;           // first output column of the item
+        auto release = [&]() {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_remote(mapa_shared(smem_u32(&acc_empty[as]), 0));
+            else mbar_arrive(&acc_empty[as]);
+          }
+        };
+        if (row_base >= p.M || n >= p.N || (kDiag && (p.ablate & 2))) { release(); continue; }
+        // the stores of this warp's previous item have read the staging boxes
+        auto stage_begin = [&]() {
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+        };
+        auto put = [&](int piece, uint4 o) { *reinterpret_cast<uint4*>(stg_row + ((piece ^ stg_sw) << 4)) = o; };
+        auto stage_end = [&]() {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && !(kDiag && (p.ablate & 1))) {
+            tma_store_2d(&tm_c, out_buf, n, row_base);
+            if (row_base + OUT_BOX_ROWS < p.M) tma_store_2d(&tm_c, out_buf + OUT_BUF_BYTES, n, row_base + OUT_BOX_ROWS);
+            tma_store_commit();
+          }
+        };
+        if constexpr (EPI == EPI_DEQUANT) {
+          const uint32_t sc = sc_tile + 64 * c * 4;
+          uint32_t va[32], vb[32];
+          tmem_ld_32x32b_x32(t_tile + 64 * c, va);
+          tmem_ld_32x32b_x32(t_tile + 64 * c + 32, vb);
+          tmem_ld_wait(va, vb);
+          release();
+          stage_begin();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) put(k, dequant_piece<KIND>(&va[8 * k], sa2, lds_f4_ro(sc + 32 * k), lds_f4_ro(sc + 32 * k + 16)));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) put(4 + k, dequant_piece<KIND>(&vb[8 * k], sa2, lds_f4_ro(sc + 128 + 32 * k), lds_f4_ro(sc + 128 + 32 * k + 16)));
+          stage_end();
+        } else if constexpr (EPI == EPI_SILU) {
+          // gate columns 64 c .. 64 c + 63 of the tile's first half, the matching up columns BN / 2 further on
+          const uint32_t scg = sc_tile + 64 * c * 4, scu = scg + (BN / 2) * 4;
+          const float2 sah2 = pk2(0.5f * sa, 0.5f * sa);      // the gate is dequantised straight to gate / 2 (exact halving)
+          uint32_t g[16], u[16];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {                      // 16 output columns -> pieces 2 h, 2 h + 1
+            tmem_ld_32x32b_x16(t_tile + 64 * c + 16 * h, g);
+            tmem_ld_32x32b_x16(t_tile + BN / 2 + 64 * c + 16 * h, u);
+            tmem_ld_wait(g, u);
+            if (h == 0) stage_begin();
+            if (h == 3) release();
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+              const int k = 2 * h + kk;
+              const float4 g_lo = lds_f4_ro(scg + 32 * k), g_hi = lds_f4_ro(scg + 32 * k + 16);
+              const float4 u_lo = lds_f4_ro(scu + 32 * k), u_hi = lds_f4_ro(scu + 32 * k + 16);
+              const float2 sg[4] = {{g_lo.x, g_lo.y}, {g_lo.z, g_lo.w}, {g_hi.x, g_hi.y}, {g_hi.z, g_hi.w}};
+              const float2 su[4] = {{u_lo.x, u_lo.y}, {u_lo.z, u_lo.w}, {u_hi.x, u_hi.y}, {u_hi.z, u_hi.w}};
+              uint32_t o[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 hv = dequant2<KIND>(g[8 * kk + 2 * i], g[8 * kk + 2 * i + 1], sah2, sg[i]);
+                const float2 up = dequant2<KIND>(u[8 * kk + 2 * i], u[8 * kk + 2 * i + 1], sa2, su[i]);
+                o[i] = pack_half2_from(fmul2(silu_from_half2(hv), up));
+              }
+              put(k, make_uint4(o[0], o[1], o[2], o[3]));
+            }
+          }
+          stage_end();
+        } else {
+          // one 64-wide head: x0 = its columns 0..31, x1 = columns 32..63; piece k of x0 and piece k of x1 rotate
+          // together.  Half a head (16 columns of each) is in registers at a time.
+          const uint32_t sc = sc_tile + 64 * c * 4;
+          const bool rotated = n < p.rot_cols;
+          if (rotated && !trig_scaled) {          // sin and cos premultiplied by the token scale, once per row block
+            trig_scaled = true;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) { sn2[k] = fmul2(sn2[k], sa2); cs2[k] = fmul2(cs2[k], sa2); }
+          }
+          uint32_t x0[16], x1[16];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            tmem_ld_32x32b_x16(t_tile + 64 * c + 16 * hh, x0);
+            tmem_ld_32x32b_x16(t_tile + 64 * c + 32 + 16 * hh, x1);
+            tmem_ld_wait(x0, x1);
+            if (hh == 0) stage_begin(); else release();
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+              const int k = 2 * hh + kk;           // piece of x0 / x1
+              const float4 a_lo = lds_f4_ro(sc + 32 * k), a_hi = lds_f4_ro(sc + 32 * k + 16);
+              const float4 b_lo = lds_f4_ro(sc + 128 + 32 * k), b_hi = lds_f4_ro(sc + 128 + 32 * k + 16);
+              if (rotated) {
+                const float2 sb0[4] = {{a_lo.x, a_lo.y}, {a_lo.z, a_lo.w}, {a_hi.x, a_hi.y}, {a_hi.z, a_hi.w}};
+                const float2 sb1[4] = {{b_lo.x, b_lo.y}, {b_lo.z, b_lo.w}, {b_hi.x, b_hi.y}, {b_hi.z, b_hi.w}};
+                uint32_t o0[4], o1[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  // y = acc * sB[n];  out0 = y0*(sA cos) - y1*(sA sin),  out1 = y0*(sA sin) + y1*(sA cos), each as one
+                  // rounded product and one fused multiply-add (the CPU model rounds at the same points)
+                  const float2 y0 = fmul2(pk2(acc_to_float<KIND>(x0[8 * kk + 2 * i]), acc_to_float<KIND>(x0[8 * kk + 2 * i + 1])), sb0[i]);
+                  const float2 y1 = fmul2(pk2(acc_to_float<KIND>(x1[8 * kk + 2 * i]), acc_to_float<KIND>(x1[8 * kk + 2 * i + 1])), sb1[i]);
+                  const float2 c2 = cs2[4 * k + i], s2 = sn2[4 * k + i];
+                  const float2 qa = fmul2(y1, s2), ta = fmul2(y1, c2);
+                  o0[i] = pack_half2_from(__ffma2_rn(y0, c2, make_float2(-qa.x, -qa.y)));
+                  o1[i] = pack_half2_from(__ffma2_rn(y0, s2, ta));
+                }
+                put(k, make_uint4(o0[0], o0[1], o0[2], o0[3]));
+                put(4 + k, make_uint4(o1[0], o1[1], o1[2], o1[3]));
+              } else {
+                put(k, dequant_piece<KIND>(&x0[8 * kk], sa2, a_lo, a_hi));
+                put(4 + k, dequant_piece<KIND>(&x1[8 * kk], sa2, b_lo, b_hi));
+              }
+            }
+          }
+          stage_end();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FUSEQ ? EPI_REGS_FUSEQ : EPI_REGS));
     // ------------------------------ epilogue ----------------------------------
@@ -573,16 +860,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
     for (int pc = 0; pc < 8; ++pc) stg_off[pc] = (lane & 15) * 128 + ((pc ^ (lane & 7)) << 4);
 
-    TileWalk<SCHED> tw; tw.start(p);
+    GP_DECL(e_total); GP_DECL(e_acc); GP_DECL(e_read); GP_DECL(e_ld); GP_BEGIN(gp_e0);
+    Walk tw; tw.start(p);
     if constexpr (EPI != EPI_I32) {
       if (tw.valid(p)) {
-        const int r = tw.m * BM + q * 32 + lane;
+        const int r = rowblk(tw.m) * BM + q * 32 + lane;
         if (r < p.M) sa_next = p.scale_a ? __ldg(p.scale_a + r) : 1.f;
       }
     }
     for (int it = 0; tw.valid(p); ++it) {
-      const int m_blk = tw.m, n_blk = tw.n;
+      const int m_blk = rowblk(tw.m), n_blk = tw.n;
       tw.next(p);                            // tw is now the NEXT tile
+      const int nxt_m = rowblk(tw.m);        // its row block (meaningful while tw.valid)
       const int as = it & 1; const uint32_t aph = (it >> 1) & 1;
       const int m0 = m_blk * BM;
       const int n0 = n_blk * OUT_COLS_PER_TILE;
@@ -602,7 +891,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           // rotated ones (the V part of a QKV projection, walked last), the rows of the NEXT row block are
           // fetched already, a tile or more before they are needed; otherwise at the row block's first tile.
           int want = m_blk;
-          if (n0 + wout0 >= p.rot_cols && tw.valid(p)) want = tw.m;
+          if (n0 + wout0 >= p.rot_cols && tw.valid(p)) want = nxt_m;
           if (want != trig_m_blk) {
             trig_m_blk = want;
             trig_scaled = false;
@@ -627,14 +916,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int j = 0; j < 16; ++j) { sn2[j] = fmul2(sn2[j], s2); cs2[j] = fmul2(cs2[j], s2); }
           }
         }
-        if (!FUSEQ && tw.valid(p) && tw.m != m_blk) {
-          const int r = tw.m * BM + q * 32 + lane;
+        if (!FUSEQ && tw.valid(p) && nxt_m != m_blk) {
+          const int r = nxt_m * BM + q * 32 + lane;
           sa_next = (r < p.M) ? (p.scale_a ? ldg_f_here(p.scale_a + r) : 1.f) : 0.f;
         }
       }
 
       // warp-uniform outcome of the bounded wait: the tcgen05.ld below needs the whole warp
+      GP_BEGIN(gp_tw);
       const bool got = mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as, budget);
+      GP_END(e_acc, gp_tw);
       uint32_t agreed = __all_sync(0xffffffffu, got) ? 1u : 0u;
       if (!agreed) break;
       asm volatile("" : "+r"(agreed));   // opaque from here on: the scale address below must stay dependent on the wait
@@ -657,6 +948,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           }
         }
       }
+      if constexpr (PAIR && EPI != EPI_I32) {
+        // of a pair, each CTA's scales report to a barrier of its own (buffer sbuf is filled for the (it / SCALE_BUFS)-th time)
+        if (copy_scales) {
+          const bool have = mbar_wait(&sc_full[sbuf], (uint32_t)(WRES ? 0 : it / Map::SCALE_BUFS) & 1u, abort_flag,
+                                      ST_TIMEOUT_EPILOGUE, (2u << 16) | 0x600 | sbuf, budget);
+          if (!__all_sync(0xffffffffu, have)) break;
+        }
+      }
       // The tile's channel scales landed with its first K block, before the MMAs that have now completed.
       // They are read with loads the compiler may move across the staging stores below (plain loads would
       // be kept in order with every store to shared memory); the address depends on the outcome of the
@@ -671,10 +970,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       auto release = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[as]);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_remote(mapa_shared(smem_u32(&acc_empty[as]), 0));    // the barrier of the CTA that issues the MMAs
+          else mbar_arrive(&acc_empty[as]);
+        }
       };
 
-      if (row_base < p.M && !(kDiag && (p.ablate & 2))) {
+      if (row_base < p.M && !(kDiag && ((p.ablate & 2) || ((p.ablate & 8) && half == 1)))) {
         if constexpr (EPI == EPI_I32) {
           // raw accumulators, direct 16-byte stores
           auto emit = [&](const uint32_t (&v)[32], int c) {
@@ -759,8 +1061,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             auto pair_begin = [&]() {
               buf_a = obuf; buf_b = (obuf + 1 == OUT_BUFS) ? 0 : obuf + 1;
               if constexpr (!DIRECT) {
+                GP_BEGIN(gp_tr);
                 if (lane == 0) tma_store_wait_read<OUT_BUFS - 2>();   // the stores that last used these two buffers have read them
                 __syncwarp();
+                GP_END(e_read, gp_tr);
               }
             };
             uint4 held[2];                       // direct stores: the even piece of a 32-byte sector waits for the odd one
@@ -869,10 +1173,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               // instruction cache holds makes the warps stall on instruction fetch
 #pragma unroll 1
               for (int c = 0; c < WACC; c += 64) {
+                GP_BEGIN(gp_l0);
                 tmem_ld_wait(xa0, xa1);
+                GP_END(e_ld, gp_l0);
                 ldh(c, 1, xb0, xb1);
                 emit(xa0, xa1, c, 0);
+                GP_BEGIN(gp_l1);
                 tmem_ld_wait(xb0, xb1);
+                GP_END(e_ld, gp_l1);
                 if (c + 64 < WACC) ldh(c + 64, 0, xa0, xa1); else release();
                 emit(xb0, xb1, c, 1);
               }
@@ -922,12 +1230,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         release();
       }
     }
+    GP_END(e_total, gp_e0);
+    if (lane == 0 && q == 0) { GP_STORE(5 + 4 * half, e_total); GP_STORE(6 + 4 * half, e_acc); GP_STORE(7 + 4 * half, e_read); GP_STORE(8 + 4 * half, e_ld); }
     if (lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before();
-  __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if constexpr (PAIR) {
+    // neither CTA leaves (or frees tensor memory) while the other may still arrive at its barriers or its MMAs write here
+    cluster_sync_all();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc_pair(tmem_base, TMEM_COLS); }
+  } else {
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  }
 }
 
 }  // namespace gsb

@@ -18,3 +18,16 @@ def test_no_kernel_spills_registers():
     # every tcgen05 kernel keeps one CTA per SM: its register allocation fits the register file
     for name, v in res.items():
         assert v["registers"] <= 255, name
+
+
+def test_twelve_warp_gemm_register_pool_covers_its_resplit():
+    """The twelve-epilogue-warp GEMM raises its epilogue warps to 152 registers with setmaxnreg, which waits for the
+    CTA's pool: 512 threads x the compiled register count must cover 128 x 56 + 384 x 152 (the host checks the same
+    through cudaFuncGetAttributes before it ever launches that form)."""
+    from gigaslop_b200 import build
+    build.build()
+    res = {k: v for k, v in build.kernel_resources().items() if "gemm_tcgen05_kernel" in k and k.endswith("Li12EEEv14CUtensorMap_stS1_S1_S1_NS_10GemmParamsE")}
+    assert len(res) >= 12, sorted(res)
+    for name, v in res.items():
+        assert 512 * v["registers"] >= 128 * 56 + 384 * 152, (name, v)
+        assert 512 * v["registers"] <= 65536, (name, v)
