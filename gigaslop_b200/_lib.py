@@ -21,6 +21,7 @@ SIGNATURES = {
     "gsb200_device_status": (_i32, [C.POINTER(C.c_uint32)]),
     "gsb200_set_spin_budget": (_i32, [C.c_uint32]),
     "gsb200_set_sm_limit": (_i32, [_i32]),
+    "gsb200_set_gemm_variant": (_i32, [_i32, _i32]),
     "gsb200_selftest_wait_timeout": (_i32, [_p]),
     "gsb200_tensor_peak_probe": (_i32, [_i32, _i32, _i32, _p, C.POINTER(C.c_int32), _p]),
     "gsb200_tensor_map_encodes": (_i64, []),

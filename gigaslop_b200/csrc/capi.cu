@@ -19,6 +19,11 @@ int32_t gsb200_device_status(uint32_t out[4]) {
 
 int32_t gsb200_set_spin_budget(uint32_t clocks) { return set_spin_budget(clocks); }
 
+int32_t gsb200_set_gemm_variant(int32_t epilogue_warps, int32_t cta_pairs) {
+  if ((epilogue_warps != -1 && epilogue_warps != 8 && epilogue_warps != 12) || cta_pairs < -1 || cta_pairs > 1) return GSB200_ERR_BAD_ARG;
+  set_gemm_variant(epilogue_warps, cta_pairs);
+  return GSB200_OK;
+}
 int32_t gsb200_set_sm_limit(int32_t sms) {
   if (sms < 0) return GSB200_ERR_BAD_ARG;
   set_sm_limit(sms);

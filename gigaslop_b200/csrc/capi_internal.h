@@ -66,6 +66,7 @@ int32_t launch_tensor_peak_probe(int kind, int n, int mmas, long long* clocks, i
 int32_t ensure_device();          // validates the current device once, returns GSB200_OK / error
 int sm_count();                   // SMs of the current device (cached), capped by set_sm_limit
 int sm_count_physical();          // SMs of the current device, whatever the cap
+void set_gemm_variant(int epilogue_warps, int cta_pairs);   // -1 = by shape
 void set_sm_limit(int sms);       // process-wide cap for the grids of the persistent GEMM kernels (0 = none)
 // Tiled 2-D tensor map of a row-major [rows, cols] tensor (served from a per-thread table when the same
 // arguments come again); false if the driver refuses it.

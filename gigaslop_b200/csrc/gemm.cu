@@ -94,9 +94,7 @@ static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const v
 // ---- per-device state -------------------------------------------------------------------------
 // Atomics: the contract allows one host thread per GPU, and two of them may meet here.
 constexpr int kMaxDevices = 64;
-constexpr int kPairMinRowBlocks = 4 * 148;     // below this many 128-row blocks the single-CTA kernels are used
-constexpr bool kDefaultTwelveWarps = false;    // defaults of the variant choice (see Variant below)
-constexpr bool kDefaultPairs = false;
+constexpr int kVariantMinRowBlocks = 256;      // below this many 128-row blocks every shape runs the eight-warp single-CTA kernel
 static std::atomic<int> g_dev_ok[kMaxDevices];       // 0 unknown, 1 ok, -1 unsupported
 static std::atomic<int> g_dev_sms[kMaxDevices];
 
@@ -207,18 +205,22 @@ static int variant_dispatch(int kind, int epi, bool pair, bool ew12, bool launch
   }
 }
 
-// Environment switches for comparisons: GSB200_GEMM_PAIR = 0 never / 1 whenever the shape allows (unset: by size);
-// GSB200_GEMM_EW = 8 / 12 epilogue warps (unset: the default below).
-static int env_choice(const char* name, std::atomic<int>& state) {
-  int s = state.load(std::memory_order_relaxed);
-  if (s == 0) {
-    const char* e = getenv(name);
-    s = e ? 2 + atoi(e) : 1;               // 1 = unset, 2 + value otherwise
-    state.store(s, std::memory_order_relaxed);
+// Process-wide override of the variant choice (-1 = by shape); the environment variables GSB200_GEMM_EW (8 / 12) and
+// GSB200_GEMM_PAIR (0 / 1) give the initial value, read once.
+static std::atomic<int> g_variant_ew{-2}, g_variant_pair{-2};       // -2 = environment not read yet
+static int variant_setting(std::atomic<int>& v, const char* env) {
+  int s = v.load(std::memory_order_relaxed);
+  if (s == -2) {
+    const char* e = getenv(env);
+    s = (e && *e) ? atoi(e) : -1;
+    v.store(s, std::memory_order_relaxed);
   }
   return s;
 }
-static std::atomic<int> g_env_pair{0}, g_env_ew{0};
+void set_gemm_variant(int epilogue_warps, int cta_pairs) {
+  g_variant_ew.store(epilogue_warps, std::memory_order_relaxed);
+  g_variant_pair.store(cta_pairs, std::memory_order_relaxed);
+}
 
 int32_t ensure_device() {
   int dev = 0;
@@ -387,9 +389,13 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   const bool variants = !fused && !p.direct_store && (a.kind == KIND_I8 || a.kind == KIND_F8) &&
                         (a.epi == EPI_DEQUANT || a.epi == EPI_ROTARY || a.epi == EPI_SILU);
   if (variants) {
-    const int ew = env_choice("GSB200_GEMM_EW", g_env_ew), pm = env_choice("GSB200_GEMM_PAIR", g_env_pair);
-    ew12 = ew == 1 ? kDefaultTwelveWarps : ew == 2 + 12;
-    const bool want_pair = p.k_blocks >= 2 && sms >= 2 && (pm == 1 ? (kDefaultPairs && p.m_blocks >= kPairMinRowBlocks) : pm == 2 + 1);
+    // Defaults, from measurements at the benchmark's sizes: twelve warps pay for the SwiGLU epilogue (the heaviest
+    // per output), pairs for the streaming schedule (K > 512: both operands come from L2 for every tile, and a pair
+    // halves the W part); everywhere else the eight-warp single-CTA kernel is as fast or faster.
+    const int ew = variant_setting(g_variant_ew, "GSB200_GEMM_EW"), pm = variant_setting(g_variant_pair, "GSB200_GEMM_PAIR");
+    ew12 = ew < 0 ? (a.epi == EPI_SILU && p.m_blocks >= kVariantMinRowBlocks) : ew == 12;
+    const bool want_pair = p.k_blocks >= 2 && sms >= 2 &&
+                           (pm < 0 ? (!resident && a.epi == EPI_DEQUANT && p.m_blocks >= kVariantMinRowBlocks) : pm == 1);
     if (ew12 && !variant_dispatch(a.kind, a.epi, false, true, false, ta, tb0, tb1, tc, p, 0, resident, st)) ew12 = false;
     if (want_pair) {
       int cap = variant_dispatch(a.kind, a.epi, true, ew12, false, ta, tb0, tb1, tc, p, 0, resident, st);

@@ -287,10 +287,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   static_assert(EW == EPI_WARPS || (EW == 12 && !FUSEQ && (EPI == EPI_DEQUANT || EPI == EPI_ROTARY || EPI == EPI_SILU)),
                 "twelve epilogue warps: built for the dequant, rotary and SwiGLU epilogues");
   constexpr int NTHREADS = 32 * (FRONT_WARPS + EW);
-  // EW = 12: the epilogue's unit of work is an ITEM, 32 rows x 64 output columns; every item hands its part of the
-  // accumulator stage back by itself
+  // EW = 12: the epilogue's unit of work is an ITEM, 32 rows x 64 output columns.  Every epilogue warp hands every
+  // accumulator stage back once (also for a tile in which it has no item: the MMA warp may then never run more than
+  // two tiles ahead of ANY epilogue warp, which is what keeps each warp's barrier phases in step).
   constexpr int ITEMS = (EPI == EPI_SILU || EPI == EPI_SILU_MX) ? 2 : 4;
-  constexpr int ACC_RELEASES = (EW == 12 ? 4 * ITEMS : EPI_WARPS) * (PAIR ? 2 : 1);
+  constexpr int ACC_RELEASES = EW * (PAIR ? 2 : 1);
   using Walk = TileWalk<SCHED, PAIR>;
   constexpr int NSTAGE = Map::NSTAGE;
   constexpr bool WRES = SCHED == SCHED_WRES;
@@ -488,7 +489,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         else umma_commit(bar);
       };
       int s = 0; uint32_t ph = 0; bool ok = true;
-      GP_DECL(m_total); GP_DECL(m_acc); GP_DECL(m_full); GP_BEGIN(gp_m0);
+      GP_DECL(m_total); GP_DECL(m_acc); GP_DECL(m_full); GP_DECL(m_res); GP_BEGIN(gp_m0);
       if (WRES && !(kDiag && (p.ablate & 4))) {
         ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200, budget);
         tc_fence_after();
@@ -507,10 +508,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const bool rb_first = tw.first(), rb_last = tw.last();
         if (ARES && rb_first && it != 0) rph ^= 1;
         for (int kb = 0; kb < p.k_blocks && !(kDiag && (p.ablate & 4)); ++kb) {
-          GP_BEGIN(gp_tf);
+          GP_BEGIN(gp_tr0);
           if constexpr (ARES) {
             if (rb_first && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
           }
+          GP_END(m_res, gp_tr0);
+          GP_BEGIN(gp_tf);
           if (!mbar_wait(&full_bar[s], ph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | s, budget)) { ok = false; break; }
           GP_END(m_full, gp_tf);
           tc_fence_after();
@@ -540,7 +543,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         if (ok) commit(&acc_full[as]);          // accumulator complete
       }
-      GP_END(m_total, gp_m0); GP_STORE(0, m_total); GP_STORE(1, m_acc); GP_STORE(2, m_full);
+      GP_END(m_total, gp_m0); GP_STORE(0, m_total); GP_STORE(1, m_acc); GP_STORE(2, m_full); GP_STORE(13, m_res);
     }
   } else if constexpr (FUSEQ) {
     // ------------------------------ activation quantiser (warps 2 and 3) ------------------------------
@@ -646,9 +649,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // Three warps per SM sub-partition (the eight-warp epilogue is bound by the latency of each warp's own chain:
     // tensor-memory load -> arithmetic -> staging -> store issue).  Warp e reads TMEM lane quarter e % 4.  The
     // quarter's work is a stream of items -- (tile, 64-column group): a head of the QKV projection, 64 gate + 64 up
-    // columns of the SwiGLU -- dealt to its three warps in turn.  An item loads its accumulator columns, returns
-    // them to the MMA warp at once (the stage's barrier counts items), computes, stages one pair of 16-row boxes and
-    // issues their TMA stores.
+    // columns of the SwiGLU -- dealt to its three warps in turn.  An item loads its accumulator columns, computes,
+    // stages one pair of 16-row boxes and issues their TMA stores; a warp returns the accumulator stage to the MMA
+    // warp when the columns of its last item of the tile are in registers.
     const int e = warp - FRONT_WARPS;      // 0..11
     const int q = warp & 3;                // TMEM lane quarter
     const int j = e >> 2;                  // which of the quarter's three warps
@@ -698,7 +701,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       asm volatile("" : "+r"(agreed));     // the scale address below stays dependent on the wait
       tc_fence_after();
       if constexpr (PAIR) {
-        if (copy_scales) {
+        if (copy_scales && !(kDiag && (p.ablate & 4))) {
           const bool have = mbar_wait(&sc_full[sbuf], (uint32_t)(WRES ? 0 : it / Map::SCALE_BUFS) & 1u, abort_flag,
                                       ST_TIMEOUT_EPILOGUE, (2u << 16) | 0x600 | sbuf, budget);
           if (!__all_sync(0xffffffffu, have)) break;
@@ -708,17 +711,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!WRES && ++sbuf == Map::SCALE_BUFS) sbuf = 0;
       const uint32_t t_tile = tmem_base + as * BN + ((uint32_t)(q * 32) << 16);
       const float2 sa2 = pk2(sa, sa);
+      auto release_stage = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_remote(mapa_shared(smem_u32(&acc_empty[as]), 0));
+          else mbar_arrive(&acc_empty[as]);
+        }
+      };
+      if (first >= ITEMS) release_stage();   // no item in this tile
 #pragma unroll 1
       for (int c = first; c < ITEMS; c += 3) {
         const int n = n0 + 64 * c;           // first output column of the item
-        auto release = [&]() {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (PAIR) mbar_arrive_remote(mapa_shared(smem_u32(&acc_empty[as]), 0));
-            else mbar_arrive(&acc_empty[as]);
-          }
-        };
+        const bool last_item = c + 3 >= ITEMS;
+        auto release = [&]() { if (last_item) release_stage(); };
         if (row_base >= p.M || n >= p.N || (kDiag && (p.ablate & 2))) { release(); continue; }
         // the stores of this warp's previous item have read the staging boxes
         auto stage_begin = [&]() {
@@ -950,7 +956,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       if constexpr (PAIR && EPI != EPI_I32) {
         // of a pair, each CTA's scales report to a barrier of its own (buffer sbuf is filled for the (it / SCALE_BUFS)-th time)
-        if (copy_scales) {
+        if (copy_scales && !(kDiag && (p.ablate & 4))) {
           const bool have = mbar_wait(&sc_full[sbuf], (uint32_t)(WRES ? 0 : it / Map::SCALE_BUFS) & 1u, abort_flag,
                                       ST_TIMEOUT_EPILOGUE, (2u << 16) | 0x600 | sbuf, budget);
           if (!__all_sync(0xffffffffu, have)) break;

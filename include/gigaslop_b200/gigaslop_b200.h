@@ -62,6 +62,12 @@ int32_t gsb200_set_spin_budget(uint32_t clocks); /* bound (SM clocks) for device
  * for the whole process: it applies to every device and every host thread, and not to the LSTM kernels (whose CTAs
  * wait on one another and are always launched in full). */
 int32_t gsb200_set_sm_limit(int32_t sms);
+/* Tuning override for the dequant / rotary / SwiGLU GEMMs on 8-bit operands, which exist with eight or twelve epilogue
+ * warps and with one CTA or a CTA pair (tcgen05 cta_group::2) per tile; every form gives the same bytes.
+ * epilogue_warps: 8 or 12; cta_pairs: 0 or 1; -1 = chosen by shape (the default).  A shape a form cannot run (fewer
+ * than two K blocks for pairs) falls back to the eight-warp single-CTA kernel.  One setting for the whole process;
+ * the environment variables GSB200_GEMM_EW / GSB200_GEMM_PAIR give its initial value.  No reference counterpart. */
+int32_t gsb200_set_gemm_variant(int32_t epilogue_warps, int32_t cta_pairs);
 /* Launches one warp that waits on a barrier nothing signals; with a small spin budget the wait gives up and
  * sets bit 2 of the status word.  Exercises the give-up path without hanging the device. */
 int32_t gsb200_selftest_wait_timeout(gsb200_stream_t stream);
