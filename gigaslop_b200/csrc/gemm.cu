@@ -103,7 +103,7 @@ static cudaError_t set_attr() {
   cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
+  constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_ROTARY_GEN || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
   return cudaFuncSetAttribute(gemm_tcgen05_kernel<KIND, EPI, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               GEMM_SMEM_BYTES);
 }
@@ -120,7 +120,7 @@ static cudaError_t set_attr() {
 //   shared-memory traffic per tile.
 template <int KIND, int EPI, bool PAIR, int EW>
 struct Variant {
-  static constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
+  static constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_ROTARY_GEN || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
   static constexpr int THREADS = 32 * (FRONT_WARPS + EW);
   using Fn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmParams);
   static Fn kernel(bool resident) {
@@ -242,7 +242,7 @@ int32_t ensure_device() {
       set_attr<KIND_I8, EPI_I32>(),     set_attr<KIND_I8, EPI_DEQUANT>(), set_attr<KIND_I8, EPI_ROTARY>(),
       set_attr<KIND_I8, EPI_SILU>(),    set_attr<KIND_F8, EPI_DEQUANT>(), set_attr<KIND_F8, EPI_ROTARY>(),
       set_attr<KIND_F8, EPI_SILU>(),    set_attr<KIND_F8, EPI_SILU_MX>(), set_attr<KIND_F16, EPI_DEQUANT>(),
-      set_attr<KIND_F16, EPI_BIAS>()};
+      set_attr<KIND_F16, EPI_BIAS>(),   set_attr<KIND_I8, EPI_ROTARY_GEN>(), set_attr<KIND_F8, EPI_ROTARY_GEN>()};
   for (cudaError_t er : errs)
     if (er != cudaSuccess) return cuda_status(er, "cudaFuncSetAttribute");
   {
@@ -285,7 +285,7 @@ static cudaError_t launch_inst(const CUtensorMap& ta, const CUtensorMap& tb0, co
   // resident-operand schedule: rotary and the bias epilogue keep A (activation-stationary: one CTA reads a row
   // block's A completely before it writes any of that row block's output, which is what lets the low-rank
   // projection keep its intermediate inside the output buffer), the others keep W (weight-stationary)
-  constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
+  constexpr int RES = (EPI == EPI_ROTARY || EPI == EPI_ROTARY_GEN || EPI == EPI_BIAS) ? SCHED_ARES : SCHED_WRES;
   if (resident) gemm_tcgen05_kernel<KIND, EPI, RES><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
   else gemm_tcgen05_kernel<KIND, EPI, SCHED_STREAM><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
   return cudaGetLastError();
@@ -328,12 +328,19 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
       return GSB200_ERR_BAD_ARG;
   }
   int rot_cols = 0;
+  bool general_rotary = false;
   if (a.epi == EPI_ROTARY) {
     if (!a.sin_tab || !a.cos_tab || !aligned16(a.sin_tab) || !aligned16(a.cos_tab)) return GSB200_ERR_BAD_ARG;
     if (a.seqlen < 1 || a.nhead < 1 || a.row_offset < 0) return GSB200_ERR_BAD_ARG;
-    if (a.head_dim != 64 || a.rotary_dim != 64) return GSB200_ERR_UNSUPPORTED;
+    if (a.head_dim <= 0 || a.rotary_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1)) return GSB200_ERR_BAD_ARG;
+    // heads of 64 or 128 columns, the first 32 / 64 / 96 / 128 of them rotated (pairs are handled 16 columns at a time)
+    if ((a.head_dim != 64 && a.head_dim != 128) || a.rotary_dim % 32 != 0) return GSB200_ERR_UNSUPPORTED;
     rot_cols = 2 * a.nhead * a.head_dim;
-    if (rot_cols > a.N || a.N % 64 != 0) return GSB200_ERR_BAD_ARG;
+    if (rot_cols > a.N || a.N % a.head_dim != 0) return GSB200_ERR_BAD_ARG;
+    if (a.head_dim != 64 || a.rotary_dim != 64) {
+      if (fused) return GSB200_ERR_UNSUPPORTED;         // the fused quantiser is built for the 64 / 64 epilogue only
+      general_rotary = true;
+    }
   }
   int32_t rc = ensure_device();
   if (rc != GSB200_OK) return rc;
@@ -351,6 +358,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   p.sin_tab = a.sin_tab; p.cos_tab = a.cos_tab;
   p.seqlen = a.seqlen > 0 ? a.seqlen : 1;
   p.rot_cols = rot_cols;
+  p.head_dim = a.head_dim; p.rot_half = a.rotary_dim / 2;
   p.row_offset = (int)(a.row_offset % p.seqlen);
   p.direct_store = (a.flags & GSB200_DIAG_FLAG_MASK & GSB200_DIAG_FLAG_DIRECT_STORE) ? 1 : 0;
   p.ablate = ((a.flags & GSB200_DIAG_FLAG_MASK) >> 8) & 15;
@@ -386,7 +394,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   // buffers need that), and enough row blocks that pairs of SMs stay busy.  From here on a "row block" of the
   // schedule is the pair's 256 rows and `sms` counts pairs.
   bool pair = false, ew12 = false;
-  const bool variants = !fused && !p.direct_store && (a.kind == KIND_I8 || a.kind == KIND_F8) &&
+  const bool variants = !fused && !general_rotary && !p.direct_store && (a.kind == KIND_I8 || a.kind == KIND_F8) &&
                         (a.epi == EPI_DEQUANT || a.epi == EPI_ROTARY || a.epi == EPI_SILU);
   if (variants) {
     // Defaults, from measurements at the benchmark's sizes: twelve warps pay for the SwiGLU epilogue (the heaviest
@@ -443,6 +451,8 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
         if (fused) {
           gemm_tcgen05_kernel<KIND_I8, EPI_ROTARY, SCHED_ARES, true><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(ta, tb0, tb1, tc, p);
           e = cudaGetLastError();
+        } else if (general_rotary) {
+          e = launch_inst<KIND_I8, EPI_ROTARY_GEN>(ta, tb0, tb1, tc, p, grid, resident, st);
         } else {
           e = launch_inst<KIND_I8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st);
         }
@@ -453,7 +463,10 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   } else if (a.kind == KIND_F8) {
     switch (a.epi) {
       case EPI_DEQUANT: e = launch_inst<KIND_F8, EPI_DEQUANT>(ta, tb0, tb1, tc, p, grid, resident, st); break;
-      case EPI_ROTARY: e = launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st); break;
+      case EPI_ROTARY:
+        e = general_rotary ? launch_inst<KIND_F8, EPI_ROTARY_GEN>(ta, tb0, tb1, tc, p, grid, resident, st)
+                           : launch_inst<KIND_F8, EPI_ROTARY>(ta, tb0, tb1, tc, p, grid, resident, st);
+        break;
       case EPI_SILU: e = launch_inst<KIND_F8, EPI_SILU>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       case EPI_SILU_MX: e = launch_inst<KIND_F8, EPI_SILU_MX>(ta, tb0, tb1, tc, p, grid, resident, st); break;
       default: return GSB200_ERR_BAD_ARG;

@@ -4,7 +4,8 @@
 //
 //   EPI_I32      raw int32 accumulators                       (bit-exact tier)
 //   EPI_DEQUANT  f16( acc * sA[m] * sB[n] )                   per-token x per-channel dequant
-//   EPI_ROTARY   dequant, then rotate-half on the Q|K columns  (QKV projection)
+//   EPI_ROTARY   dequant, then rotate-half on the Q|K columns  (QKV projection; heads of 64, all of it rotated)
+//   EPI_ROTARY_GEN  the same for heads of 64 or 128 columns of which the first 32, 64, 96 or 128 are rotated
 //   EPI_SILU     f16( silu(gate) * up ), gate|up in one UMMA   (SwiGLU dual GEMM)
 //   EPI_SILU_MX  the same product emitted as MXFP8: E4M3 elements + one E8M0 scale per 32 output columns
 //   EPI_BIAS     f16( acc * sA[m] + b[n] )                    second GEMM of the low-rank input projection
@@ -40,7 +41,7 @@
 
 namespace gsb {
 
-enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3, EPI_SILU_MX = 4, EPI_BIAS = 5 };
+enum : int { EPI_I32 = 0, EPI_DEQUANT = 1, EPI_ROTARY = 2, EPI_SILU = 3, EPI_SILU_MX = 4, EPI_BIAS = 5, EPI_ROTARY_GEN = 6 };
 enum : int { KIND_I8 = 0, KIND_F8 = 1, KIND_F16 = 2 };   // F16: fp16 operands (K counted in bytes = 2 per element), f32 accumulate
 enum : int { SCHED_STREAM = 0, SCHED_WRES = 1, SCHED_ARES = 2 };
 
@@ -126,7 +127,9 @@ struct GemmParams {
   const float* sin_tab;        // [seqlen_max, 32]
   const float* cos_tab;
   int seqlen;                  // runtime sequence length: angle row = (row + row_offset) % seqlen
-  int rot_cols;                // 2 * nhead * head_dim: columns below this are rotated (head_dim = 64, rotary_dim = 64)
+  int rot_cols;                // 2 * nhead * head_dim: the Q and K columns
+  int head_dim;                // EPI_ROTARY_GEN: 64 or 128 (EPI_ROTARY: 64)
+  int rot_half;                // EPI_ROTARY_GEN: rotary_dim / 2, a multiple of 16 (EPI_ROTARY: 32); also the width of a sin / cos row
   int row_offset;              // global row index of this shard's row 0
   const __half* x_f16;         // fused activation quantiser: fp16 activations [M, K] (the int8 A operand is then made on chip)
   long long ldx;               //   row stride of x_f16 in elements
@@ -1005,6 +1008,73 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (c + 64 < WACC) tmem_ld_32x32b_x32(t_row + c + 64, va); else release();
             emit(vb, c + 32);
           }
+        } else if constexpr (EPI == EPI_ROTARY_GEN) {
+          // Any head of 64 or 128 columns with its first 2 * rot_half columns rotated: x0 = columns [0, rot_half) of
+          // the head, x1 = [rot_half, 2 rot_half), the rest of the head and every V column only dequantised
+          // (cute/ampere_gemm_i8_rotary.py:362-393).  Same arithmetic, rounded at the same points, as EPI_ROTARY; 16
+          // columns of x0 and the matching 16 of x1 at a time, sin / cos rows read per use, 32-byte stores straight
+          // from registers (a rotated pair can lie 64 columns apart, further than one staging box is wide).
+          const float2 sa2 = pk2(sa, sa);
+          __half* drow = reinterpret_cast<__half*>(p.C) + (long long)row * p.ldc;
+          const bool wide_ok = (reinterpret_cast<uintptr_t>(drow) & 31) == 0;
+          auto store16 = [&](int n, const uint32_t (&o)[8]) {          // 16 fp16 at output column n
+            if (!row_ok) return;
+            __half* dst = drow + n;
+            if (wide_ok && (n & 15) == 0) stg_v8(dst, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+            else {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+          };
+          auto plain16 = [&](int lc) {                                   // local column lc of this warp's 128: dequant only
+            uint32_t v[16], o[8];
+            tmem_ld_32x32b_x16(t_row + lc, v);
+            tmem_ld_wait(v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = pack_half2_from(dequant2<KIND>(v[2 * i], v[2 * i + 1], sa2, scp(lc + 2 * i)));
+            store16(n0 + wout0 + lc, o);
+          };
+          const long long pos = ((long long)row + p.row_offset) % p.seqlen;
+          const float* srow = p.sin_tab + pos * p.rot_half;
+          const float* crow = p.cos_tab + pos * p.rot_half;
+#pragma unroll 1
+          for (int hc = 0; hc < WACC; hc += p.head_dim) {             // the heads inside this warp's 128 columns
+            const int nh = n0 + wout0 + hc;
+            if (nh >= p.N) break;
+            int done = 0;                                              // columns of the head finished so far
+            if (nh < p.rot_cols) {
+#pragma unroll 1
+              for (int u = 0; u < p.rot_half; u += 16) {
+                uint32_t x0[16], x1[16], o0[8], o1[8];
+                tmem_ld_32x32b_x16(t_row + hc + u, x0);
+                tmem_ld_32x32b_x16(t_row + hc + p.rot_half + u, x1);
+                float4 sv[4], cv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  sv[i] = row_ok ? __ldg(reinterpret_cast<const float4*>(srow + u) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                  cv[i] = row_ok ? __ldg(reinterpret_cast<const float4*>(crow + u) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                tmem_ld_wait(x0, x1);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float4 s4 = sv[i >> 1], c4 = cv[i >> 1];
+                  const float2 s2 = fmul2((i & 1) ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y), sa2);   // sA sin
+                  const float2 c2 = fmul2((i & 1) ? make_float2(c4.z, c4.w) : make_float2(c4.x, c4.y), sa2);   // sA cos
+                  const float2 y0 = fmul2(pk2(acc_to_float<KIND>(x0[2 * i]), acc_to_float<KIND>(x0[2 * i + 1])), scp(hc + u + 2 * i));
+                  const float2 y1 = fmul2(pk2(acc_to_float<KIND>(x1[2 * i]), acc_to_float<KIND>(x1[2 * i + 1])), scp(hc + p.rot_half + u + 2 * i));
+                  const float2 qa = fmul2(y1, s2), ta = fmul2(y1, c2);
+                  o0[i] = pack_half2_from(__ffma2_rn(y0, c2, make_float2(-qa.x, -qa.y)));
+                  o1[i] = pack_half2_from(__ffma2_rn(y0, s2, ta));
+                }
+                store16(nh + u, o0);
+                store16(nh + p.rot_half + u, o1);
+              }
+              done = 2 * p.rot_half;
+            }
+#pragma unroll 1
+            for (int lc = done; lc < p.head_dim; lc += 16) plain16(hc + lc);
+          }
+          release();
         } else if constexpr (EPI == EPI_SILU_MX) {
           // SwiGLU product quantised per 32 output columns: e = biased exponent of the block maximum,
           // scale byte = clamp(e - 8, 0, 254) (value 2^(byte-127)), elements = e4m3_rn_satfinite(v * 2^(127-byte)).

@@ -111,11 +111,14 @@ int32_t gsb200_gemm_i8_f16(const int8_t* A, int64_t lda, const int8_t* B, int64_
 
 /* QKV projection with rotary embedding fused into the epilogue.  TensorOpGemmI8Rotary
  * (cute/ampere_gemm_i8_rotary.py:44-397; wrapper called at cute/main_rotary.cpp:158).
- * Columns [0, 2*nhead*head_dim) are rotated per head (x0 = first half, x1 = second half of the
- * head; out0 = x0*cos - x1*sin, out1 = x0*sin + x1*cos), the rest (V) passes through.
+ * In every head of the columns [0, 2*nhead*head_dim) the first rotary_dim columns are rotated (x0 = columns
+ * [0, rotary_dim/2), x1 = [rotary_dim/2, rotary_dim) of the head; out0 = x0*cos - x1*sin, out1 = x0*sin + x1*cos); the
+ * rest of the head and the V columns pass through (cute/ampere_gemm_i8_rotary.py:362-393).
  * sin/cos are fp32 [>= seqlen, rotary_dim/2] row-major; the angle row of output row m is
  * (m + row_offset) % seqlen (row_offset lets a shard of M keep global positions).
- * Built for head_dim = rotary_dim = 64; N % 64 == 0. */
+ * head_dim 64 or 128, rotary_dim 32, 64, 96 or 128 (<= head_dim), N % head_dim == 0; other values return
+ * GSB200_ERR_UNSUPPORTED.  head_dim = rotary_dim = 64, the shape the reference exports and benchmarks, has a
+ * kernel of its own; the others share a general (slower) epilogue.  The FP8 twin and its limits are the same. */
 int32_t gsb200_gemm_i8_rotary_f16(const int8_t* A, int64_t lda, const int8_t* B, int64_t ldb, void* C,
                                   int64_t ldc, const float* scale_a, const float* scale_b, const float* sin_tab,
                                   const float* cos_tab, int64_t M, int32_t N, int32_t K, int32_t nhead,

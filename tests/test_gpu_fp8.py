@@ -78,6 +78,19 @@ def test_fp8_rotary_shapes(M, seqlen):
     assert_close(c, ref.half(), atol=float(ref.abs().max()) * 2 ** -9, rtol=2e-2, what="fp8 rotary")
 
 
+@pytest.mark.parametrize("head_dim,rotary_dim,nhead,M,seqlen", [(128, 128, 4, 300, 2048), (128, 64, 2, 1000, 333), (64, 32, 8, 700, 100)])
+def test_fp8_rotary_other_head_and_rotary_dims(head_dim, rotary_dim, nhead, M, seqlen):
+    g = need_lib()
+    K, N = 512, 3 * nhead * head_dim
+    gen = torch.Generator().manual_seed(177 + M + head_dim)
+    A, sa = oracle.fp8_quantize_per_token(torch.randn(M, K, generator=gen))
+    W, sb = rand_e4m3(gen, N, K), rand_scales(gen, N)
+    sn, cs = oracle.rope_tables(seqlen, rotary_dim // 2, head_dim)
+    c = g.gemm_fp8_rotary(A.cuda(), W.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(), nhead, head_dim, rotary_dim, seqlen)
+    ref = oracle.fp8_rotary_ref(A, W, sa, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen)
+    assert_close(c, ref.half(), atol=float(ref.abs().max()) * 2 ** -9, rtol=2e-2, what="fp8 rotary, general heads")
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 2048, 512), (1000, 256, 512), (64, 136, 128)])
 def test_fp8_dual_silu(M, N, K):
     g = need_lib()

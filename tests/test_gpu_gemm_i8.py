@@ -210,9 +210,14 @@ def test_bad_arguments_are_rejected_before_launch():
     sn = torch.zeros(16, 32, device="cuda")
     with pytest.raises(RuntimeError):
         g.gemm_i8_rotary(A, B, s, s, sn, sn, 8, 64, 64, 16)  # 2*nhead*head_dim > N
-    sn64 = torch.zeros(16, 64, device="cuda")
+    sn48 = torch.zeros(16, 48, device="cuda")
     with pytest.raises(RuntimeError):
-        g.gemm_i8_rotary(A, B, s, s, sn64, sn64, 1, 128, 128, 16)  # unsupported head_dim
+        g.gemm_i8_rotary(A, B, s, s, sn48, sn48, 1, 96, 96, 16)    # unsupported head_dim
+    sn24 = torch.zeros(16, 24, device="cuda")
+    with pytest.raises(RuntimeError):
+        g.gemm_i8_rotary(A, B, s, s, sn24, sn24, 1, 64, 48, 16)    # unsupported rotary_dim
+    with pytest.raises(RuntimeError):
+        g.gemm_i8_rotary(A, B, s, s, sn48, sn48, 1, 64, 96, 16)    # rotary_dim > head_dim
     with pytest.raises(RuntimeError):
         g.gemm_i8(A.cpu(), B.cpu(), s.cpu(), s.cpu())        # no CPU path
     for bad_flags in (1, 2, 0x100, 0x200, 16):
@@ -395,3 +400,25 @@ def test_tensor_maps_are_cached_per_thread():
     g.gemm_i8_rotary(A, W, sa, sw, sn, cs, 8, 64, 64, 128, out=out2)
     assert int(L.gsb200_tensor_map_encodes()) == n0 + 1
     assert torch.equal(out2, first)
+
+
+@pytest.mark.parametrize("head_dim,rotary_dim,nhead,M,K,seqlen,row_offset",
+                         [(128, 128, 4, 300, 512, 2048, 0), (128, 64, 2, 1000, 512, 333, 7), (64, 32, 8, 700, 256, 100, 0),
+                          (128, 32, 1, 130, 384, 64, 0), (128, 96, 3, 2500, 512, 2048, 1536), (128, 128, 4, 700, 1024, 77, 0),
+                          (64, 32, 5, 20000, 512, 2048, 0)])
+def test_rotary_other_head_and_rotary_dims(head_dim, rotary_dim, nhead, M, K, seqlen, row_offset):
+    """Heads of 128 columns and partially rotated heads (the columns of a head past rotary_dim pass through, as the V
+    columns do): the general epilogue against the same exact-accumulator model, bit for bit."""
+    g = need_lib()
+    N = 3 * nhead * head_dim
+    gen = torch.Generator().manual_seed(6000 + head_dim + rotary_dim + M)
+    A, sa = oracle.quantize_tensor(torch.randn(M, K, generator=gen))
+    B, sb = rand_i8(gen, N, K), rand_scales(gen, N)
+    sn, cs = oracle.rope_tables(max(seqlen, 16), rotary_dim // 2, head_dim)
+    c = g.gemm_i8_rotary(A.cuda(), B.cuda(), sa.cuda(), sb.cuda(), sn.cuda(), cs.cuda(), nhead, head_dim, rotary_dim, seqlen,
+                         row_offset=row_offset)
+    assert g.device_status()[0] == 0
+    exact = rotary_rows(oracle.rotary_exact, A, sa, B, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen, row_offset)
+    assert f16_equal_up_to_signed_zero(c, exact) == 0
+    ref = rotary_rows(oracle.rotary_ref, A, sa, B, sb, sn, cs, nhead, head_dim, rotary_dim, seqlen, row_offset)
+    assert_close(c, ref.half(), atol=2 * float(ref.abs().max()) * 2 ** -11, rtol=1e-2, what="rotary vs reference math")

@@ -28,7 +28,7 @@ def force():
 @pytest.mark.parametrize("M,N,K", [(128, 256, 256), (129, 520, 512), (1000, 1536, 384), (4096 + 130, 512, 2048), (70000, 512, 256)])
 def test_dequant_variants(force, ew, pair, M, N, K):
     g = need_lib()
-    force(force, ew, pair)
+    force(ew, pair)
     gen = torch.Generator().manual_seed(77 + M + N + K)
     A, B = rand_i8(gen, M, K), rand_i8(gen, N, K)
     sa, sb = rand_scales(gen, M, 5e-3, 5e-2), rand_scales(gen, N)
@@ -42,7 +42,7 @@ def test_dequant_variants(force, ew, pair, M, N, K):
                                                          (700, 77, 3, 640, 3), (2500, 100, 0, 256, 6)])
 def test_rotary_variants(force, ew, pair, M, seqlen, row_offset, K, nhead):
     g = need_lib()
-    force(force, ew, pair)
+    force(ew, pair)
     head_dim = rotary_dim = 64
     N = 3 * nhead * head_dim
     gen = torch.Generator().manual_seed(3000 + M + seqlen)
@@ -71,7 +71,7 @@ def test_dual_silu_variants_agree(force, ew, pair, M, N, K):
     args = (A.cuda(), Wg.cuda(), Wu.cuda(), sa.cuda(), sg.cuda(), su.cuda())
     force(8, 0)
     base = g.dual_gemm_i8_silu(*args)
-    force(force, ew, pair)
+    force(ew, pair)
     got = g.dual_gemm_i8_silu(*args)
     assert g.device_status()[0] == 0
     assert_bitexact(got, base, f"SwiGLU, {ew} epilogue warps, pair={pair}")
