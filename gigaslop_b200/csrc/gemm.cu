@@ -440,6 +440,10 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   cudaError_t e = cudaErrorInvalidValue;
   if (pair || ew12) {
     if (pair) grid *= 2;
+    // the twelve-warp form stores a warp's 32 rows x 64 columns as ONE box
+    if (ew12 && !make_map_2d(&tc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.C, (uint64_t)a.M, (uint64_t)a.N, (uint64_t)a.ldc,
+                             OUT_BOX_COLS, 2 * OUT_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_128B))
+      return GSB200_ERR_BAD_ARG;
     e = (cudaError_t)variant_dispatch(a.kind, a.epi, pair, ew12, true, ta, tb0, tb1, tc, p, grid, resident, st);
     return cuda_status(e, "gemm launch");
   }

@@ -429,14 +429,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (ARES && rb_first && it != 0) rph ^= 1;
         // A comes from HBM with a latency the small ring cannot cover: ask for it in L2 well ahead.
         //   WRES: the row block two tiles on (one CTA of the group asks, the others find it in L2)
-        //   ARES: this CTA's next row block, at the start of the current one
+        //   ARES: this CTA's next row block, when the last tile of the current one is requested
         if constexpr (WRES) {
           const int pm = tw.m + 2 * p.n_groups;
           if (pm < p.m_blocks && rot == n_blk)
             for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, rowblk(pm) * BM);
           if (++rot == p.n_blocks) rot = 0;
         } else if constexpr (ARES) {
-          if (!FUSEQ && rb_first) {
+          // (asked for at the row block's first tile, six tiles ahead, the lines are gone from L2 again when the
+          // block is loaded -- 201 MB of output pass through it meanwhile -- and the wait for the resident block doubles)
+          if (!FUSEQ && tw.n == tw.n_hi - 1) {
             const int nm = tw.next_row_block(p);
             if (nm >= 0)
               for (int kb = 0; kb < p.k_blocks; ++kb) tma_prefetch_l2_2d(&tm_a, kb * BK, rowblk(nm) * BM);
@@ -739,8 +741,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && !(kDiag && (p.ablate & 1))) {
+            // the two 16-row boxes lie one after the other: one store of a 32-row box (this form's output map), which
+            // clips the rows past M
             tma_store_2d(&tm_c, out_buf, n, row_base);
-            if (row_base + OUT_BOX_ROWS < p.M) tma_store_2d(&tm_c, out_buf + OUT_BUF_BYTES, n, row_base + OUT_BOX_ROWS);
             tma_store_commit();
           }
         };
