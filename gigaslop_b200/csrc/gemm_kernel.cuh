@@ -405,16 +405,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (bytes) { mbar_arrive_expect_tx(&sc_full[sb], bytes); load_scales(scale_base + sb * BN, n0, &sc_full[sb]); }
       };
       int sbuf = 0;                           // scale buffer of the current tile
-      if constexpr (WRES) {
+      // WRES: every K block of the resident W slice has a barrier of its own, and a single CTA requests them one by one
+      // beside the first tile's A blocks, so the first MMAs start after 48 KiB have landed instead of 144 (a pair asks
+      // for its W halves up front: its producer has no registers left for the interleaved form)
+      auto load_w_block = [&](int kb, int n0, int n1) {
+        mbar_arrive_expect_tx(&res_full[kb], B_STAGE_BYTES + (kb == 0 ? scale_bytes(n0) : 0u));
+        if (kb == 0) load_scales(scale_base, n0, &res_full[0]);
+        load_b(res_base + kb * Map::B_BYTES, &res_full[kb], kb * BK, n0, n1);
+      };
+      if constexpr (WRES && PAIR) {
         const int n0 = (Walk::cta() % p.n_blocks) * OUT_COLS_PER_TILE;
         const int n1 = DUAL ? n0 : n0 + BN / 2;
-        if constexpr (PAIR) {
-          load_scales_own(0, n0);
-          expect(&res_full[0], p.k_blocks * Map::B_BYTES);
-        } else {
-          mbar_arrive_expect_tx(&res_full[0], p.k_blocks * B_STAGE_BYTES + scale_bytes(n0));
-          load_scales(scale_base, n0, &res_full[0]);
-        }
+        load_scales_own(0, n0);
+        expect(&res_full[0], p.k_blocks * Map::B_BYTES);
         for (int kb = 0; kb < p.k_blocks; ++kb) load_b(res_base + kb * Map::B_BYTES, &res_full[0], kb * BK, n0, n1);
       }
       uint32_t rph = 0;                       // ARES: phase of the resident-A barriers, flips per row block
@@ -460,6 +463,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const uint32_t sc_bytes = (!PAIR && !WRES && kb == 0) ? scale_bytes(n0) : 0u;
           if (PAIR && !WRES && kb == 0) load_scales_own(sbuf, n0);
           if constexpr (WRES) {
+            if (!PAIR && it == 0) load_w_block(kb, n0, n1);
             expect(&full_bar[s], A_STAGE_BYTES);
             load_a(st, &full_bar[s], kb * BK, m0);
           } else if constexpr (ARES) {
@@ -495,7 +499,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       };
       int s = 0; uint32_t ph = 0; bool ok = true;
       GP_DECL(m_total); GP_DECL(m_acc); GP_DECL(m_full); GP_DECL(m_res); GP_BEGIN(gp_m0);
-      if (WRES && !(kDiag && (p.ablate & 4))) {
+      if (WRES && PAIR && !(kDiag && (p.ablate & 4))) {       // a pair waits for its whole W slice (one barrier) before the first MMA
         ok = mbar_wait(&res_full[0], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200, budget);
         tc_fence_after();
       }
@@ -516,6 +520,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           GP_BEGIN(gp_tr0);
           if constexpr (ARES) {
             if (rb_first && !mbar_wait(&res_full[kb], rph, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x300 | kb, budget)) { ok = false; break; }
+          } else if constexpr (WRES && !PAIR) { // the W slice arrives during the first tile, K block by K block
+            if (it == 0 && !mbar_wait(&res_full[kb], 0, abort_flag, ST_TIMEOUT_MMA, (1u << 16) | 0x200 | kb, budget)) { ok = false; break; }
           }
           GP_END(m_res, gp_tr0);
           GP_BEGIN(gp_tf);
