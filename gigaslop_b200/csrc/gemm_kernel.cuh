@@ -72,18 +72,18 @@ constexpr int SCALE_BUF_BYTES = BN * 4;                 // channel scales of one
 //   WRES:   [W slice 4 x 32 KiB][A ring 3 x 16 KiB]       [staging 8 warps x 3 x 2 KiB][scales 1 KiB][barriers]
 //   ARES:   [A block 4 x 16 KiB][B ring 3 x 32 KiB]       [staging 8 warps x 3 x 2 KiB][scales 6 x 1 KiB][barriers]
 //   PAIR (two CTAs on one tcgen05.mma.cta_group::2): a CTA holds only HALF of the tile's W rows (16 KiB per K block), and
-//   the memory that frees goes into deeper rings (4 stages streaming, 6 with a resident operand).
+//   the memory that frees goes into deeper rings (5 stages streaming, 6 with a resident operand).
 //   EW = 12 (twelve epilogue warps, each working on 64-column items): one box pair (4 KiB) of staging per warp.
 template <int SCHED, bool PAIR = false, int EW = EPI_WARPS>
 struct SmemMap {
   static constexpr int B_BYTES = PAIR ? B_STAGE_BYTES / 2 : B_STAGE_BYTES;      // W bytes per K block in one CTA
-  static constexpr int NSTAGE = !PAIR ? gsb::NSTAGE : SCHED == SCHED_STREAM ? 4 : 6;
+  static constexpr int NSTAGE = !PAIR ? gsb::NSTAGE : SCHED == SCHED_STREAM ? 5 : 6;
   static constexpr int RES_BYTES = SCHED == SCHED_WRES ? RES_MAX_KBLOCKS * B_BYTES
                                  : SCHED == SCHED_ARES ? RES_MAX_KBLOCKS * A_STAGE_BYTES : 0;
   static constexpr int STAGE_BYTES = SCHED == SCHED_WRES ? A_STAGE_BYTES
                                    : SCHED == SCHED_ARES ? B_BYTES : A_STAGE_BYTES + B_BYTES;
   static constexpr int RING_OFF = RES_BYTES;
-  static constexpr int OUT_BUFS = EW == 12 ? 2 : SCHED == SCHED_STREAM ? 4 : 3;   // 2 KiB staging boxes per epilogue warp
+  static constexpr int OUT_BUFS = EW == 12 ? 2 : (SCHED == SCHED_STREAM && !PAIR) ? 4 : 3;   // 2 KiB staging boxes per epilogue warp
   // Channel-scale buffers, filled by the producer beside each tile's first K block.  A weight-stationary
   // CTA keeps one column block, hence one buffer.  Otherwise tile j uses buffer j % 6: when the producer
   // fills it again (tile j + 6) it holds a ring slot the MMA warp freed at most ceil(NSTAGE / k_blocks) <= 3
@@ -104,7 +104,8 @@ static_assert(SmemMap<0>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<1>::USED + 1
               SmemMap<2>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<0, true>::USED + 1024 <= GEMM_SMEM_BYTES &&
               SmemMap<1, true>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<2, true>::USED + 1024 <= GEMM_SMEM_BYTES &&
               SmemMap<0, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<1, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES &&
-              SmemMap<2, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES,
+              SmemMap<2, false, 12>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<0, true, 12>::USED + 1024 <= GEMM_SMEM_BYTES &&
+              SmemMap<1, true, 12>::USED + 1024 <= GEMM_SMEM_BYTES && SmemMap<2, true, 12>::USED + 1024 <= GEMM_SMEM_BYTES,
               "shared memory budget");
 static_assert(GEMM_SMEM_BYTES > 116 * 1024, "one CTA per SM is what makes the 512-column TMEM allocation safe");
 
