@@ -578,15 +578,23 @@ def run_native(args):
     outs = [torch.empty(M, N, dtype=torch.float16, device=dev) for _ in range(NSETS)]
     row_offset = rank * M
 
-    # A step = quantise batch b, then the QKV+rotary GEMM on it.  The steps are captured into a CUDA graph, twelve to
+    # A step = quantise batch b, then the QKV+rotary GEMM on it.  The steps are captured into CUDA graphs, twelve to
     # a replay (four passes over the three buffer sets), so that the two kernels of a step follow each other without
     # the gap an eager launch leaves; every step's two kernels are launched, and finish, inside the timed region.
-    # Steps that do not fill a replay are launched eagerly, also inside the timed region.
+    # Steps that do not fill a twelve-step replay run from a second, shorter graph.  The last graph launched in the
+    # timed region is a copy with CUDA events around three of its GEMMs (an event node costs about 4 us, so not more).
     from gigaslop_b200.devpipe import QkvRotaryGraph
-    runner = QkvRotaryGraph(M, K, N, dev, slots=NSETS)
-    runner.capture(xs, outs, w, s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"], cfg["seqlen"],
-                   row_offset=row_offset, repeat=4, time_gemms=True)
-    G = runner.steps
+    G = 12
+    n_events = 3
+    def make_runner(steps, like=None):
+        r = QkvRotaryGraph(M, K, N, dev, slots=NSETS)
+        if like is not None:
+            r.q, r.s = like.q, like.s                    # one set of int8 buffers for all graphs
+        return r.capture(xs, outs, w, s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"], cfg["seqlen"],
+                         row_offset=row_offset, steps=steps, time_gemms=n_events)
+    runner = make_runner(G)
+    rest = make_runner(args.steps % G, like=runner) if args.steps % G else None
+    last = rest if rest is not None else runner          # the graph whose timed copy closes the region
 
     def eager_step(i):
         b = i % NSETS
@@ -595,11 +603,15 @@ def run_native(args):
                          cfg["seqlen"], row_offset=row_offset, out=outs[b])
 
     def run_steps(n, time_last=False):
-        reps = n // G
+        reps, tail = n // G, n % G
         for r in range(reps):
-            runner.replay(timed=time_last and r == reps - 1)    # the region's last replay carries the GEMM events
-        for i in range(n % G):
-            eager_step(i)
+            runner.replay(timed=time_last and tail == 0 and r == reps - 1)
+        if tail:
+            if rest is not None and tail == rest.steps:
+                rest.replay(timed=time_last)
+            else:
+                for i in range(tail):
+                    eager_step(i)
 
     def barrier():
         torch.cuda.synchronize()
@@ -613,34 +625,30 @@ def run_native(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    runner.replay(timed=True)                        # both graphs uploaded before anything is timed
-    run_steps(args.warmup)
-    barrier()
-    sampler = ClockSampler(local)
+    runner.replay(timed=True)                        # every graph uploaded before anything is timed
+    runner.replay()
+    if rest is not None:
+        rest.replay(timed=True)
+        rest.replay()
+    sampler = ClockSampler(local)                    # (NVML set-up takes milliseconds: before the warm-up, not after it)
     sampler.sample()
-    sampler.start()
+    run_steps(args.warmup)
+    barrier()                                        # nothing but the two event objects between this and the first launch
     t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
     run_steps(args.steps, time_last=True)
     t1.record()
+    # The clock sampler starts once the region's launches are queued (they take the host tens of microseconds, the GPU
+    # works on them for milliseconds): its NVML queries go through the same driver as the launches, and a launch held
+    # up by a query leaves the GPU idle inside a region this short.  Its samples are taken while the region executes.
+    sampler.start()
     barrier()
     sampler.sample()
     sampler.stop_flag = True
     ms_step = max_over_ranks(t0.elapsed_time(t1)) / args.steps
-    # duration of the GEMM launches inside the timed region: the events captured around each GEMM of the graph hold
-    # the times of the region's last replay (twelve launches); with fewer steps than a replay, eager launches are timed
-    if args.steps >= G:
-        gemm_ms = [a.elapsed_time(b) for a, b in runner.gemm_events]
-    else:
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(args.steps, 1))]
-        for i, (ea_, eb_) in enumerate(evs):
-            b = i % NSETS
-            ea_.record()
-            g.gemm_i8_rotary(runner.q[b], w, runner.s[b], s_w, sin, cos, cfg["nhead"], cfg["head_dim"], cfg["rotary_dim"],
-                             cfg["seqlen"], row_offset=row_offset, out=outs[b])
-            eb_.record()
-        torch.cuda.synchronize()
-        gemm_ms = [a.elapsed_time(b) for a, b in evs]
+    # duration of GEMM launches inside the timed region: the events captured around three GEMMs of the region's last
+    # graph launch
+    gemm_ms = [a.elapsed_time(b) for a, b in last.gemm_events]
     st = g.device_status()
     if st[0] != 0:
         raise RuntimeError(f"device status word reports a timed-out wait: {st}")
@@ -746,7 +754,7 @@ def run_native(args):
         "config": {"workload": WORKLOAD,
                    "M_per_gpu": M, "N": N, "K": K, "parallelism": f"row-sharded x{world}, no collective",
                    "l2": f"{NSETS} rotating buffer sets of 302 MB (> 126 MB L2)",
-                   "launch": "devpipe.QkvRotaryGraph: the steps are captured into a CUDA graph (12 steps per replay, one stream) and replayed"},
+                   "launch": "devpipe.QkvRotaryGraph: the steps are captured into a CUDA graph (12 steps per replay, the steps left over from a shorter graph; one stream) and replayed"},
         "tokens_per_s": world * M / (ms_step * 1e-3),
         "kernel_tops": {"qkv_rotary_gemm": gemm_tops,
                         "frac_of_nominal_4500": gemm_tops / NOMINAL_TENSOR_TOPS,
@@ -757,7 +765,7 @@ def run_native(args):
                      "frac": achieved / hbm_peak, "traffic": GEMM_DRAM_TRAFFIC, "peak_source": which,
                      "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS,
                      "kernel": "gemm_tcgen05_kernel<i8, rotary>", "bytes_per_launch": gemm_bytes,
-                     "timed": "CUDA events captured around each GEMM launch of the step graph, on the launching stream: the 12 launches of the timed region's last replay",
+                     "timed": "CUDA events captured in the step graph around GEMM launches, on the launching stream: %d launches of the timed region's last graph launch" % len(gemm_ms),
                      "achieved_alone": gemm_bytes / (gemm_alone_ms * 1e-3) / 1e9,
                      "frac_alone": gemm_bytes / (gemm_alone_ms * 1e-3) / 1e9 / hbm_peak},
         "e2e": {"value": world * ops_step / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,

@@ -83,10 +83,11 @@ class QkvRotaryGraph:
     89-97 us for eager launches on one or two streams, B200).  The reference drives its per-step LSTM launches the same
     way (fly/bench_factored_lstm.py:104-121).  Results are those of the direct calls: same kernels, same arguments.
 
-    ``time_gemms=True`` additionally captures a second graph of the same steps with a pair of CUDA events around
-    every GEMM launch (``replay(timed=True)``; afterwards ``gemm_events[i][0].elapsed_time(gemm_events[i][1])`` is the
-    duration of the i-th GEMM inside the step).  The event nodes cost several microseconds per step, which is why they
-    live in a graph of their own.
+    ``steps`` overrides the number of steps (default ``repeat`` passes over the batches; step i works on batch
+    i % len(xs)).  ``time_gemms`` additionally captures a second graph of the same steps with a pair of CUDA events
+    around GEMM launches (``replay(timed=True)``; afterwards ``gemm_events[i][0].elapsed_time(gemm_events[i][1])`` is
+    the duration of a GEMM inside the step): ``True`` = around every GEMM, an integer n = around n of them, evenly
+    spaced.  An event node costs about 4 us, which is why they live in a graph of their own and can be few.
     """
 
     def __init__(self, M, K, N, device, slots=3):
@@ -100,9 +101,14 @@ class QkvRotaryGraph:
         self.steps = 0
 
     def capture(self, xs, outs, w, s_w, sin, cos, nhead, head_dim, rotary_dim, seqlen, row_offset=0, repeat=1,
-                time_gemms=False):
+                time_gemms=False, steps=None):
         if len(xs) != len(outs) or len(xs) > len(self.q):
             raise ValueError("one output per batch, and no more batches than slots")
+        n_steps = repeat * len(xs) if steps is None else int(steps)
+        if n_steps < 1:
+            raise ValueError("at least one step")
+        n_timed = n_steps if time_gemms is True else min(int(time_gemms), n_steps)
+        timed_at = {(k * n_steps) // n_timed + (n_steps // n_timed) // 2 for k in range(n_timed)} if n_timed else set()
         def one(b, ev):
             ops.quantize_tensor(xs[b], out=self.q[b], out_scale=self.s[b])
             if ev is not None:
@@ -118,19 +124,19 @@ class QkvRotaryGraph:
             self.gemm_events = []
             self.graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(self.graph):
-                for r in range(repeat):
-                    for b in range(len(xs)):
-                        one(b, None)
-            if time_gemms:
+                for i in range(n_steps):
+                    one(i % len(xs), None)
+            if n_timed:
                 self.timed_graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(self.timed_graph):
-                    for r in range(repeat):
-                        for b in range(len(xs)):
+                    for i in range(n_steps):
+                        ev = None
+                        if i in timed_at:
                             ev = (torch.cuda.Event(enable_timing=True, external=True),
                                   torch.cuda.Event(enable_timing=True, external=True))
                             self.gemm_events.append(ev)
-                            one(b, ev)
-            self.steps = repeat * len(xs)
+                        one(i % len(xs), ev)
+            self.steps = n_steps
         return self
 
     def replay(self, timed=False):
