@@ -297,6 +297,39 @@ def test_stream_pipeline_equals_direct_calls():
     assert g.device_status()[0] == 0
 
 
+@pytest.mark.parametrize("steps,time_gemms", [(3, False), (5, 2), (7, True)])
+def test_step_graph_equals_direct_calls(steps, time_gemms):
+    """The step graph (quantiser + GEMM per batch, captured once, any number of steps, with or without event nodes
+    around GEMMs) leaves the bytes of the direct calls in every output, and its events time real launches."""
+    g = need_lib()
+    from gigaslop_b200.devpipe import QkvRotaryGraph
+    gen = torch.Generator().manual_seed(44)
+    M, K, N, seqlen = 2000, 512, 1536, 333
+    W = rand_i8(gen, N, K).cuda()
+    sw = rand_scales(gen, N).cuda()
+    sn, cs = (t.cuda() for t in oracle.rope_tables(seqlen, 32, 64))
+    xs = [(torch.randn(M, K, generator=gen) * (1 + i)).half().cuda() for i in range(3)]
+    want = []
+    for x in xs:
+        q, s = g.quantize_tensor(x)
+        want.append(g.gemm_i8_rotary(q, W, s, sw, sn, cs, 8, 64, 64, seqlen, row_offset=9).cpu())
+    outs = [torch.empty(M, N, dtype=torch.float16, device="cuda") for _ in xs]
+    runner = QkvRotaryGraph(M, K, N, "cuda").capture(xs, outs, W, sw, sn, cs, 8, 64, 64, seqlen, row_offset=9,
+                                                      steps=steps, time_gemms=time_gemms)
+    assert runner.steps == steps
+    for timed in ([False, True] if time_gemms else [False]):
+        for o in outs:
+            o.zero_()
+        runner.replay(timed=timed)
+        torch.cuda.synchronize()
+        for i in range(min(steps, 3)):
+            assert_bitexact(outs[i].cpu(), want[i], f"step graph, batch {i}, timed copy {timed}")
+    if time_gemms:
+        assert len(runner.gemm_events) == (steps if time_gemms is True else time_gemms)
+        assert all(a_.elapsed_time(b_) > 0 for a_, b_ in runner.gemm_events)
+    assert g.device_status()[0] == 0
+
+
 @pytest.mark.parametrize("M,K,nhead,seqlen", [(300, 512, 8, 2048), (128, 128, 8, 64), (1000, 256, 3, 333), (2500, 384, 6, 100),
                                               (40000, 512, 8, 2048)])
 def test_fused_quantise_rotary_equals_two_calls(M, K, nhead, seqlen):
