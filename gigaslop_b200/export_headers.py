@@ -53,8 +53,8 @@ def _hooks(prefix):
 
 
 def rotary_header(K, nhead, head_dim, rotary_dim, seqlen):
-    if head_dim != 64 or rotary_dim != 64:
-        raise ValueError("the rotary epilogue is built for head_dim = rotary_dim = 64")
+    if head_dim not in (64, 128) or rotary_dim not in (32, 64, 96, 128) or rotary_dim > head_dim:
+        raise ValueError("the rotary epilogues take head_dim 64 or 128 and rotary_dim 32 / 64 / 96 / 128 (<= head_dim)")
     N = 3 * nhead * head_dim
     name = f"gemm_i8_rotary_N{N}_K{K}_H{nhead}D{head_dim}R{rotary_dim}S{seqlen}"
     text = (f"/* {name}: W8A8 QKV GEMM + rotary, N = {N}, K = {K}, {nhead} heads x {head_dim}, sin/cos tables of\n"
