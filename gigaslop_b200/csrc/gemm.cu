@@ -397,13 +397,14 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
   const bool variants = !fused && !general_rotary && !p.direct_store && (a.kind == KIND_I8 || a.kind == KIND_F8) &&
                         (a.epi == EPI_DEQUANT || a.epi == EPI_ROTARY || a.epi == EPI_SILU);
   if (variants) {
-    // Defaults, from measurements at the benchmark's sizes: twelve warps pay for the SwiGLU epilogue (the heaviest
-    // per output), pairs for the streaming schedule (K > 512: both operands come from L2 for every tile, and a pair
-    // halves the W part); everywhere else the eight-warp single-CTA kernel is as fast or faster.
+    // Defaults, from measurements at the benchmark's sizes: twelve warps pay for the weight-stationary SwiGLU (the
+    // heaviest epilogue per output), pairs for the streaming schedule with any of the three epilogues (K > 512: both
+    // operands come from L2 for every tile, a single CTA asks for 96 bytes per clock where about 64 arrive, and a
+    // pair halves the W part: 12-22 % at M = 65536); everywhere else the eight-warp single-CTA kernel is as fast or faster.
     const int ew = variant_setting(g_variant_ew, "GSB200_GEMM_EW"), pm = variant_setting(g_variant_pair, "GSB200_GEMM_PAIR");
-    ew12 = ew < 0 ? (a.epi == EPI_SILU && p.m_blocks >= kVariantMinRowBlocks) : ew == 12;
+    ew12 = ew < 0 ? (a.epi == EPI_SILU && resident && p.m_blocks >= kVariantMinRowBlocks) : ew == 12;
     const bool want_pair = p.k_blocks >= 2 && sms >= 2 &&
-                           (pm < 0 ? (!resident && a.epi == EPI_DEQUANT && p.m_blocks >= kVariantMinRowBlocks) : pm == 1);
+                           (pm < 0 ? (!resident && p.m_blocks >= kVariantMinRowBlocks) : pm == 1);
     if (ew12 && !variant_dispatch(a.kind, a.epi, false, true, false, ta, tb0, tb1, tc, p, 0, resident, st)) ew12 = false;
     if (want_pair) {
       int cap = variant_dispatch(a.kind, a.epi, true, ew12, false, ta, tb0, tb1, tc, p, 0, resident, st);
