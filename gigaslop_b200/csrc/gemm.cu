@@ -94,7 +94,8 @@ static bool make_map_2d(CUtensorMap* m, CUtensorMapDataType dt, int esz, const v
 // ---- per-device state -------------------------------------------------------------------------
 // Atomics: the contract allows one host thread per GPU, and two of them may meet here.
 constexpr int kMaxDevices = 64;
-constexpr int kVariantMinRowBlocks = 256;      // below this many 128-row blocks every shape runs the eight-warp single-CTA kernel
+constexpr int kVariantMinRowBlocks = 256;      // 128-row blocks from which the twelve-warp form is the default for the SwiGLU
+constexpr int kPairMinRowBlocks = 16;          // ... and from which the streaming schedule runs as CTA pairs (measured down to M = 2048)
 static std::atomic<int> g_dev_ok[kMaxDevices];       // 0 unknown, 1 ok, -1 unsupported
 static std::atomic<int> g_dev_sms[kMaxDevices];
 
@@ -404,7 +405,7 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     const int ew = variant_setting(g_variant_ew, "GSB200_GEMM_EW"), pm = variant_setting(g_variant_pair, "GSB200_GEMM_PAIR");
     ew12 = ew < 0 ? (a.epi == EPI_SILU && resident && p.m_blocks >= kVariantMinRowBlocks) : ew == 12;
     const bool want_pair = p.k_blocks >= 2 && sms >= 2 &&
-                           (pm < 0 ? (!resident && p.m_blocks >= kVariantMinRowBlocks) : pm == 1);
+                           (pm < 0 ? (!resident && p.m_blocks >= kPairMinRowBlocks) : pm == 1);
     if (ew12 && !variant_dispatch(a.kind, a.epi, false, true, false, ta, tb0, tb1, tc, p, 0, resident, st)) ew12 = false;
     if (want_pair) {
       int cap = variant_dispatch(a.kind, a.epi, true, ew12, false, ta, tb0, tb1, tc, p, 0, resident, st);
