@@ -495,7 +495,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       constexpr uint32_t idesc = (KIND == KIND_I8) ? umma_idesc(2, 1, 1, MMA_M, BN) : umma_idesc(1, 0, 0, MMA_M, BN);
       // completion of the MMAs issued so far -> the barrier (of a pair: the same barrier in both CTAs)
       auto commit = [&](uint64_t* bar) {
-        if constexpr (PAIR) { umma_commit_pair(smem_u32(bar)); umma_commit_pair(mapa_shared(smem_u32(bar), 1)); }
+        if constexpr (PAIR) umma_commit_pair_both(bar);
         else umma_commit(bar);
       };
       int s = 0; uint32_t ph = 0; bool ok = true;

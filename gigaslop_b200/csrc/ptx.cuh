@@ -411,6 +411,14 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
 }
+// The same arrival delivered to the barrier at this shared-memory offset in BOTH CTAs of the pair with one instruction
+// (a commit costs its thread about 58 clocks, and the thread that issues a pair's MMAs has few to spare).  This is
+// the multicast of an mbarrier ARRIVAL; no data moves and no load is involved.
+__device__ __forceinline__ void umma_commit_pair_both(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+               : "memory");
+}
 // shared -> TMEM copy of scale factors (32 lanes x 128 bit, replicated to the 4 lane quarters)
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t s_desc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(s_desc) : "memory");
