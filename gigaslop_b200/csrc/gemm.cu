@@ -401,11 +401,16 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     // Defaults, from measurements at the benchmark's sizes: twelve warps pay for the weight-stationary SwiGLU (the
     // heaviest epilogue per output), pairs for the streaming schedule with any of the three epilogues (K > 512: both
     // operands come from L2 for every tile, a single CTA asks for 96 bytes per clock where about 64 arrive, and a
-    // pair halves the W part: 12-22 % at M = 65536); everywhere else the eight-warp single-CTA kernel is as fast or faster.
+    // pair halves the W part: 12-22 % at M = 65536); the activation-stationary rotary kernel takes both together (twelve
+    // warps alone leave it waiting for operands, pairs alone for its epilogue; together 3 % at config 2 and less
+    // power); everywhere else the eight-warp single-CTA kernel is as fast or faster.
     const int ew = variant_setting(g_variant_ew, "GSB200_GEMM_EW"), pm = variant_setting(g_variant_pair, "GSB200_GEMM_PAIR");
-    ew12 = ew < 0 ? (a.epi == EPI_SILU && resident && p.m_blocks >= kVariantMinRowBlocks) : ew == 12;
+    const bool big = p.m_blocks >= kVariantMinRowBlocks;
+    // twelve warps AND pairs, or neither (so not when the caller has fixed one of the two)
+    const bool rotary_both = a.epi == EPI_ROTARY && resident && big && p.k_blocks >= 2 && sms >= 2 && ew < 0 && pm < 0;
+    ew12 = ew < 0 ? ((a.epi == EPI_SILU && resident && big) || rotary_both) : ew == 12;
     const bool want_pair = p.k_blocks >= 2 && sms >= 2 &&
-                           (pm < 0 ? (!resident && p.m_blocks >= kPairMinRowBlocks) : pm == 1);
+                           (pm < 0 ? ((!resident && p.m_blocks >= kPairMinRowBlocks) || (rotary_both && ew12)) : pm == 1);
     if (ew12 && !variant_dispatch(a.kind, a.epi, false, true, false, ta, tb0, tb1, tc, p, 0, resident, st)) ew12 = false;
     if (want_pair) {
       int cap = variant_dispatch(a.kind, a.epi, true, ew12, false, ta, tb0, tb1, tc, p, 0, resident, st);
