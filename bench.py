@@ -33,8 +33,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the QKV+rotary GEMM at the bench's full size, from an
-# ncu capture of this kernel on this workload (35.5 MB read + 142.5 MB written, the mean of two launches)
-GEMM_DRAM_TRAFFIC = 178.0e6
+# ncu capture of this kernel on this workload (35.6 MB read + 141.5 MB written, the mean of two launches)
+GEMM_DRAM_TRAFFIC = 177.2e6
 WORKLOAD = ("config2: per-token int8 quantise [65536,512] fp16 + W8A8 QKV GEMM N=1536 K=512 "
             "with fused rotary (8 heads x 64, seqlen 2048), per GPU")
 METRIC = "w8a8_qkv_rotary_gemm_tops"
@@ -764,7 +764,7 @@ def run_native(args):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "traffic": GEMM_DRAM_TRAFFIC, "peak_source": which,
                      "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS,
-                     "kernel": "gemm_tcgen05_kernel<i8, rotary>", "bytes_per_launch": gemm_bytes,
+                     "kernel": "gemm_tcgen05_kernel<i8, rotary, activation-stationary, CTA pairs, 12 epilogue warps>", "bytes_per_launch": gemm_bytes,
                      "timed": "CUDA events captured in the step graph around GEMM launches, on the launching stream: %d launches of the timed region's last graph launch" % len(gemm_ms),
                      "achieved_alone": gemm_bytes / (gemm_alone_ms * 1e-3) / 1e9,
                      "frac_alone": gemm_bytes / (gemm_alone_ms * 1e-3) / 1e9 / hbm_peak},
