@@ -28,7 +28,13 @@
 //               (setmaxnreg: 56 per thread for warps 0-3, 224 for the two epilogue warpgroups)
 //   warps 4..11 epilogue, free-running (no barrier between them): tcgen05.ld (thread = accumulator row,
 //               next chunk in flight during the math of the current) -> math -> swizzled smem staging
-//               -> TMA store (per-warp 32 x 32 fp16 boxes, issued in pairs)
+//               -> TMA store (per-warp boxes of 16 rows x 64 fp16, issued in pairs)
+//
+// Two more template parameters give the dequant / rotary / SwiGLU kernels four forms (same bytes from each):
+//   EW = 12    twelve epilogue warps (512 threads, 56 / 152 registers), three per SM sub-partition, each working on
+//              64-column items of its lane quarter's stream of tiles
+//   PAIR       two CTAs of a cluster on one tcgen05.mma.cta_group::2: 256 rows x 256 columns per MMA, half of the
+//              tile's W rows in each CTA's shared memory, barriers of the first CTA collecting both CTAs' loads
 //
 // Two 256-column accumulator stages fill the 512 TMEM columns, so the epilogue of tile i overlaps the
 // MMAs of tile i+1; a warp returns its part of a stage as soon as its last chunk is in registers.  The
