@@ -408,9 +408,14 @@ int32_t launch_gemm(const GemmArgs& a, cudaStream_t st) {
     const bool big = p.m_blocks >= kVariantMinRowBlocks;
     // twelve warps AND pairs, or neither (so not when the caller has fixed one of the two)
     const bool rotary_both = a.epi == EPI_ROTARY && resident && big && p.k_blocks >= 2 && sms >= 2 && ew < 0 && pm < 0;
-    ew12 = ew < 0 ? ((a.epi == EPI_SILU && resident && big) || rotary_both) : ew == 12;
+    // ... and so does the weight-stationary dequant GEMM when its output is far larger than L2 (the hoisted LSTM
+    // projection: 3 % at M = 262144, 5 % at a million rows, nothing at 131072)
+    const bool huge_dequant_both = a.epi == EPI_DEQUANT && resident && p.m_blocks >= 2048 && p.n_blocks >= 4 &&
+                                   p.k_blocks >= 2 && sms >= 2 && ew < 0 && pm < 0;
+    const bool both = rotary_both || huge_dequant_both;
+    ew12 = ew < 0 ? ((a.epi == EPI_SILU && resident && big) || both) : ew == 12;
     const bool want_pair = p.k_blocks >= 2 && sms >= 2 &&
-                           (pm < 0 ? ((!resident && p.m_blocks >= kPairMinRowBlocks) || (rotary_both && ew12)) : pm == 1);
+                           (pm < 0 ? ((!resident && p.m_blocks >= kPairMinRowBlocks) || (both && ew12)) : pm == 1);
     if (ew12 && !variant_dispatch(a.kind, a.epi, false, true, false, ta, tb0, tb1, tc, p, 0, resident, st)) ew12 = false;
     if (want_pair) {
       int cap = variant_dispatch(a.kind, a.epi, true, ew12, false, ta, tb0, tb1, tc, p, 0, resident, st);
