@@ -9,6 +9,7 @@ independent, no collective on the data path).
     python bench.py --gpus N --steps K --warmup W          # this library: one JSON line (rank 0)
     python bench.py --impl reference ...                    # the reference's CPU (PyTorch) math, same JSON shape
     python bench.py --only <op> [--M rows] [--iters n]      # one kernel of the path by itself (profiling target)
+    python bench.py --role-timers <op> [--M rows]           # where one launch of a GEMM kernel waits, role by role
 
 Beside the headline keys the JSON line carries
     configs            every kernel and chain of the five benchmark configurations: CUDA-event time, T(FL)OPS, GB/s
@@ -401,6 +402,48 @@ def run_only(args):
     if ops_:
         line += f", {ops_ / us / 1e6:.0f} T(FL)OPS"
     print(line, "status", G.device_status())
+
+
+ROLE_TIMER_NAMES = ["MMA thread: loop", "MMA thread: waits for accumulator stages", "MMA thread: waits for ring stages",
+                    "producer: waits for free ring stages", "producer: loop", "epilogue warp (column half 0): loop",
+                    "... waits for accumulators", "... waits for its stores to be read", "... waits for tensor-memory loads",
+                    "epilogue warp (column half 1): loop", "... waits for accumulators", "... waits for its stores to be read",
+                    "... waits for tensor-memory loads", "MMA thread: waits for the resident operand"]
+
+
+def run_role_timers(args):
+    """Clocks each role of a GEMM kernel spends in its waits, per CTA: builds the library a second time with
+    -DGSB200_GEMM_PROF (beside the shipped one; the shipped library carries no timers), runs one launch of the
+    kernel in a child process that loads that build, and prints the median / min / max over the CTAs.  The epilogue
+    rows are filled by the eight-warp form only."""
+    import subprocess
+    from gigaslop_b200 import build
+    lib = os.path.join(ROOT, "gigaslop_b200", "libgigaslop_b200_prof.so")
+    if os.environ.get("GIGASLOP_B200_LIB") != lib:
+        build.build(force=True, defines=("GSB200_GEMM_PROF",), out=lib)
+        env = dict(os.environ, GIGASLOP_B200_LIB=lib)
+        raise SystemExit(subprocess.call([sys.executable, os.path.abspath(__file__), "--role-timers", args.role_timers,
+                                          "--M", str(args.M)], env=env))
+    import statistics
+    import gigaslop_b200 as G
+    G.lib()
+    torch.cuda.set_device(0)
+    fn, _, _, _ = build_op(args.role_timers, args.M or 65536)
+    prof = ctypes.CDLL(lib).gsb200_debug_gemm_prof
+    buf = (ctypes.c_longlong * (160 * 16))()
+    for i in range(6):
+        fn(i)
+    torch.cuda.synchronize()
+    prof(buf)                                        # clears the timers
+    fn(0)
+    torch.cuda.synchronize()
+    prof(buf)
+    print(f"{args.role_timers}: clocks per CTA in one launch (median / min / max over the CTAs that reported)")
+    for slot, name in enumerate(ROLE_TIMER_NAMES):
+        v = [buf[c * 16 + slot] for c in range(160) if buf[c * 16 + slot] > 0]
+        if v:
+            print(f"  {name:52s} {statistics.median(v):9.0f} {min(v):9.0f} {max(v):9.0f}   ({len(v)} CTAs)")
+    print("status", G.device_status())
 
 
 def tensor_peak_probe(G):
@@ -799,8 +842,12 @@ def main():
     ap.add_argument("--only", default=None, help="time one kernel of the path by itself: " + ", ".join(OPS))
     ap.add_argument("--M", type=int, default=0, help="rows for --only")
     ap.add_argument("--iters", type=int, default=20, help="timed calls for --only")
+    ap.add_argument("--role-timers", default=None, metavar="OP",
+                    help="per-role wait clocks of one launch of a GEMM kernel (builds a profiling copy of the library)")
     args = ap.parse_args()
-    if args.only:
+    if args.role_timers:
+        run_role_timers(args)
+    elif args.only:
         run_only(args)
     elif args.impl == "reference":
         run_reference(args)
