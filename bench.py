@@ -405,17 +405,17 @@ def run_only(args):
 
 
 ROLE_TIMER_NAMES = ["MMA thread: loop", "MMA thread: waits for accumulator stages", "MMA thread: waits for ring stages",
-                    "producer: waits for free ring stages", "producer: loop", "epilogue warp (column half 0): loop",
+                    "producer: waits for free ring stages", "producer: loop", "epilogue warp 0 of lane quarter 0: loop",
                     "... waits for accumulators", "... waits for its stores to be read", "... waits for tensor-memory loads",
-                    "epilogue warp (column half 1): loop", "... waits for accumulators", "... waits for its stores to be read",
+                    "epilogue warp 1 of lane quarter 0: loop", "... waits for accumulators", "... waits for its stores to be read",
                     "... waits for tensor-memory loads", "MMA thread: waits for the resident operand"]
 
 
 def run_role_timers(args):
     """Clocks each role of a GEMM kernel spends in its waits, per CTA: builds the library a second time with
     -DGSB200_GEMM_PROF (beside the shipped one; the shipped library carries no timers), runs one launch of the
-    kernel in a child process that loads that build, and prints the median / min / max over the CTAs.  The epilogue
-    rows are filled by the eight-warp form only."""
+    kernel in a child process that loads that build, and prints the median / min / max over the CTAs (tensor-memory
+    load waits are timed in the rotary epilogues only)."""
     import subprocess
     from gigaslop_b200 import build
     lib = os.path.join(ROOT, "gigaslop_b200", "libgigaslop_b200_prof.so")

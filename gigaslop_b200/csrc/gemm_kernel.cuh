@@ -684,6 +684,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     bool trig_scaled = false;
     int sbuf = 0;
     int base3 = 0;                         // (tiles so far * ITEMS) % 3
+    GP_DECL(e_total); GP_DECL(e_acc); GP_DECL(e_read); GP_DECL(e_ld); GP_BEGIN(gp_e0);
     Walk tw; tw.start(p);
     for (int it = 0; tw.valid(p); ++it, tw.next(p)) {
       const int m_blk = rowblk(tw.m), n_blk = tw.n;
@@ -713,7 +714,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
       // every warp follows every tile's barrier (also tiles in which it has no item), so the phase it waits for is
       // always the next one
+      GP_BEGIN(gp_tw);
       const bool got = mbar_wait(&acc_full[as], aph, abort_flag, ST_TIMEOUT_EPILOGUE, (2u << 16) | as, budget);
+      GP_END(e_acc, gp_tw);
       uint32_t agreed = __all_sync(0xffffffffu, got) ? 1u : 0u;
       if (!agreed) break;
       asm volatile("" : "+r"(agreed));     // the scale address below stays dependent on the wait
@@ -746,8 +749,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (row_base >= p.M || n >= p.N || (kDiag && (p.ablate & 2))) { release(); continue; }
         // the stores of this warp's previous item have read the staging boxes
         auto stage_begin = [&]() {
+          GP_BEGIN(gp_tr);
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
+          GP_END(e_read, gp_tr);
         };
         auto put = [&](int piece, uint4 o) { *reinterpret_cast<uint4*>(stg_row + ((piece ^ stg_sw) << 4)) = o; };
         auto stage_end = [&]() {
@@ -816,9 +821,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           uint32_t x0[16], x1[16];
 #pragma unroll
           for (int hh = 0; hh < 2; ++hh) {
+            GP_BEGIN(gp_tl);
             tmem_ld_32x32b_x16(t_tile + 64 * c + 16 * hh, x0);
             tmem_ld_32x32b_x16(t_tile + 64 * c + 32 + 16 * hh, x1);
             tmem_ld_wait(x0, x1);
+            GP_END(e_ld, gp_tl);
             if (hh == 0) stage_begin(); else release();
 #pragma unroll
             for (int kk = 0; kk < 2; ++kk) {
@@ -852,6 +859,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       }
     }
+    GP_END(e_total, gp_e0);
+    if (lane == 0 && q == 0 && j < 2) { GP_STORE(5 + 4 * j, e_total); GP_STORE(6 + 4 * j, e_acc); GP_STORE(7 + 4 * j, e_read); GP_STORE(8 + 4 * j, e_ld); }
     if (lane == 0) tma_store_wait_all<0>();
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FUSEQ ? EPI_REGS_FUSEQ : EPI_REGS));
